@@ -1,0 +1,115 @@
+/*
+ * Kernel-level C ABI of the B200 forward engine: plain device pointers, sizes
+ * and a stream; no C++ or framework types.  These are the launchers the layer
+ * classes inside libcaffe.so call, exported so that each kernel can be
+ * parity-tested and timed on its own.  Every pointer is a device pointer
+ * unless it says "host".  `stream` is a cudaStream_t passed as void*.
+ *
+ * Functions return 0 on success, a negative value for a rejected argument,
+ * or a positive cudaError_t.  Kernels that wait on hardware barriers report a
+ * timed-out wait by writing a non-zero code to the int `*status` points at
+ * (device memory, may be NULL); they never spin without a limit.
+ *
+ * Each entry point cites the mini-caffe function whose arithmetic it
+ * replaces (paths relative to that project).
+ */
+#ifndef MCB200_KERNELS_H_
+#define MCB200_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ layout
+ * Activations inside the engine are channels-last: element (n, y, x, c) of a
+ * tensor lives at ((n*H + y)*W + x)*c_stride + c, with c_stride >= C and
+ * c_stride % 4 == 0 for the tensor-core path.  Blobs at the API boundary are
+ * NCHW; mcb200_nchw_to_nhwc / mcb200_nhwc_to_nchw convert.                  */
+
+typedef struct mcb200_conv_shape {
+  int n, h, w, c;          /* input extent                                   */
+  int c_stride;            /* allocated channels per input pixel             */
+  int cout;                /* output channels                                */
+  int kh, kw;
+  int stride_h, stride_w;
+  int pad_h, pad_w;
+  int dil_h, dil_w;
+  int group;               /* 1, or c (depthwise); other values: direct path */
+  int ho, wo;              /* output extent (filled by mcb200_conv_out_shape) */
+} mcb200_conv_shape;
+
+/* Fused tail applied to each accumulator before it is stored:
+ *   v = acc * scale[co] + shift[co]        (either array may be NULL)
+ *   v += residual_coeff * residual[m*residual_ld + co]   (if residual != NULL)
+ *   v = v > 0 ? v : v * slope              (act == 1; slope 0 is plain ReLU)
+ *   v = v > 0 ? v : v * prelu[co or 0]     (act == 2)
+ * It replaces the separate in-place passes of BatchNormLayer, ScaleLayer,
+ * BiasLayer, EltwiseLayer(SUM) and ReLU/PReLULayer
+ * (src/layers/batch_norm_layer.cpp:72-136, scale_layer.cpp:96-113,
+ *  eltwise_layer.cpp:51-57, relu_layer.cpp:12-29, prelu_layer.cpp:52-84).   */
+typedef struct mcb200_epilogue {
+  const float* scale;
+  const float* shift;
+  const float* residual;
+  int residual_ld;
+  float residual_coeff;
+  int act;                 /* 0 none, 1 (leaky) ReLU, 2 PReLU                 */
+  float slope;
+  const float* prelu;
+  int prelu_shared;        /* PReLU: one slope for all channels               */
+  int round_tf32;          /* round stored values to TF32 (next op is a conv) */
+} mcb200_epilogue;
+
+/* Output extent of a convolution: floor((in + 2p - (d(k-1)+1)) / s) + 1
+ * (src/layers/conv_layer.cpp:12-25).  Returns -1 if the window does not fit. */
+int mcb200_conv_out_shape(mcb200_conv_shape* s);
+
+/* Number of floats of the packed tensor-core weight image for `s`:
+ * cout rows of kh*kw taps, each tap padded to a multiple of 32 channels.     */
+size_t mcb200_conv_packed_weight_count(const mcb200_conv_shape* s);
+
+/* Re-lay Caffe weights [cout, c, kh, kw] (src/layers/base_conv_layer.cpp:98-104)
+ * as [cout][kh*kw][roundup(c,32)], rounded to TF32 (round-to-nearest).       */
+int mcb200_conv_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed, void* stream);
+
+/* Opaque-to-C plan: two TMA descriptors and the launch geometry.  Valid while
+ * `in`, `packed_w` stay where they are.  Host memory, 64-byte aligned.       */
+typedef struct mcb200_conv_plan {
+  uint64_t tma_a[16];
+  uint64_t tma_b[16];
+  mcb200_conv_shape shape;
+  int m, k_iters, c_blocks, block_n, im2col;
+  int reserved[3];
+} __attribute__((aligned(64))) mcb200_conv_plan;
+
+/* Implicit-GEMM convolution on the tensor cores (tcgen05.mma kind::tf32,
+ * accumulators in tensor memory, operands fetched by TMA; activations through
+ * an im2col-mode tensor map so no column buffer exists).  group must be 1 and
+ * c_stride % 4 == 0.  Replaces im2col_cpu + caffe_cpu_gemm + forward_cpu_bias
+ * (src/layers/base_conv_layer.cpp:254-278, src/util/im2col.cpp:19-55).
+ * InnerProduct is the same call with h = w = kh = kw = 1
+ * (src/layers/inner_product_layer.cpp:80-93).                                */
+int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float* packed_w,
+                        mcb200_conv_plan* plan);
+int mcb200_conv_tc_launch(const mcb200_conv_plan* plan, float* out, int out_ld,
+                          const mcb200_epilogue* ep, int* status, void* stream);
+
+/* Direct convolution, one thread per output element, any group count; the
+ * fallback for shapes the tensor-core path rejects.  Weights stay in Caffe
+ * order [cout, c/group, kh, kw].                                             */
+int mcb200_conv_direct(const mcb200_conv_shape* s, const float* in, const float* w_oihw, float* out,
+                       int out_ld, const mcb200_epilogue* ep, void* stream);
+
+/* Number of kernels launched by this library on the calling thread since the
+ * last reset (bench.py reports it as gpu_launches).                          */
+long long mcb200_launch_count(void);
+void mcb200_launch_count_reset(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MCB200_KERNELS_H_ */

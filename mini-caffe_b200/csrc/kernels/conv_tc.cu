@@ -1,0 +1,504 @@
+// Convolution / InnerProduct as an implicit GEMM on the Blackwell tensor cores.
+//
+//   D[m, co] = sum over taps (r, s) and channels c of  X[pixel(m) + (r, s), c] * W[co, r, s, c]
+//
+// m runs over the N*Ho*Wo output pixels of a channels-last activation tensor.
+// One CTA computes a 128 x BN tile of D:
+//   warp 0   one elected thread issues the TMA loads.  The activation tile
+//            (128 pixels x 32 channels of one filter tap) comes through an
+//            im2col-mode tensor map, so the hardware walks the output pixels
+//            across image rows and images and zero-fills the padding; the
+//            weight tile (BN x 32) comes through a tiled map.  Both land in
+//            shared memory 128-byte swizzled, K-major.
+//   warp 1   one thread issues tcgen05.mma kind::tf32 (M=128, N=BN, K=8), four per
+//            stage, accumulating in tensor memory; tcgen05.commit hands each
+//            shared-memory stage back to the producer.
+//   warps 2-5 read the accumulator out of tensor memory (tcgen05.ld), apply
+//            the fused tail (per-channel scale/shift, residual add, ReLU or
+//            PReLU) and store channels-last.
+// Every barrier wait is bounded; a timed-out wait raises an abort flag, the
+// roles drain, tensor memory is freed and *status is set.
+//
+// Arithmetic replaced: mini-caffe's per-image im2col + SGEMM + bias GEMM
+// (src/layers/base_conv_layer.cpp:254-278, src/util/im2col.cpp:19-55).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "../../../include/mcb200_kernels.h"
+#include "launch_count.h"
+#include "sm100.cuh"
+
+namespace mcb200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 32;                            // fp32 elements = one 128-byte swizzle row
+constexpr int kTileABytes = kBlockM * kBlockK * 4;     // 16 KiB
+constexpr int kThreads = 192;
+constexpr long long kWaitLimitCycles = 2000000000LL;   // about one second
+
+struct ConvTcArgs {
+  float* out;
+  int out_ld;
+  int m;             // output pixels
+  int cout;
+  int k_iters;       // taps * c_blocks
+  int c_blocks;      // ceil(c / 32)
+  int kw;            // filter width (tap -> (r, s))
+  int ho, wo;
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  mcb200_epilogue ep;
+  int* status;
+};
+
+template <int BN>
+struct SmemPlan {
+  static constexpr int kTileBBytes = BN * kBlockK * 4;
+  static constexpr int kStageBytes = kTileABytes + kTileBBytes;
+  // Two CTAs per SM: stay below ~110 KiB each.
+  static constexpr int kStages = (BN == 256) ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int kDynamicBytes = kStages * kStageBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ float apply_act(float v, int act, float slope) {
+  if (act != 0) v = v > 0.f ? v : v * slope;
+  return v;
+}
+
+template <int BN, bool kIm2col>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const ConvTcArgs args) {
+  using Plan = SmemPlan<BN>;
+  constexpr int kStages = Plan::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[kStages];
+  __shared__ uint64_t empty_bar[kStages];
+  __shared__ uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  // 128-byte swizzled tiles must start on a 1024-byte boundary.
+  const uint32_t raw_addr = smem_addr(smem_raw);
+  uint8_t* tiles = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // Tiles that share an activation tile (same m, different n) get adjacent
+  // block ids so they run together and the tile is fetched from HBM once.
+  const int n_tiles = (args.cout + BN - 1) / BN;
+  const int n_tile = blockIdx.x % n_tiles;
+  const int m_tile = blockIdx.x / n_tiles;
+  const int m0 = m_tile * kBlockM;
+  const int n0 = n_tile * BN;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_descriptor(&map_a);
+    tma_prefetch_descriptor(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_acc = tmem_base_slot;
+  volatile int* abort = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int base_w = 0, base_h = 0, base_n = 0;
+      if (kIm2col) {
+        const int q = m0 % args.wo;
+        const int p = (m0 / args.wo) % args.ho;
+        base_n = m0 / (args.wo * args.ho);
+        base_w = q * args.stride_w - args.pad_w;
+        base_h = p * args.stride_h - args.pad_h;
+      }
+      int issued = 0;
+      for (int it = 0; it < args.k_iters; ++it) {
+        const int s = it % kStages;
+        const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
+        if (!mbar_wait_bounded(&empty_bar[s], phase ^ 1u, abort, kWaitLimitCycles)) break;
+        uint8_t* a_dst = tiles + s * Plan::kStageBytes;
+        uint8_t* b_dst = a_dst + kTileABytes;
+        mbar_expect_tx(&full_bar[s], Plan::kStageBytes);
+        const int tap = it / args.c_blocks;
+        const int cb = it - tap * args.c_blocks;
+        if (kIm2col) {
+          const int r = tap / args.kw;
+          const int sx = tap - r * args.kw;
+          tma_load_im2col_4d(&map_a, &full_bar[s], a_dst, cb * kBlockK, base_w, base_h, base_n,
+                             static_cast<uint16_t>(sx * args.dil_w), static_cast<uint16_t>(r * args.dil_h));
+        } else {
+          tma_load_2d(&map_a, &full_bar[s], a_dst, cb * kBlockK, m0);
+        }
+        tma_load_2d(&map_b, &full_bar[s], b_dst, it * kBlockK, n0);
+        issued = it + 1;
+      }
+      if (*abort) {
+        // Give copies that are still in flight a bounded time to land before
+        // the CTA's shared memory is released.
+        const int first = issued > kStages ? issued - kStages : 0;
+        for (int it = first; it < issued; ++it) {
+          const long long start = clock64();
+          while (!mbar_try_wait(&full_bar[it % kStages], static_cast<uint32_t>(it / kStages) & 1u)) {
+            if (clock64() - start > kWaitLimitCycles / 8) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_tf32(kBlockM, BN);
+      bool ok = true;
+      for (int it = 0; it < args.k_iters; ++it) {
+        const int s = it % kStages;
+        const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
+        if (!mbar_wait_bounded(&full_bar[s], phase, abort, kWaitLimitCycles)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_addr(tiles + s * Plan::kStageBytes);
+        const uint32_t b_addr = a_addr + kTileABytes;
+        const uint64_t desc_a = umma_desc_k_sw128(a_addr);
+        const uint64_t desc_b = umma_desc_k_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 8; ++k) {
+          // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
+          // descriptor's 16-byte address units.
+          umma_tf32(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(&accum_bar);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quad = warp & 3;                  // tensor-memory lanes [32*quad, 32*quad+32)
+    const int row = m0 + quad * 32 + lane;
+    // tcgen05.ld is warp-collective: the whole warp takes the same branch.
+    const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(&accum_bar, 0, abort, kWaitLimitCycles));
+    tc_fence_after_sync();
+    if (ok) {
+      const mcb200_epilogue& ep = args.ep;
+      float* out_row = args.out + static_cast<size_t>(row) * args.out_ld;
+      const float* res_row =
+          ep.residual ? ep.residual + static_cast<size_t>(row) * ep.residual_ld : nullptr;
+      const bool row_ok = row < args.m;
+      const bool vec_ok = ((args.out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0) &&
+                          (!ep.residual || (((ep.residual_ld & 3) == 0) &&
+                                            ((reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0)));
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        const int col0 = n0 + chunk * 32;
+        if (col0 >= args.cout) break;          // uniform across the warp
+        uint32_t acc[32];
+        tmem_load_32x32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chunk * 32),
+                        acc);
+        tmem_load_wait();
+        if (!row_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const int col = col0 + j;
+          if (col >= args.cout) break;
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = col + e;
+            float x = __uint_as_float(acc[j + e]);
+            if (c < args.cout) {
+              if (ep.scale) x *= __ldg(ep.scale + c);
+              if (ep.shift) x += __ldg(ep.shift + c);
+            }
+            v[e] = x;
+          }
+          const bool full4 = vec_ok && (col + 3 < args.cout);
+          if (res_row) {
+            if (full4) {
+              const float4 rr = *reinterpret_cast<const float4*>(res_row + col);
+              v[0] += ep.residual_coeff * rr.x;
+              v[1] += ep.residual_coeff * rr.y;
+              v[2] += ep.residual_coeff * rr.z;
+              v[3] += ep.residual_coeff * rr.w;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (col + e < args.cout) v[e] += ep.residual_coeff * res_row[col + e];
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = col + e;
+            float slope = ep.slope;
+            if (ep.act == 2 && c < args.cout) slope = __ldg(ep.prelu + (ep.prelu_shared ? 0 : c));
+            v[e] = apply_act(v[e], ep.act, slope);
+            if (ep.round_tf32) v[e] = round_to_tf32(v[e]);
+          }
+          if (full4) {
+            *reinterpret_cast<float4*>(out_row + col) = make_float4(v[0], v[1], v[2], v[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < args.cout) out_row[col + e] = v[e];
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_acc, BN);
+  }
+  if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 1);
+}
+
+// ------------------------------------------------------------------ weight packing
+
+__global__ void pack_weights_kernel(const float* __restrict__ w, float* __restrict__ packed, int cout, int c, int taps,
+                                    int c_pad) {
+  const size_t total = static_cast<size_t>(cout) * taps * c_pad;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % c_pad);
+    const int tap = static_cast<int>((i / c_pad) % taps);
+    const int co = static_cast<int>(i / (static_cast<size_t>(c_pad) * taps));
+    float v = 0.f;
+    if (cc < c) v = round_to_tf32(w[(static_cast<size_t>(co) * c + cc) * taps + tap]);
+    packed[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------ tensor maps
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DriverApi {
+  EncodeTiledFn tiled = nullptr;
+  EncodeIm2colFn im2col = nullptr;
+  int driver_version = 0;
+  bool ok = false;
+};
+
+const DriverApi& driver_api() {
+  static DriverApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn)
+      return;
+    api.tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn)
+      return;
+    api.im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+    cudaDriverGetVersion(&api.driver_version);
+    api.ok = true;
+  });
+  return api;
+}
+
+int pick_block_n(int cout) {
+  if (cout <= 64) return 64;
+  if (cout <= 128) return 128;
+  return 256;
+}
+
+template <int BN, bool kIm2col>
+cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args, cudaStream_t stream) {
+  using Plan = SmemPlan<BN>;
+  // The large-shared-memory opt-in is per device: do it once for each device
+  // this process launches on.
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool configured[64] = {false};
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<BN, kIm2col>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Plan::kDynamicBytes);
+      if (e != cudaSuccess) return e;
+      configured[dev] = true;
+    }
+  }
+  const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * ((plan->m + kBlockM - 1) / kBlockM);
+  if (tiles > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  dim3 grid(static_cast<unsigned>(tiles), 1, 1);
+  const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
+  const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
+  conv_tc_kernel<BN, kIm2col><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, args);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace mcb200
+
+using namespace mcb200;
+
+extern "C" int mcb200_conv_out_shape(mcb200_conv_shape* s) {
+  if (!s || s->kh < 1 || s->kw < 1 || s->stride_h < 1 || s->stride_w < 1 || s->dil_h < 1 || s->dil_w < 1) return -1;
+  const int ext_h = s->dil_h * (s->kh - 1) + 1;
+  const int ext_w = s->dil_w * (s->kw - 1) + 1;
+  const int num_h = s->h + 2 * s->pad_h - ext_h;
+  const int num_w = s->w + 2 * s->pad_w - ext_w;
+  if (num_h < 0 || num_w < 0) return -1;
+  s->ho = num_h / s->stride_h + 1;
+  s->wo = num_w / s->stride_w + 1;
+  return 0;
+}
+
+extern "C" size_t mcb200_conv_packed_weight_count(const mcb200_conv_shape* s) {
+  const size_t c_pad = static_cast<size_t>((s->c + kBlockK - 1) / kBlockK) * kBlockK;
+  return static_cast<size_t>(s->cout) * s->kh * s->kw * c_pad;
+}
+
+extern "C" int mcb200_conv_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed,
+                                        void* stream) {
+  if (!s || !w_oihw || !packed || s->group != 1) return -1;
+  const int c_pad = (s->c + kBlockK - 1) / kBlockK * kBlockK;
+  const size_t total = mcb200_conv_packed_weight_count(s);
+  const int threads = 256;
+  const int blocks = static_cast<int>((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
+                                                                                  : 148 * 8);
+  pack_weights_kernel<<<blocks > 0 ? blocks : 1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      w_oihw, packed, s->cout, s->c, s->kh * s->kw, c_pad);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float* packed_w,
+                                   mcb200_conv_plan* plan) {
+  if (!s || !in || !packed_w || !plan) return -1;
+  if (s->group != 1 || (s->c_stride & 3) != 0 || s->c_stride < s->c) return -2;
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(packed_w) & 15)) return -3;
+  if (s->pad_h > 127 || s->pad_w > 127 || (s->kh - 1) * s->dil_h > 255 || (s->kw - 1) * s->dil_w > 255) return -4;
+  const DriverApi& api = driver_api();
+  if (!api.ok) return -5;
+
+  plan->shape = *s;
+  if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
+  const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
+  if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
+  plan->m = static_cast<int>(m_ll);
+  plan->c_blocks = (s->c + kBlockK - 1) / kBlockK;
+  plan->k_iters = s->kh * s->kw * plan->c_blocks;
+  plan->block_n = pick_block_n(s->cout);
+  const bool pointwise = s->kh == 1 && s->kw == 1 && s->stride_h == 1 && s->stride_w == 1 && s->pad_h == 0 &&
+                         s->pad_w == 0;
+  plan->im2col = pointwise ? 0 : 1;
+
+  CUtensorMap* ma = reinterpret_cast<CUtensorMap*>(plan->tma_a);
+  CUtensorMap* mb = reinterpret_cast<CUtensorMap*>(plan->tma_b);
+  CUresult r;
+  if (pointwise) {
+    // Plain row-major matrix [m, c] with row pitch c_stride.
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(s->c), static_cast<cuuint64_t>(plan->m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(s->c_stride) * 4};
+    const cuuint32_t box[2] = {kBlockK, kBlockM};
+    const cuuint32_t estr[2] = {1, 1};
+    r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(in), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(s->c), static_cast<cuuint64_t>(s->w),
+                                static_cast<cuuint64_t>(s->h), static_cast<cuuint64_t>(s->n)};
+    const cuuint64_t pix = static_cast<cuuint64_t>(s->c_stride) * 4;
+    const cuuint64_t strides[3] = {pix, pix * s->w, pix * s->w * s->h};
+    // Window of base pixels (top-left filter corners): starts at -pad and ends
+    // where the last tap still lies inside the padded image.
+    const int lower[2] = {-s->pad_w, -s->pad_h};
+    const int upper[2] = {s->pad_w - (s->kw - 1) * s->dil_w, s->pad_h - (s->kh - 1) * s->dil_h};
+    const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(s->stride_w), static_cast<cuuint32_t>(s->stride_h), 1};
+    r = api.im2col(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(in), dims, strides, lower, upper,
+                   kBlockK, kBlockM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    // Drivers up to CUDA 13.1 encode a flag in im2col descriptors of tensors
+    // smaller than 128 KiB that makes the load misbehave; NVIDIA's CUTLASS
+    // clears it the same way (cute/atom/copy_traits_sm90_im2col.hpp).
+    if (r == CUDA_SUCCESS && api.driver_version <= 13010) {
+      const unsigned long long bytes = static_cast<unsigned long long>(pix) * s->w * s->h * s->n;
+      if (bytes < 131072ull) reinterpret_cast<uint64_t*>(ma)[1] &= ~(1ull << 21);
+    }
+  }
+  if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
+  {
+    const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kBlockK;
+    const cuuint64_t dims[2] = {kp, static_cast<cuuint64_t>(s->cout)};
+    const cuuint64_t strides[1] = {kp * 4};
+    const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(plan->block_n)};
+    const cuuint32_t estr[2] = {1, 1};
+    r = api.tiled(mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(packed_w), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -200 - static_cast<int>(r);
+  }
+  return 0;
+}
+
+extern "C" int mcb200_conv_tc_launch(const mcb200_conv_plan* plan, float* out, int out_ld, const mcb200_epilogue* ep,
+                                     int* status, void* stream) {
+  if (!plan || !out || out_ld < plan->shape.cout) return -1;
+  ConvTcArgs a;
+  a.out = out;
+  a.out_ld = out_ld;
+  a.m = plan->m;
+  a.cout = plan->shape.cout;
+  a.k_iters = plan->k_iters;
+  a.c_blocks = plan->c_blocks;
+  a.kw = plan->shape.kw;
+  a.ho = plan->shape.ho;
+  a.wo = plan->shape.wo;
+  a.stride_h = plan->shape.stride_h;
+  a.stride_w = plan->shape.stride_w;
+  a.pad_h = plan->shape.pad_h;
+  a.pad_w = plan->shape.pad_w;
+  a.dil_h = plan->shape.dil_h;
+  a.dil_w = plan->shape.dil_w;
+  if (ep) {
+    a.ep = *ep;
+  } else {
+    a.ep = mcb200_epilogue();
+    a.ep.residual_coeff = 1.f;
+  }
+  if (a.ep.act == 2 && !a.ep.prelu) return -2;
+  a.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  const bool im = plan->im2col != 0;
+  switch (plan->block_n) {
+    case 64: e = im ? launch_variant<64, true>(plan, a, st) : launch_variant<64, false>(plan, a, st); break;
+    case 128: e = im ? launch_variant<128, true>(plan, a, st) : launch_variant<128, false>(plan, a, st); break;
+    case 256: e = im ? launch_variant<256, true>(plan, a, st) : launch_variant<256, false>(plan, a, st); break;
+    default: return -3;
+  }
+  return static_cast<int>(e);
+}

@@ -1,0 +1,152 @@
+"""Parity of the tensor-core convolution kernel, called through the kernel-level
+C ABI (include/mcb200_kernels.h), against an fp32 reference of the same op.
+
+Tolerance: TF32 operands (10-bit mantissa) with fp32 accumulation; elementwise
+|a-b| <= 2e-2 + 1e-2*|b| as the engine's contract states, and the error
+normalised by the output's largest magnitude must stay below 2e-3.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+
+
+class ConvShape(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in
+                ("n", "h", "w", "c", "c_stride", "cout", "kh", "kw", "stride_h", "stride_w",
+                 "pad_h", "pad_w", "dil_h", "dil_w", "group", "ho", "wo")]
+
+
+class Epilogue(ctypes.Structure):
+    _fields_ = [("scale", ctypes.c_void_p), ("shift", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+                ("residual_ld", ctypes.c_int), ("residual_coeff", ctypes.c_float), ("act", ctypes.c_int),
+                ("slope", ctypes.c_float), ("prelu", ctypes.c_void_p), ("prelu_shared", ctypes.c_int),
+                ("round_tf32", ctypes.c_int)]
+
+
+class ConvPlan(ctypes.Structure):
+    _fields_ = [("tma_a", ctypes.c_uint64 * 16), ("tma_b", ctypes.c_uint64 * 16), ("shape", ConvShape),
+                ("m", ctypes.c_int), ("k_iters", ctypes.c_int), ("c_blocks", ctypes.c_int),
+                ("block_n", ctypes.c_int), ("im2col", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
+
+
+def aligned_plan():
+    raw = ctypes.create_string_buffer(ctypes.sizeof(ConvPlan) + 64)
+    addr = (ctypes.addressof(raw) + 63) & ~63
+    plan = ConvPlan.from_address(addr)
+    plan._keep = raw
+    return plan
+
+
+def run_conv(lib, x_nchw, w, *, stride=1, pad=0, dil=1, c_stride=None, scale=None, shift=None,
+             residual=None, res_coeff=1.0, act=0, slope=0.0, prelu=None):
+    L = lib
+    L.mcb200_conv_packed_weight_count.restype = ctypes.c_size_t
+    n, c, h, wd = x_nchw.shape
+    cout, _, kh, kw = w.shape
+    cs = c_stride or c
+    x_nhwc = torch.zeros((n, h, wd, cs), device="cuda", dtype=torch.float32)
+    x_nhwc[..., :c] = x_nchw.permute(0, 2, 3, 1)
+    s = ConvShape(n, h, wd, c, cs, cout, kh, kw, stride, stride, pad, pad, dil, dil, 1, 0, 0)
+    assert L.mcb200_conv_out_shape(ctypes.byref(s)) == 0
+    packed = torch.empty(L.mcb200_conv_packed_weight_count(ctypes.byref(s)), device="cuda", dtype=torch.float32)
+    wdev = w.contiguous().cuda()
+    assert L.mcb200_conv_pack_weights(ctypes.byref(s), ctypes.c_void_p(wdev.data_ptr()),
+                                      ctypes.c_void_p(packed.data_ptr()), None) == 0
+    plan = aligned_plan()
+    rc = L.mcb200_conv_tc_plan(ctypes.byref(s), ctypes.c_void_p(x_nhwc.data_ptr()),
+                               ctypes.c_void_p(packed.data_ptr()), ctypes.byref(plan))
+    assert rc == 0, rc
+    out = torch.full((n, s.ho, s.wo, cout), float("nan"), device="cuda", dtype=torch.float32)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    ep = Epilogue()
+    ep.residual_coeff = res_coeff
+    keep = []
+    for name, t in (("scale", scale), ("shift", shift), ("prelu", prelu)):
+        if t is not None:
+            d = t.contiguous().cuda()
+            keep.append(d)
+            setattr(ep, name, d.data_ptr())
+    if residual is not None:
+        r = residual.permute(0, 2, 3, 1).contiguous().cuda()
+        keep.append(r)
+        ep.residual = r.data_ptr()
+        ep.residual_ld = cout
+    ep.act = act
+    ep.slope = slope
+    rc = L.mcb200_conv_tc_launch(ctypes.byref(plan), ctypes.c_void_p(out.data_ptr()), cout, ctypes.byref(ep),
+                                 ctypes.c_void_p(status.data_ptr()), None)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "kernel reported a timed-out barrier wait"
+    return out.permute(0, 3, 1, 2).contiguous(), plan
+
+
+def reference(x, w, *, stride, pad, dil, scale, shift, residual, res_coeff, act, slope, prelu):
+    y = torch.nn.functional.conv2d(x.double(), w.double(), None, stride, pad, dil)
+    if scale is not None:
+        y = y * scale.double().view(1, -1, 1, 1)
+    if shift is not None:
+        y = y + shift.double().view(1, -1, 1, 1)
+    if residual is not None:
+        y = y + res_coeff * residual.double()
+    if act == 1:
+        y = torch.where(y > 0, y, y * slope)
+    elif act == 2:
+        y = torch.where(y > 0, y, y * prelu.double().view(1, -1, 1, 1))
+    return y.float()
+
+
+CASES = [
+    # name, N, C, H, W, Cout, k, stride, pad, dil, c_stride
+    ("pointwise_gemm", 1, 64, 25, 40, 64, 1, 1, 0, 1, None),
+    ("cfg1_3x3", 2, 64, 56, 56, 64, 3, 1, 1, 1, None),
+    ("pointwise_wide", 2, 256, 14, 14, 1000, 1, 1, 0, 1, None),
+    ("3x3_stride2", 3, 128, 28, 28, 128, 3, 2, 1, 1, None),
+    ("1x1_stride2", 2, 256, 56, 56, 512, 1, 2, 0, 1, None),
+    ("7x7_stride2_rgb", 2, 3, 224, 224, 64, 7, 2, 3, 1, 4),
+    ("3x3_dilated6", 1, 512, 19, 19, 1024, 3, 1, 6, 6, None),
+    ("odd_sizes", 3, 20, 13, 17, 24, 3, 1, 1, 1, None),
+    ("tiny_1x1x1", 1, 4, 1, 1, 8, 1, 1, 0, 1, None),
+    ("5x5_pad2", 2, 32, 9, 11, 96, 5, 1, 2, 1, None),
+    ("inner_product", 16, 2048, 1, 1, 1000, 1, 1, 0, 1, None),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_conv_tc_matches_fp32(kernels, case):
+    name, n, c, h, w, cout, k, stride, pad, dil, cs = case
+    g = torch.Generator().manual_seed(1234)
+    x = torch.randn((n, c, h, w), generator=g)
+    wt = torch.randn((cout, c, k, k), generator=g) * (2.0 / (c * k * k)) ** 0.5
+    got, plan = run_conv(kernels, x.cuda(), wt, stride=stride, pad=pad, dil=dil, c_stride=cs)
+    want = reference(x, wt, stride=stride, pad=pad, dil=dil, scale=None, shift=None, residual=None,
+                     res_coeff=1.0, act=0, slope=0.0, prelu=None)
+    got = got.cpu()
+    assert got.shape == want.shape
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    assert (err <= 2e-2 + 1e-2 * want.abs()).all(), float(err.max())
+    assert float(err.max() / want.abs().max()) < 2e-3
+
+
+def test_conv_tc_fused_tail(kernels):
+    g = torch.Generator().manual_seed(7)
+    n, c, h, w, cout = 2, 64, 20, 20, 200
+    x = torch.randn((n, c, h, w), generator=g)
+    wt = torch.randn((cout, c, 3, 3), generator=g) * 0.05
+    scale = torch.rand(cout, generator=g) + 0.5
+    shift = torch.randn(cout, generator=g)
+    res = torch.randn((n, cout, h, w), generator=g)
+    prelu = torch.rand(cout, generator=g) * 0.3
+    for act, slope in ((0, 0.0), (1, 0.0), (1, 0.1), (2, 0.0)):
+        kw = dict(stride=1, pad=1, dil=1, scale=scale, shift=shift, residual=res, res_coeff=0.75, act=act,
+                  slope=slope, prelu=prelu if act == 2 else None)
+        got, _ = run_conv(kernels, x.cuda(), wt, **kw)
+        want = reference(x, wt, **kw)
+        err = (got.cpu() - want).abs()
+        assert (err <= 2e-2 + 1e-2 * want.abs()).all(), (act, slope, float(err.max()))
