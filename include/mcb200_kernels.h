@@ -103,6 +103,69 @@ int mcb200_conv_tc_launch(const mcb200_conv_plan* plan, float* out, int out_ld,
 int mcb200_conv_direct(const mcb200_conv_shape* s, const float* in, const float* w_oihw, float* out,
                        int out_ld, const mcb200_epilogue* ep, void* stream);
 
+/* Depthwise convolution (group == c == cout), channels-last, four channels per
+ * thread; weights re-laid as [kh*kw][c] by mcb200_dw_pack_weights.  HBM-bound.
+ * Replaces ConvolutionDepthwiseLayer::Forward_cpu (src/layers/conv_dw_layer.cpp:104-152)
+ * and the per-group M=1 GEMMs of the generic path (base_conv_layer.cpp:265-270). */
+int mcb200_dw_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed, void* stream);
+int mcb200_conv_depthwise(const mcb200_conv_shape* s, const float* in, const float* packed_w, float* out,
+                          const mcb200_epilogue* ep, void* stream);
+
+/* ------------------------------------------------------------------ layout */
+/* (N,C,H,W) -> (N,H,W,c_stride) with channels c..c_stride-1 zero-filled, and back. */
+int mcb200_nchw_to_nhwc(const float* src, float* dst, int n, int c, int h, int w, int c_stride, void* stream);
+int mcb200_nhwc_to_nchw(const float* src, float* dst, int n, int c, int h, int w, int c_stride, void* stream);
+
+/* ------------------------------------------------------------------ elementwise */
+/* y[i] = act(x[i] * scale[ch] + shift[ch]),  ch = (i / inner) % channels.
+ * inner = H*W for (N,C,H,W) data, 1 for channels-last data.  scale / shift may
+ * be NULL.  `ep` supplies act / slope / prelu only.  Stand-alone form of
+ * BatchNorm, Scale, Bias, ReLU and PReLU (src/layers/batch_norm_layer.cpp:72-136,
+ * scale_layer.cpp:96-113, bias_layer.cpp:68-83, relu_layer.cpp:12-29,
+ * prelu_layer.cpp:52-84) for when they cannot be fused into a producer.      */
+int mcb200_channel_affine_act(const float* x, float* y, long long count, int channels, int inner,
+                              const float* scale, const float* shift, const mcb200_epilogue* ep, void* stream);
+
+#define MCB200_ELTWISE_PROD 0
+#define MCB200_ELTWISE_SUM 1
+#define MCB200_ELTWISE_MAX 2
+#define MCB200_MAX_ELTWISE_INPUTS 8
+/* out = op over the inputs (SUM uses coeffs), then the optional activation.
+ * EltwiseLayer::Forward_cpu, src/layers/eltwise_layer.cpp:37-78.             */
+int mcb200_eltwise(int op, int num_inputs, const float* const* inputs, const float* coeffs, float* out,
+                   long long count, int act, float slope, void* stream);
+
+/* ------------------------------------------------------------------ pooling */
+#define MCB200_POOL_MAX 0
+#define MCB200_POOL_AVE 1
+/* Output extent with Caffe's ceil rule and last-window clip
+ * (src/layers/pooling_layer.cpp:92-107).                                     */
+void mcb200_pool_out_shape(int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int* ho, int* wo);
+/* Channels-last pooling.  MAX starts from -FLT_MAX over the window clipped to
+ * the image; AVE sums the clipped window and divides by the window area clipped
+ * to the padded image (src/layers/pooling_layer.cpp:124-181).                */
+int mcb200_pool_nhwc(const float* in, float* out, int n, int h, int w, int c, int kh, int kw, int sh, int sw,
+                     int ph, int pw, int ho, int wo, int method, void* stream);
+
+/* ------------------------------------------------------------------ softmax */
+/* Softmax over `channels` of data viewed as [outer, channels, inner]
+ * (src/layers/softmax_layer.cpp:29-63): subtract the max, exp, divide by the sum. */
+int mcb200_softmax(const float* in, float* out, int outer, int channels, int inner, void* stream);
+
+/* ------------------------------------------------------------------ copies */
+/* rows x cols floats from a pitched source to a pitched destination (pitches
+ * in floats).  Concat / Slice style block copies (src/layers/concat_layer.cpp:53-70). */
+int mcb200_copy_2d(const float* src, long long src_pitch, float* dst, long long dst_pitch, long long rows,
+                   long long cols, void* stream);
+/* out[permuted index] = in[index] for up to 6 axes; order[i] is the input axis
+ * that becomes output axis i (src/layers/permute_layer.cpp:8-22).           */
+int mcb200_permute(const float* in, float* out, int num_axes, const int* in_shape, const int* order, void* stream);
+/* Per pixel L2 normalisation across channels of channels-last data, times a
+ * per-channel (or single) scale: y = x / sqrt(sum_c x^2 + eps) * scale[c]
+ * (src/layers/normalize_layer.cpp:86-135 with across_spatial = false).       */
+int mcb200_normalize_nhwc(const float* in, float* out, long long pixels, int channels, const float* scale,
+                          int scale_shared, float eps, void* stream);
+
 /* Number of kernels launched by this library on the calling thread since the
  * last reset (bench.py reports it as gpu_launches).                          */
 long long mcb200_launch_count(void);

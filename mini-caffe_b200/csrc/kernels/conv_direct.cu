@@ -1,0 +1,174 @@
+// Convolutions that do not go to the tensor cores.
+//
+//  * mcb200_conv_depthwise: group == channels (MobileNet).  2.25 FLOP per byte:
+//    HBM-bound, so the kernel is organised around memory traffic -- channels
+//    last, one thread per output pixel and four channels, every input and
+//    weight access a 128-bit load, fused scale/shift/activation on the way out.
+//  * mcb200_conv_direct: any group count, any channel count; one thread per
+//    output element.  Slow but shape-agnostic; the fallback for layers the
+//    tensor-core path rejects (e.g. grouped convolutions, channel counts that
+//    are not a multiple of four).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/mcb200_kernels.h"
+#include "launch_count.h"
+
+namespace mcb200 {
+namespace {
+
+constexpr int kSMs = 148;
+
+inline int grid_for(long long items, int threads) {
+  long long blocks = (items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(kSMs) * 16;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : static_cast<int>(blocks);
+}
+
+__device__ __forceinline__ float tail(float v, int c, const mcb200_epilogue& ep, const float* res) {
+  if (ep.scale) v *= __ldg(ep.scale + c);
+  if (ep.shift) v += __ldg(ep.shift + c);
+  if (res) v += ep.residual_coeff * res[c];
+  if (ep.act != 0 && v <= 0.f) {
+    const float slope = ep.act == 2 ? __ldg(ep.prelu + (ep.prelu_shared ? 0 : c)) : ep.slope;
+    v *= slope;
+  }
+  return v;
+}
+
+__global__ void depthwise_vec4_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
+                                      mcb200_conv_shape s, mcb200_epilogue ep) {
+  const int cg = s.c / 4;
+  const long long total = static_cast<long long>(s.n) * s.ho * s.wo * cg;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(i % cg);
+    long long t = i / cg;
+    const int ox = static_cast<int>(t % s.wo);
+    t /= s.wo;
+    const int oy = static_cast<int>(t % s.ho);
+    const int n = static_cast<int>(t / s.ho);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < s.kh; ++r) {
+      const int y = oy * s.stride_h - s.pad_h + r * s.dil_h;
+      if (y < 0 || y >= s.h) continue;
+      for (int q = 0; q < s.kw; ++q) {
+        const int x = ox * s.stride_w - s.pad_w + q * s.dil_w;
+        if (x < 0 || x >= s.w) continue;
+        const float4 v =
+            *reinterpret_cast<const float4*>(in + ((static_cast<size_t>(n) * s.h + y) * s.w + x) * s.c_stride + g * 4);
+        const float4 k = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(r * s.kw + q) * s.c + g * 4));
+        acc.x += v.x * k.x;
+        acc.y += v.y * k.y;
+        acc.z += v.z * k.z;
+        acc.w += v.w * k.w;
+      }
+    }
+    const size_t o = ((static_cast<size_t>(n) * s.ho + oy) * s.wo + ox) * s.c + g * 4;
+    const float* res = ep.residual ? ep.residual + ((static_cast<size_t>(n) * s.ho + oy) * s.wo + ox) * ep.residual_ld
+                                   : nullptr;
+    const int c0 = g * 4;
+    float4 r4;
+    r4.x = tail(acc.x, c0, ep, res);
+    r4.y = tail(acc.y, c0 + 1, ep, res);
+    r4.z = tail(acc.z, c0 + 2, ep, res);
+    r4.w = tail(acc.w, c0 + 3, ep, res);
+    *reinterpret_cast<float4*>(out + o) = r4;
+  }
+}
+
+__global__ void dw_pack_kernel(const float* __restrict__ w, float* __restrict__ packed, int c, int taps) {
+  const int total = c * taps;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int ch = i % c;
+    const int tap = i / c;
+    packed[i] = w[static_cast<size_t>(ch) * taps + tap];
+  }
+}
+
+__global__ void conv_direct_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
+                                   int out_ld, mcb200_conv_shape s, mcb200_epilogue ep) {
+  const int cin_g = s.c / s.group;
+  const int cout_g = s.cout / s.group;
+  const long long total = static_cast<long long>(s.n) * s.ho * s.wo * s.cout;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int co = static_cast<int>(i % s.cout);
+    long long t = i / s.cout;
+    const long long pixel = t;
+    const int ox = static_cast<int>(t % s.wo);
+    t /= s.wo;
+    const int oy = static_cast<int>(t % s.ho);
+    const int n = static_cast<int>(t / s.ho);
+    const int g = co / cout_g;
+    const float* wk = w + static_cast<size_t>(co) * cin_g * s.kh * s.kw;
+    float acc = 0.f;
+    for (int r = 0; r < s.kh; ++r) {
+      const int y = oy * s.stride_h - s.pad_h + r * s.dil_h;
+      if (y < 0 || y >= s.h) continue;
+      for (int q = 0; q < s.kw; ++q) {
+        const int x = ox * s.stride_w - s.pad_w + q * s.dil_w;
+        if (x < 0 || x >= s.w) continue;
+        const float* px = in + ((static_cast<size_t>(n) * s.h + y) * s.w + x) * s.c_stride + g * cin_g;
+        for (int ci = 0; ci < cin_g; ++ci) acc += px[ci] * __ldg(wk + (static_cast<size_t>(ci) * s.kh + r) * s.kw + q);
+      }
+    }
+    const float* res = ep.residual ? ep.residual + pixel * ep.residual_ld : nullptr;
+    out[pixel * out_ld + co] = tail(acc, co, ep, res);
+  }
+}
+
+mcb200_epilogue default_epilogue() {
+  mcb200_epilogue ep = mcb200_epilogue();
+  ep.residual_coeff = 1.f;
+  return ep;
+}
+
+}  // namespace
+}  // namespace mcb200
+
+using namespace mcb200;
+
+extern "C" int mcb200_dw_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed, void* stream) {
+  if (!s || !w_oihw || !packed || s->group != s->c || s->cout != s->c) return -1;
+  const int taps = s->kh * s->kw;
+  dw_pack_kernel<<<grid_for(static_cast<long long>(s->c) * taps, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      w_oihw, packed, s->c, taps);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_conv_depthwise(const mcb200_conv_shape* s, const float* in, const float* packed_w, float* out,
+                                     const mcb200_epilogue* ep, void* stream) {
+  if (!s || !in || !packed_w || !out) return -1;
+  if (s->group != s->c || s->cout != s->c || (s->c & 3) || (s->c_stride & 3)) return -2;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(packed_w)) & 15)
+    return -3;
+  mcb200_conv_shape shape = *s;
+  if (mcb200_conv_out_shape(&shape) != 0) return -4;
+  const mcb200_epilogue e = ep ? *ep : default_epilogue();
+  if (e.act == 2 && !e.prelu) return -5;
+  const long long items = static_cast<long long>(shape.n) * shape.ho * shape.wo * (shape.c / 4);
+  if (items == 0) return 0;
+  depthwise_vec4_kernel<<<grid_for(items, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, packed_w, out, shape,
+                                                                                            e);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_conv_direct(const mcb200_conv_shape* s, const float* in, const float* w_oihw, float* out,
+                                  int out_ld, const mcb200_epilogue* ep, void* stream) {
+  if (!s || !in || !w_oihw || !out || s->group < 1) return -1;
+  if (s->c % s->group != 0 || s->cout % s->group != 0 || out_ld < s->cout || s->c_stride < s->c) return -2;
+  mcb200_conv_shape shape = *s;
+  if (mcb200_conv_out_shape(&shape) != 0) return -4;
+  const mcb200_epilogue e = ep ? *ep : default_epilogue();
+  if (e.act == 2 && !e.prelu) return -5;
+  const long long items = static_cast<long long>(shape.n) * shape.ho * shape.wo * shape.cout;
+  if (items == 0) return 0;
+  conv_direct_kernel<<<grid_for(items, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, w_oihw, out, out_ld,
+                                                                                         shape, e);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}

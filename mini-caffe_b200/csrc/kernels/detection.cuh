@@ -1,0 +1,96 @@
+// Device building blocks shared by the detection kernels (RPN Proposal, SSD
+// DetectionOutput): order-preserving float keys, a block-wide radix select of
+// the K smallest 64-bit keys, a block-wide bitonic sort in shared memory, and
+// IEEE arithmetic helpers that the compiler may not contract into fused
+// multiply-adds (the CPU code being matched is compiled without FMA, and the
+// kept-box sets have to agree bit for bit).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mcb200 {
+namespace det {
+
+__device__ __forceinline__ float fadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float fsub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float fmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float fdiv(float a, float b) { return __fdiv_rn(a, b); }
+
+// Unsigned key that sorts ascending exactly when the float sorts DEScending;
+// -0.0 and +0.0 get the same key (they compare equal on the CPU).
+__device__ __forceinline__ uint32_t descending_key(float score) {
+  uint32_t bits = __float_as_uint(score);
+  if ((bits << 1) == 0u) bits = 0u;                                    // -0.0 -> +0.0
+  const uint32_t ascending = bits ^ ((bits >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+  return ~ascending;
+}
+
+// 64-bit sort key: descending score first, ascending index second (unique).
+__device__ __forceinline__ unsigned long long make_key(float score, uint32_t index) {
+  return (static_cast<unsigned long long>(descending_key(score)) << 32) | index;
+}
+
+constexpr unsigned long long kPadKey = 0xFFFFFFFFFFFFFFFFull;
+
+// Finds the k-th smallest (1-based) of n distinct keys with an MSB-first radix
+// walk, 8 bits per pass.  Whole block; `hist` is 256 ints of shared memory,
+// `bcast` two unsigned long longs.  `fetch(i)` returns key i.
+template <typename Fetch>
+__device__ unsigned long long block_kth_smallest(Fetch fetch, int n, int k, int* hist, unsigned long long* bcast) {
+  unsigned long long prefix = 0, mask = 0;
+  int remaining = k;
+  for (int pass = 7; pass >= 0; --pass) {
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0;
+    __syncthreads();
+    const int shift = pass * 8;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const unsigned long long key = fetch(i);
+      if ((key & mask) == prefix) atomicAdd(&hist[static_cast<int>((key >> shift) & 0xFFull)], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int cum = 0, bin = 0;
+      for (; bin < 255; ++bin) {
+        if (cum + hist[bin] >= remaining) break;
+        cum += hist[bin];
+      }
+      bcast[0] = prefix | (static_cast<unsigned long long>(bin) << shift);
+      bcast[1] = static_cast<unsigned long long>(remaining - cum);
+    }
+    __syncthreads();
+    prefix = bcast[0];
+    remaining = static_cast<int>(bcast[1]);
+    mask |= 0xFFull << shift;
+    __syncthreads();
+  }
+  return prefix;
+}
+
+// Ascending bitonic sort of `count` (a power of two) keys in shared memory.
+__device__ inline void block_bitonic_sort(unsigned long long* keys, int count) {
+  for (int size = 2; size <= count; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < (count >> 1); t += blockDim.x) {
+        const int lo = ((t / stride) * (stride << 1)) + (t % stride);
+        const int hi = lo + stride;
+        const bool ascending = ((lo & size) == 0);
+        const unsigned long long a = keys[lo], b = keys[hi];
+        if ((a > b) == ascending) {
+          keys[lo] = b;
+          keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+__host__ __device__ inline int next_pow2(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+}  // namespace det
+}  // namespace mcb200

@@ -1,0 +1,365 @@
+// RPN ProposalLayer on the device, batched over images:
+//   1. decode      anchor + deltas -> clipped box, min-size filter, sort key
+//   2. top-k sort  per image: radix-select the pre_nms_topn best keys, bitonic
+//                  sort them in shared memory, gather boxes in score order
+//   3. nms mask    64 x 64 IoU tiles of the upper triangle, one 64-bit word per
+//                  (row, column block), built with warp ballots
+//   4. nms scan    per image: greedy pass over the mask, 64 boxes at a time,
+//                  stops at post_nms_topn; writes rois (+ scores) and the count
+// The host only reads the per-image counts back.
+//
+// Every float operation that decides which boxes are kept is done with the
+// rounding of the CPU code it replaces (mini-caffe src/layers/proposal_layer.cpp:
+// TransformBBox :14-53, GenerateProposalsCPU :114-148, SortBBox :88-111,
+// NonMaximumSuppressionCPU :150-185, RetrieveRoisCPU :187-203): separate
+// multiply and add (no FMA), exp() evaluated in double and the product rounded
+// to float once, IEEE division.  Boxes with equal scores are ordered by
+// proposal index (the CPU quicksort leaves that order unspecified).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/mcb200_kernels.h"
+#include "detection.cuh"
+#include "launch_count.h"
+
+namespace mcb200 {
+namespace {
+
+using namespace det;
+
+struct Workspace {
+  float4* boxes;                 // [batch][n]        decoded boxes, proposal order
+  float* scores;                 // [batch][n]
+  unsigned long long* keys;      // [batch][n]
+  float4* sorted_boxes;          // [batch][k]        score order
+  float* sorted_scores;          // [batch][k]
+  unsigned long long* mask;      // [batch][k][col_blocks]
+  int n, k, col_blocks;
+};
+
+size_t align_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+size_t carve(const mcb200_proposal_params& p, int batch, char* base, Workspace* ws) {
+  const int n = p.num_anchors * p.height * p.width;
+  const int k = n < p.pre_nms_topn ? n : p.pre_nms_topn;
+  const int cb = (k + 63) / 64;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char* ptr = base ? base + off : nullptr;
+    off += align_up(bytes);
+    return ptr;
+  };
+  Workspace w;
+  w.n = n;
+  w.k = k;
+  w.col_blocks = cb;
+  w.boxes = reinterpret_cast<float4*>(take(sizeof(float4) * n * static_cast<size_t>(batch)));
+  w.scores = reinterpret_cast<float*>(take(sizeof(float) * n * static_cast<size_t>(batch)));
+  w.keys = reinterpret_cast<unsigned long long*>(take(8 * static_cast<size_t>(n) * batch));
+  w.sorted_boxes = reinterpret_cast<float4*>(take(sizeof(float4) * k * static_cast<size_t>(batch)));
+  w.sorted_scores = reinterpret_cast<float*>(take(sizeof(float) * k * static_cast<size_t>(batch)));
+  w.mask = reinterpret_cast<unsigned long long*>(take(8 * static_cast<size_t>(k) * cb * batch));
+  if (ws) *ws = w;
+  return off;
+}
+
+// ---------------------------------------------------------------- 1. decode
+
+__global__ void proposal_decode_kernel(const float* __restrict__ score_maps, const float* __restrict__ delta_maps,
+                                       const float* __restrict__ im_info, const float* __restrict__ anchors,
+                                       mcb200_proposal_params p, Workspace ws) {
+  const int image = blockIdx.y;
+  const int hw = p.height * p.width;
+  const int n = ws.n;
+  // Foreground scores are the second half of the 2A score channels.
+  const float* score = score_maps + static_cast<size_t>(image) * 2 * p.num_anchors * hw + static_cast<size_t>(n);
+  const float* delta = delta_maps + static_cast<size_t>(image) * 4 * p.num_anchors * hw;
+  const float img_h = im_info[image * 3 + 0];
+  const float img_w = im_info[image * 3 + 1];
+  const float min_size = fmul(static_cast<float>(p.min_size), im_info[image * 3 + 2]);
+  // Threads run over (anchor, y, x) with x fastest, so the map reads coalesce.
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n; t += gridDim.x * blockDim.x) {
+    const int k = t / hw;
+    const int pos = t - k * hw;
+    const int y = pos / p.width;
+    const int x = pos - y * p.width;
+    const float fx = static_cast<float>(x * p.feat_stride);
+    const float fy = static_cast<float>(y * p.feat_stride);
+    float b0 = fadd(fx, anchors[k * 4 + 0]);
+    float b1 = fadd(fy, anchors[k * 4 + 1]);
+    float b2 = fadd(fx, anchors[k * 4 + 2]);
+    float b3 = fadd(fy, anchors[k * 4 + 3]);
+    const float dx = delta[(k * 4 + 0) * hw + pos];
+    const float dy = delta[(k * 4 + 1) * hw + pos];
+    const float dlw = delta[(k * 4 + 2) * hw + pos];
+    const float dlh = delta[(k * 4 + 3) * hw + pos];
+
+    const float w = fadd(fsub(b2, b0), 1.f);
+    const float h = fadd(fsub(b3, b1), 1.f);
+    const float ctr_x = fadd(b0, fmul(0.5f, w));
+    const float ctr_y = fadd(b1, fmul(0.5f, h));
+    const float pred_ctr_x = fadd(fmul(dx, w), ctr_x);
+    const float pred_ctr_y = fadd(fmul(dy, h), ctr_y);
+    // exp in double, product in double, one rounding to float.
+    const float pred_w = static_cast<float>(__dmul_rn(exp(static_cast<double>(dlw)), static_cast<double>(w)));
+    const float pred_h = static_cast<float>(__dmul_rn(exp(static_cast<double>(dlh)), static_cast<double>(h)));
+    b0 = fsub(pred_ctr_x, fmul(0.5f, pred_w));
+    b1 = fsub(pred_ctr_y, fmul(0.5f, pred_h));
+    b2 = fadd(pred_ctr_x, fmul(0.5f, pred_w));
+    b3 = fadd(pred_ctr_y, fmul(0.5f, pred_h));
+    const float max_x = fsub(img_w, 1.f);
+    const float max_y = fsub(img_h, 1.f);
+    b0 = fmaxf(0.f, fminf(b0, max_x));
+    b1 = fmaxf(0.f, fminf(b1, max_y));
+    b2 = fmaxf(0.f, fminf(b2, max_x));
+    b3 = fmaxf(0.f, fminf(b3, max_y));
+    const float box_w = fadd(fsub(b2, b0), 1.f);
+    const float box_h = fadd(fsub(b3, b1), 1.f);
+    const int valid = (box_w >= min_size) && (box_h >= min_size);
+    const float s = fmul(static_cast<float>(valid), score[k * hw + pos]);
+
+    const int index = pos * p.num_anchors + k;   // proposal order: (y, x, anchor)
+    const size_t o = static_cast<size_t>(image) * n + index;
+    ws.boxes[o] = make_float4(b0, b1, b2, b3);
+    ws.scores[o] = s;
+    ws.keys[o] = make_key(s, static_cast<uint32_t>(index));
+  }
+}
+
+// ---------------------------------------------------------------- 2. top-k + sort
+
+__global__ void __launch_bounds__(1024, 1)
+proposal_topk_sort_kernel(Workspace ws, int padded) {
+  extern __shared__ unsigned long long sorted[];   // `padded` keys
+  __shared__ int hist[256];
+  __shared__ unsigned long long bcast[2];
+  __shared__ int fill;
+  const int image = blockIdx.x;
+  const unsigned long long* keys = ws.keys + static_cast<size_t>(image) * ws.n;
+  const int n = ws.n, k = ws.k;
+
+  unsigned long long threshold = kPadKey;
+  if (k < n) {
+    threshold = block_kth_smallest([&](int i) { return keys[i]; }, n, k, hist, bcast);
+  }
+  if (threadIdx.x == 0) fill = 0;
+  for (int i = threadIdx.x; i < padded; i += blockDim.x) sorted[i] = kPadKey;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const unsigned long long key = keys[i];
+    if (key <= threshold) {
+      const int slot = atomicAdd(&fill, 1);
+      if (slot < padded) sorted[slot] = key;
+    }
+  }
+  __syncthreads();
+  block_bitonic_sort(sorted, padded);
+  const float4* boxes = ws.boxes + static_cast<size_t>(image) * n;
+  const float* scores = ws.scores + static_cast<size_t>(image) * n;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const uint32_t index = static_cast<uint32_t>(sorted[i] & 0xFFFFFFFFull);
+    ws.sorted_boxes[static_cast<size_t>(image) * k + i] = boxes[index];
+    ws.sorted_scores[static_cast<size_t>(image) * k + i] = scores[index];
+  }
+}
+
+// ---------------------------------------------------------------- 3. NMS mask
+
+// IoU with the "+1 pixel" convention; areas[i] + areas[j] - inter, IEEE division.
+__device__ __forceinline__ bool suppresses(const float4& a, float area_a, const float4& b, float area_b,
+                                           float threshold) {
+  const float x1 = fmaxf(a.x, b.x);
+  const float y1 = fmaxf(a.y, b.y);
+  const float x2 = fminf(a.z, b.z);
+  const float y2 = fminf(a.w, b.w);
+  const float w = fmaxf(0.f, fadd(fsub(x2, x1), 1.f));
+  const float h = fmaxf(0.f, fadd(fsub(y2, y1), 1.f));
+  const float inter = fmul(w, h);
+  const float ov = fdiv(inter, fsub(fadd(area_a, area_b), inter));
+  return ov > threshold;
+}
+
+__device__ __forceinline__ float box_area(const float4& b) {
+  return fmul(fadd(fsub(b.z, b.x), 1.f), fadd(fsub(b.w, b.y), 1.f));
+}
+
+// grid: (column block, row block, image); 256 threads = 8 warps, 8 rows each.
+__global__ void __launch_bounds__(256)
+proposal_nms_mask_kernel(Workspace ws, float threshold) {
+  const int col_block = blockIdx.x, row_block = blockIdx.y, image = blockIdx.z;
+  if (col_block < row_block) return;   // only pairs (i, j) with j > i matter
+  __shared__ float4 row_box[64], col_box[64];
+  __shared__ float row_area[64], col_area[64];
+  const int k = ws.k;
+  const float4* boxes = ws.sorted_boxes + static_cast<size_t>(image) * k;
+  const int t = threadIdx.x;
+  if (t < 64) {
+    const int i = row_block * 64 + t;
+    const float4 b = i < k ? boxes[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    row_box[t] = b;
+    row_area[t] = box_area(b);
+  } else if (t < 128) {
+    const int j = col_block * 64 + (t - 64);
+    const float4 b = j < k ? boxes[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    col_box[t - 64] = b;
+    col_area[t - 64] = box_area(b);
+  }
+  __syncthreads();
+  const int warp = t >> 5, lane = t & 31;
+  for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+    const int i = row_block * 64 + r;
+    if (i >= k) break;
+    unsigned long long word = 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int c = half * 32 + lane;
+      const int j = col_block * 64 + c;
+      const bool hit = (j < k) && (j > i) && suppresses(row_box[r], row_area[r], col_box[c], col_area[c], threshold);
+      const unsigned bits = __ballot_sync(0xffffffffu, hit);
+      word |= static_cast<unsigned long long>(bits) << (half * 32);
+    }
+    if (lane == 0) ws.mask[(static_cast<size_t>(image) * k + i) * ws.col_blocks + col_block] = word;
+  }
+}
+
+// ---------------------------------------------------------------- 4. scan + output
+
+// One block per image.  Boxes are taken 64 at a time: thread 0 resolves the
+// block's own 64 x 64 diagonal word chain in registers, then every thread
+// ORs the kept rows' words of "its" later column block into the removed set.
+__global__ void __launch_bounds__(256)
+proposal_nms_scan_kernel(Workspace ws, int post_nms_topn, float* __restrict__ rois, float* __restrict__ roi_scores,
+                         int* __restrict__ counts) {
+  extern __shared__ unsigned long long removed[];   // col_blocks words
+  __shared__ unsigned long long keep_word;
+  __shared__ int kept_total;
+  __shared__ int stop;
+  const int image = blockIdx.x;
+  const int k = ws.k, cb = ws.col_blocks;
+  const unsigned long long* mask = ws.mask + static_cast<size_t>(image) * k * cb;
+  const float4* boxes = ws.sorted_boxes + static_cast<size_t>(image) * k;
+  const float* scores = ws.sorted_scores + static_cast<size_t>(image) * k;
+  float* out = rois + static_cast<size_t>(image) * post_nms_topn * 5;
+  float* out_scores = roi_scores ? roi_scores + static_cast<size_t>(image) * post_nms_topn : nullptr;
+
+  for (int w = threadIdx.x; w < cb; w += blockDim.x) removed[w] = 0;
+  if (threadIdx.x == 0) {
+    kept_total = 0;
+    stop = 0;
+  }
+  __syncthreads();
+  for (int block = 0; block < cb && !stop; ++block) {
+    if (threadIdx.x == 0) {
+      unsigned long long gone = removed[block];
+      unsigned long long keep = 0;
+      int total = kept_total;
+      const int rows = min(64, k - block * 64);
+      for (int r = 0; r < rows; ++r) {
+        if (!((gone >> r) & 1ull)) {
+          keep |= 1ull << r;
+          const int i = block * 64 + r;
+          const float4 b = boxes[i];
+          out[total * 5 + 0] = static_cast<float>(image);
+          out[total * 5 + 1] = b.x;
+          out[total * 5 + 2] = b.y;
+          out[total * 5 + 3] = b.z;
+          out[total * 5 + 4] = b.w;
+          if (out_scores) out_scores[total] = scores[i];
+          ++total;
+          if (total == post_nms_topn) {
+            stop = 1;
+            break;
+          }
+          gone |= mask[static_cast<size_t>(i) * cb + block];
+        }
+      }
+      keep_word = keep;
+      kept_total = total;
+    }
+    __syncthreads();
+    if (!stop) {
+      const unsigned long long keep = keep_word;
+      for (int w = block + 1 + threadIdx.x; w < cb; w += blockDim.x) {
+        unsigned long long acc = removed[w];
+        unsigned long long bits = keep;
+        while (bits) {
+          const int r = __ffsll(static_cast<long long>(bits)) - 1;
+          bits &= bits - 1;
+          acc |= mask[static_cast<size_t>(block * 64 + r) * cb + w];
+        }
+        removed[w] = acc;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[image] = kept_total;
+}
+
+}  // namespace
+}  // namespace mcb200
+
+using namespace mcb200;
+
+static int validate(const mcb200_proposal_params* p, int batch) {
+  if (!p || batch < 1) return -1;
+  if (p->num_anchors < 1 || p->height < 1 || p->width < 1 || p->feat_stride < 1 || p->pre_nms_topn < 1 ||
+      p->post_nms_topn < 1)
+    return -2;
+  const long long n = static_cast<long long>(p->num_anchors) * p->height * p->width;
+  if (n > (1 << 24)) return -3;
+  const int k = n < p->pre_nms_topn ? static_cast<int>(n) : p->pre_nms_topn;
+  // The sorted keys of one image live in shared memory (8 bytes each).
+  if (det::next_pow2(k) > 16384) return -4;
+  return 0;
+}
+
+extern "C" size_t mcb200_proposal_workspace_bytes(const mcb200_proposal_params* p, int batch) {
+  if (validate(p, batch) != 0) return 0;
+  return carve(*p, batch, nullptr, nullptr);
+}
+
+extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batch, const float* scores,
+                                       const float* deltas, const float* im_info, const float* anchors,
+                                       void* workspace, float* rois, float* roi_scores, int* counts, void* stream) {
+  const int rc = validate(p, batch);
+  if (rc != 0) return rc;
+  if (!scores || !deltas || !im_info || !anchors || !workspace || !rois || !counts) return -5;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return -6;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Workspace ws;
+  carve(*p, batch, static_cast<char*>(workspace), &ws);
+
+  {
+    const int threads = 256;
+    int blocks = (ws.n + threads - 1) / threads;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    proposal_decode_kernel<<<dim3(blocks, batch), threads, 0, st>>>(scores, deltas, im_info, anchors, *p, ws);
+    count_launch();
+  }
+  {
+    const int padded = det::next_pow2(ws.k);
+    const size_t smem = static_cast<size_t>(padded) * 8;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(proposal_topk_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           16384 * 8);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[dev] = true;
+    }
+    proposal_topk_sort_kernel<<<batch, 1024, smem, st>>>(ws, padded);
+    count_launch();
+  }
+  {
+    dim3 grid(ws.col_blocks, ws.col_blocks, batch);
+    proposal_nms_mask_kernel<<<grid, 256, 0, st>>>(ws, p->nms_thresh);
+    count_launch();
+  }
+  {
+    proposal_nms_scan_kernel<<<batch, 256, static_cast<size_t>(ws.col_blocks) * 8, st>>>(ws, p->post_nms_topn, rois,
+                                                                                          roi_scores, counts);
+    count_launch();
+  }
+  return static_cast<int>(cudaGetLastError());
+}

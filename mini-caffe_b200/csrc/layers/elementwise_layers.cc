@@ -1,0 +1,291 @@
+// BatchNorm, Scale, Bias, ReLU, PReLU, Dropout and Eltwise.
+//
+// The first five are "y = act(x * scale[c] + shift[c])" layers.  Inside a net
+// they are normally folded into the convolution or inner product in front of
+// them (see FusedTail); the stand-alone forward here runs one vectorised pass
+// in whichever memory order the bottom currently has.
+#include <cmath>
+
+#include "../filler.h"
+#include "layers.h"
+
+namespace caffe {
+
+// ---------------------------------------------------------------- ChannelwiseLayer
+
+void ChannelwiseLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  if (top[0] != bottom[0]) top[0]->ReshapeLike(*bottom[0]);
+}
+
+void ChannelwiseLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  Context& ctx = Context::Get();
+  const int channels = Channels(bottom[0]);
+  std::vector<double> scale, shift;
+  const bool affine = AsChannelAffine(channels, nullptr, nullptr);
+  if (affine) {
+    const unsigned long long v = 1 + ParamVersion();
+    if (v != built_version_ || channels != built_channels_) {
+      CHECK(AsChannelAffine(channels, &scale, &shift));
+      scale_dev_.Assign(std::vector<float>(scale.begin(), scale.end()));
+      shift_dev_.Assign(std::vector<float>(shift.begin(), shift.end()));
+      built_version_ = v;
+      built_channels_ = channels;
+    }
+  }
+  mcb200_epilogue ep = mcb200_epilogue();
+  ActivationSpec spec;
+  if (AsActivation(&spec)) {
+    ep.act = spec.kind;
+    ep.slope = spec.slope;
+    if (spec.kind == 2) {
+      ep.prelu = spec.slopes->gpu_data();
+      ep.prelu_shared = spec.shared ? 1 : 0;
+    }
+  }
+  const bool nhwc = bottom[0]->device_is_nhwc();
+  const float* x = nhwc ? bottom[0]->gpu_data_nhwc() : bottom[0]->gpu_data();
+  float* y = nhwc ? top[0]->mutable_gpu_data_nhwc() : top[0]->mutable_gpu_data();
+  const int inner = nhwc ? 1 : (bottom[0]->num_axes() > 2 ? bottom[0]->count(2) : 1);
+  if (!affine && ep.act == 0) {
+    if (x != y) {
+      CUDA_CHECK(cudaMemcpyAsync(y, x, sizeof(float) * bottom[0]->count(), cudaMemcpyDeviceToDevice, ctx.stream()));
+    }
+    return;
+  }
+  KERNEL_CHECK(mcb200_channel_affine_act(x, y, bottom[0]->count(), channels, inner, affine ? scale_dev_.get() : nullptr,
+                                         affine ? shift_dev_.get() : nullptr, &ep, ctx.stream_ptr()));
+}
+
+// ---------------------------------------------------------------- BatchNorm
+
+void BatchNormLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const BatchNormParameter& p = layer_param_.batch_norm_param();
+  if (p.has_use_global_stats()) {
+    CHECK(p.use_global_stats()) << "BatchNorm: only inference with stored statistics is implemented";
+  }
+  channels_ = bottom[0]->num_axes() == 1 ? 1 : bottom[0]->shape(1);
+  eps_ = p.eps();
+  if (blobs_.empty()) {
+    blobs_.resize(3);
+    blobs_[0].reset(new Blob(vector<int>(1, channels_)));
+    blobs_[1].reset(new Blob(vector<int>(1, channels_)));
+    blobs_[2].reset(new Blob(vector<int>(1, 1)));
+    for (auto& b : blobs_) {
+      real_t* d = b->mutable_cpu_data();
+      for (int i = 0; i < b->count(); ++i) d[i] = 0;
+    }
+  }
+}
+
+// mean = blobs[0] / f, var = blobs[1] / f with f = blobs[2][0] (f == 0 gives
+// mean = var = 0); y = (x - mean) / sqrt(var + eps)
+// (src/layers/batch_norm_layer.cpp:83-135).  Evaluated in float like there.
+bool BatchNormLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) {
+  if (channels != channels_ || blobs_.size() != 3) return false;
+  if (!scale) return true;
+  const float factor_raw = blobs_[2]->cpu_data()[0];
+  const float factor = factor_raw == 0.f ? 0.f : 1.f / factor_raw;
+  const float* mean = blobs_[0]->cpu_data();
+  const float* var = blobs_[1]->cpu_data();
+  scale->resize(channels);
+  shift->resize(channels);
+  for (int c = 0; c < channels; ++c) {
+    const float m = mean[c] * factor;
+    const float v = var[c] * factor + eps_;
+    const double inv_std = 1.0 / static_cast<double>(std::pow(v, 0.5f));
+    (*scale)[c] = inv_std;
+    (*shift)[c] = -static_cast<double>(m) * inv_std;
+  }
+  return true;
+}
+
+REGISTER_LAYER_CLASS(BatchNorm);
+
+// ---------------------------------------------------------------- Scale / Bias
+
+void ScaleLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const ScaleParameter& p = layer_param_.scale_param();
+  CHECK_EQ(bottom.size(), 1u) << "Scale with the factors in a second bottom is not implemented in this engine";
+  bias_term_ = p.bias_term();
+  const int axis = bottom[0]->CanonicalAxisIndex(p.axis());
+  const int num_axes = p.num_axes();
+  CHECK_GE(num_axes, -1) << "num_axes must be non-negative, or -1 to extend to the end of bottom[0]";
+  vector<int> shape;
+  if (num_axes == -1) {
+    shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().end());
+  } else {
+    CHECK_GE(bottom[0]->num_axes(), axis + num_axes)
+        << "scale blob's shape extends past bottom[0]'s shape when applied starting with bottom[0] axis = " << axis;
+    shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().begin() + axis + num_axes);
+  }
+  if (blobs_.empty()) {
+    blobs_.resize(bias_term_ ? 2 : 1);
+    blobs_[0].reset(new Blob(shape));
+    FillerParameter filler(p.filler());
+    if (!p.has_filler()) {
+      filler.set_type("constant");
+      filler.set_value(1);
+    }
+    FillBlob(filler, blobs_[0].get());
+    if (bias_term_) {
+      blobs_[1].reset(new Blob(shape));
+      FillBlob(p.bias_filler(), blobs_[1].get());
+    }
+  } else {
+    CHECK_EQ(blobs_.size(), static_cast<size_t>(bias_term_ ? 2 : 1)) << "Incorrect number of Scale blobs";
+  }
+  per_channel_ = axis == 1 && blobs_[0]->num_axes() == 1;
+  CHECK(per_channel_ || blobs_[0]->num_axes() == 0)
+      << "Scale: only per-channel (axis 1, one axis) or scalar factors are implemented in this engine";
+}
+
+void ScaleLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  if (per_channel_) {
+    CHECK_EQ(bottom[0]->shape(1), blobs_[0]->shape(0)) << "dimension mismatch between bottom[0]->shape(1) and scale->shape(0)";
+  }
+  ChannelwiseLayer::Reshape(bottom, top);
+}
+
+bool ScaleLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) {
+  if (per_channel_ && blobs_[0]->count() != channels) return false;
+  if (!scale) return true;
+  const float* g = blobs_[0]->cpu_data();
+  const float* b = bias_term_ ? blobs_[1]->cpu_data() : nullptr;
+  scale->resize(channels);
+  shift->resize(channels);
+  for (int c = 0; c < channels; ++c) {
+    (*scale)[c] = g[per_channel_ ? c : 0];
+    (*shift)[c] = b ? b[per_channel_ ? c : 0] : 0.0;
+  }
+  return true;
+}
+
+REGISTER_LAYER_CLASS(Scale);
+
+void BiasLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const BiasParameter& p = layer_param_.bias_param();
+  CHECK_EQ(bottom.size(), 1u) << "Bias with the offsets in a second bottom is not implemented in this engine";
+  const int axis = bottom[0]->CanonicalAxisIndex(p.axis());
+  const int num_axes = p.num_axes();
+  CHECK_GE(num_axes, -1) << "num_axes must be non-negative, or -1 to extend to the end of bottom[0]";
+  if (blobs_.empty()) {
+    vector<int> shape;
+    if (num_axes == -1) {
+      shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().end());
+    } else {
+      CHECK_GE(bottom[0]->num_axes(), axis + num_axes)
+          << "bias blob's shape extends past bottom[0]'s shape when applied starting with bottom[0] axis = " << axis;
+      shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().begin() + axis + num_axes);
+    }
+    blobs_.resize(1);
+    blobs_[0].reset(new Blob(shape));
+    FillBlob(p.filler(), blobs_[0].get());
+  }
+  per_channel_ = axis == 1 && blobs_[0]->num_axes() == 1;
+  CHECK(per_channel_ || blobs_[0]->num_axes() == 0)
+      << "Bias: only per-channel (axis 1, one axis) or scalar offsets are implemented in this engine";
+}
+
+void BiasLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  if (per_channel_) {
+    CHECK_EQ(bottom[0]->shape(1), blobs_[0]->shape(0)) << "dimension mismatch between bottom[0]->shape(1) and bias->shape(0)";
+  }
+  ChannelwiseLayer::Reshape(bottom, top);
+}
+
+bool BiasLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) {
+  if (per_channel_ && blobs_[0]->count() != channels) return false;
+  if (!scale) return true;
+  const float* b = blobs_[0]->cpu_data();
+  scale->assign(channels, 1.0);
+  shift->resize(channels);
+  for (int c = 0; c < channels; ++c) (*shift)[c] = b[per_channel_ ? c : 0];
+  return true;
+}
+
+REGISTER_LAYER_CLASS(Bias);
+
+// ---------------------------------------------------------------- ReLU / PReLU / Dropout
+
+// y = max(x, 0) + slope * min(x, 0) (src/layers/relu_layer.cpp:12-29).
+bool ReLULayer::AsActivation(ActivationSpec* spec) {
+  spec->kind = 1;
+  spec->slope = layer_param_.relu_param().negative_slope();
+  return true;
+}
+REGISTER_LAYER_CLASS(ReLU);
+
+void PReLULayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  CHECK_GE(bottom[0]->num_axes(), 2) << "Number of axes of bottom blob must be >=2.";
+  const PReLUParameter& p = layer_param_.prelu_param();
+  const int channels = bottom[0]->shape(1);
+  channel_shared_ = p.channel_shared();
+  if (blobs_.empty()) {
+    blobs_.resize(1);
+    blobs_[0].reset(new Blob(channel_shared_ ? vector<int>() : vector<int>(1, channels)));
+    FillerParameter filler(p.filler());
+    if (!p.has_filler()) {
+      filler.set_type("constant");
+      filler.set_value(0.25f);
+    }
+    FillBlob(filler, blobs_[0].get());
+  }
+  CHECK_EQ(blobs_[0]->count(), channel_shared_ ? 1 : channels)
+      << "Negative slope size is inconsistent with prototxt config";
+}
+
+bool PReLULayer::AsActivation(ActivationSpec* spec) {
+  spec->kind = 2;
+  spec->slopes = blobs_[0].get();
+  spec->shared = channel_shared_;
+  return true;
+}
+REGISTER_LAYER_CLASS(PReLU);
+
+REGISTER_LAYER_CLASS(Dropout);
+
+// ---------------------------------------------------------------- Eltwise
+
+void EltwiseLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const EltwiseParameter& p = layer_param_.eltwise_param();
+  CHECK(p.coeff_size() == 0 || p.coeff_size() == static_cast<int>(bottom.size()))
+      << "Eltwise Layer takes one coefficient per bottom blob.";
+  CHECK(!(p.operation() == EltwiseParameter_EltwiseOp_PROD && p.coeff_size()))
+      << "Eltwise layer only takes coefficients for summation.";
+  switch (p.operation()) {
+    case EltwiseParameter_EltwiseOp_PROD: op_ = MCB200_ELTWISE_PROD; break;
+    case EltwiseParameter_EltwiseOp_SUM: op_ = MCB200_ELTWISE_SUM; break;
+    case EltwiseParameter_EltwiseOp_MAX: op_ = MCB200_ELTWISE_MAX; break;
+    default: LOG(FATAL) << "Unknown elementwise operation.";
+  }
+  coeffs_.assign(bottom.size(), 1.f);
+  for (int i = 0; i < p.coeff_size(); ++i) coeffs_[i] = p.coeff(i);
+  CHECK_LE(bottom.size(), static_cast<size_t>(MCB200_MAX_ELTWISE_INPUTS))
+      << "Eltwise: at most " << MCB200_MAX_ELTWISE_INPUTS << " bottoms are supported";
+}
+
+void EltwiseLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  for (size_t i = 1; i < bottom.size(); ++i) CHECK(bottom[i]->shape() == bottom[0]->shape());
+  top[0]->ReshapeLike(*bottom[0]);
+}
+
+bool EltwiseLayer::AsWeightedSum(std::vector<float>* coeffs) {
+  if (op_ != MCB200_ELTWISE_SUM) return false;
+  if (coeffs) *coeffs = coeffs_;
+  return true;
+}
+
+void EltwiseLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  Context& ctx = Context::Get();
+  bool nhwc = false;
+  for (Blob* b : bottom) nhwc = nhwc || b->device_is_nhwc();
+  const float* in[MCB200_MAX_ELTWISE_INPUTS];
+  for (size_t i = 0; i < bottom.size(); ++i) in[i] = nhwc ? bottom[i]->gpu_data_nhwc() : bottom[i]->gpu_data();
+  float* out = nhwc ? top[0]->mutable_gpu_data_nhwc() : top[0]->mutable_gpu_data();
+  KERNEL_CHECK(mcb200_eltwise(op_, static_cast<int>(bottom.size()), in, coeffs_.data(), out, top[0]->count(), 0, 0.f,
+                              ctx.stream_ptr()));
+}
+
+REGISTER_LAYER_CLASS(Eltwise);
+
+}  // namespace caffe

@@ -1,0 +1,330 @@
+// Declarations of the engine's layer classes (one registry entry each).
+#ifndef MCB200_LAYERS_H_
+#define MCB200_LAYERS_H_
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../layer.h"
+#include "mcb200_kernels.h"
+
+namespace caffe {
+
+// A float array that lives on the device and is refreshed from host values.
+class DeviceArray {
+ public:
+  void Assign(const std::vector<float>& host);
+  const float* get() const { return blob_ ? blob_->gpu_data() : nullptr; }
+  void Clear() { blob_.reset(); }
+ private:
+  std::unique_ptr<Blob> blob_;
+};
+
+// Scratch device memory owned by a layer (grown on demand, never shrunk).
+class DeviceScratch {
+ public:
+  float* Reserve(size_t floats);
+ private:
+  std::unique_ptr<Blob> blob_;
+};
+
+// ---------------------------------------------------------------- producers
+
+// Convolution, 2-D, any stride / pad / dilation / group.  group == 1 runs on
+// the tensor cores, group == channels on the depthwise kernel, the rest on the
+// direct kernel.  Parameter handling follows src/layers/base_conv_layer.cpp:11-182.
+class ConvolutionLayer : public Layer {
+ public:
+  explicit ConvolutionLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Convolution"; }
+  int MinBottomBlobs() const override { return 1; }
+  int MinTopBlobs() const override { return 1; }
+  bool EqualNumBottomTopBlobs() const override { return true; }
+  bool AcceptsFusedTail() const override { return true; }
+  void SetFusedTail(const FusedTail& tail) override { tail_ = tail; tail_version_ = 0; }
+
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void RefreshParameters();
+  void FillEpilogue(mcb200_epilogue* ep);
+
+  mcb200_conv_shape shape_ = mcb200_conv_shape();
+  bool bias_term_ = false;
+  FusedTail tail_;
+  unsigned long long tail_version_ = 0;    // parameter versions the folded arrays were built from
+  unsigned long long weight_version_ = 0;
+  DeviceArray scale_, shift_;
+  DeviceScratch packed_weights_, padded_input_;
+  enum Path { kTensorCore, kDepthwise, kDirect } path_ = kDirect;
+  struct PlanSlot {
+    mcb200_conv_plan plan;
+    const float* in = nullptr;
+    const float* weights = nullptr;
+    mcb200_conv_shape shape = mcb200_conv_shape();
+    bool valid = false;
+  };
+  std::vector<std::unique_ptr<PlanSlot> > plans_;  // one per bottom
+};
+
+// y = x W^T + b as a 1x1 convolution over [M, K] (src/layers/inner_product_layer.cpp:8-93).
+class InnerProductLayer : public Layer {
+ public:
+  explicit InnerProductLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "InnerProduct"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+  bool AcceptsFusedTail() const override { return true; }
+  void SetFusedTail(const FusedTail& tail) override { tail_ = tail; tail_version_ = 0; }
+
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int M_ = 0, K_ = 0, N_ = 0;
+  bool bias_term_ = false, transpose_ = false;
+  FusedTail tail_;
+  unsigned long long tail_version_ = 0, weight_version_ = 0;
+  DeviceArray scale_, shift_;
+  DeviceScratch packed_weights_, staged_weights_;
+  mcb200_conv_plan* plan_ = nullptr;
+  std::unique_ptr<char[]> plan_storage_;
+  const float* plan_in_ = nullptr;
+  const float* plan_w_ = nullptr;
+  int plan_m_ = -1;
+};
+
+// Folds a FusedTail and an optional bias into per-channel scale / shift
+// arrays; returns the combined parameter version.
+unsigned long long TailVersion(const FusedTail& tail);
+void FoldTail(const FusedTail& tail, int channels, const float* bias, std::vector<float>* scale,
+              std::vector<float>* shift, bool* has_scale, bool* has_shift);
+void FillTailEpilogue(const FusedTail& tail, const DeviceArray& scale, const DeviceArray& shift, bool nhwc_residual,
+                      int channels, mcb200_epilogue* ep);
+
+// ---------------------------------------------------------------- per-channel / elementwise
+
+// Shared forward of layers of the form y = act(x * scale[c] + shift[c]).
+class ChannelwiseLayer : public Layer {
+ public:
+  explicit ChannelwiseLayer(const LayerParameter& param) : Layer(param) {}
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int ExactNumTopBlobs() const override { return 1; }
+
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  // The channel axis is axis 1; `inner` elements follow it in (N, C, ...) order.
+  virtual int Channels(const Blob* bottom) const { return bottom->num_axes() > 1 ? bottom->shape(1) : 1; }
+  DeviceArray scale_dev_, shift_dev_;
+  unsigned long long built_version_ = 0;
+  int built_channels_ = -1;
+};
+
+class BatchNormLayer : public ChannelwiseLayer {
+ public:
+  explicit BatchNormLayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "BatchNorm"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+ private:
+  int channels_ = 0;
+  float eps_ = 1e-5f;
+};
+
+class ScaleLayer : public ChannelwiseLayer {
+ public:
+  explicit ScaleLayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Scale"; }
+  int MinBottomBlobs() const override { return 1; }
+  int MaxBottomBlobs() const override { return 2; }
+  bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+ private:
+  bool per_channel_ = false;  // learned scale of shape [C] applied on axis 1
+  bool bias_term_ = false;
+};
+
+class BiasLayer : public ChannelwiseLayer {
+ public:
+  explicit BiasLayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Bias"; }
+  int MinBottomBlobs() const override { return 1; }
+  int MaxBottomBlobs() const override { return 2; }
+  bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+ private:
+  bool per_channel_ = false;
+};
+
+class ReLULayer : public ChannelwiseLayer {
+ public:
+  explicit ReLULayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  const char* type() const override { return "ReLU"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  bool AsActivation(ActivationSpec* spec) override;
+};
+
+class PReLULayer : public ChannelwiseLayer {
+ public:
+  explicit PReLULayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "PReLU"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  bool AsActivation(ActivationSpec* spec) override;
+ private:
+  bool channel_shared_ = false;
+};
+
+// Inference-time Dropout is the identity (the reference scales nothing at test time).
+class DropoutLayer : public ChannelwiseLayer {
+ public:
+  explicit DropoutLayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  const char* type() const override { return "Dropout"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+};
+
+class EltwiseLayer : public Layer {
+ public:
+  explicit EltwiseLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Eltwise"; }
+  int MinBottomBlobs() const override { return 2; }
+  int ExactNumTopBlobs() const override { return 1; }
+  bool AsWeightedSum(std::vector<float>* coeffs) override;
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int op_ = MCB200_ELTWISE_SUM;
+  std::vector<float> coeffs_;
+};
+
+// ---------------------------------------------------------------- pooling / softmax / normalize
+
+class PoolingLayer : public Layer {
+ public:
+  explicit PoolingLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Pooling"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int kernel_h_ = 0, kernel_w_ = 0, stride_h_ = 1, stride_w_ = 1, pad_h_ = 0, pad_w_ = 0;
+  int pooled_h_ = 0, pooled_w_ = 0;
+  bool global_ = false;
+  int method_ = MCB200_POOL_MAX;
+};
+
+class SoftmaxLayer : public Layer {
+ public:
+  explicit SoftmaxLayer(const LayerParameter& param) : Layer(param) {}
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Softmax"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int axis_ = 1;
+};
+
+class NormalizeLayer : public Layer {
+ public:
+  explicit NormalizeLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Normalize"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  bool across_spatial_ = true, channel_shared_ = true;
+  float eps_ = 1e-10f;
+};
+
+// ---------------------------------------------------------------- graph plumbing
+
+class InputLayer : public Layer {
+ public:
+  explicit InputLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override {}
+  const char* type() const override { return "Input"; }
+  int ExactNumBottomBlobs() const override { return 0; }
+  int MinTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override {}
+};
+
+class SplitLayer : public Layer {
+ public:
+  explicit SplitLayer(const LayerParameter& param) : Layer(param) {}
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Split"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int MinTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+};
+
+class FlattenLayer : public Layer {
+ public:
+  explicit FlattenLayer(const LayerParameter& param) : Layer(param) {}
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Flatten"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+};
+
+class ReshapeLayer : public Layer {
+ public:
+  explicit ReshapeLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Reshape"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  std::vector<int> copy_axes_;
+  int inferred_axis_ = -1;
+  int constant_count_ = 1;
+};
+
+class PermuteLayer : public Layer {
+ public:
+  explicit PermuteLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Permute"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  std::vector<int> order_;
+  bool need_permute_ = false;
+};
+
+class ConcatLayer : public Layer {
+ public:
+  explicit ConcatLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Concat"; }
+  int MinBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int axis_ = 1;
+};
+
+}  // namespace caffe
+
+#endif  // MCB200_LAYERS_H_

@@ -1,0 +1,248 @@
+#include "syncedmem.h"
+
+#include <cstdlib>
+#include <cstring>
+
+#include "context.h"
+#include "mcb200_kernels.h"
+
+namespace caffe {
+
+// ---------------------------------------------------------------- MemoryPool
+
+MemoryPool* MemoryPool::Get() {
+  static thread_local MemoryPool pool;
+  return &pool;
+}
+
+MemoryPool::~MemoryPool() { Clear(); }
+
+static bool Reusable(size_t has, size_t wants) { return has / 2 <= wants; }
+
+MemBlock MemoryPool::RequestCPU(size_t size) {
+  auto it = cpu_free_.lower_bound(size);
+  if (it != cpu_free_.end() && Reusable(it->second.size, size)) {
+    MemBlock b = it->second;
+    cpu_free_.erase(it);
+    cpu_unused_ -= static_cast<long long>(b.size);
+    return b;
+  }
+  MemBlock b;
+  b.size = size;
+  b.device = -1;
+  if (DeviceCount() > 0) {
+    // Pinned, so that host<->device copies can run asynchronously on the stream.
+    CUDA_CHECK(cudaMallocHost(&b.ptr, size));
+  } else {
+    CHECK_EQ(posix_memalign(&b.ptr, 64, size), 0) << "out of host memory";
+  }
+  cpu_total_ += static_cast<long long>(size);
+  return b;
+}
+
+void MemoryPool::ReturnCPU(MemBlock block) {
+  if (!block.ptr) return;
+  cpu_unused_ += static_cast<long long>(block.size);
+  cpu_free_.insert(std::make_pair(block.size, block));
+}
+
+MemBlock MemoryPool::RequestGPU(size_t size, int device) {
+  auto it = gpu_free_.lower_bound(std::make_pair(device, size));
+  if (it != gpu_free_.end() && it->second.device == device && Reusable(it->second.size, size)) {
+    MemBlock b = it->second;
+    gpu_free_.erase(it);
+    gpu_unused_ -= static_cast<long long>(b.size);
+    return b;
+  }
+  MemBlock b;
+  b.size = size;
+  b.device = device;
+  int current = 0;
+  CUDA_CHECK(cudaGetDevice(&current));
+  if (current != device) CUDA_CHECK(cudaSetDevice(device));
+  CUDA_CHECK(cudaMalloc(&b.ptr, size));
+  if (current != device) CUDA_CHECK(cudaSetDevice(current));
+  gpu_total_ += static_cast<long long>(size);
+  return b;
+}
+
+void MemoryPool::ReturnGPU(MemBlock block) {
+  if (!block.ptr) return;
+  gpu_unused_ += static_cast<long long>(block.size);
+  gpu_free_.insert(std::make_pair(std::make_pair(block.device, block.size), block));
+}
+
+void MemoryPool::Clear() {
+  const bool have_device = DeviceCount() > 0;
+  for (auto& kv : cpu_free_) {
+    if (have_device) {
+      cudaFreeHost(kv.second.ptr);
+    } else {
+      free(kv.second.ptr);
+    }
+    cpu_total_ -= static_cast<long long>(kv.second.size);
+  }
+  cpu_free_.clear();
+  cpu_unused_ = 0;
+  if (have_device && !gpu_free_.empty()) {
+    int current = 0;
+    if (cudaGetDevice(&current) == cudaSuccess) {
+      // Blocks may still be read by kernels queued on this thread's stream.
+      Context::Get().Sync();
+      for (auto& kv : gpu_free_) {
+        if (kv.second.device != current) cudaSetDevice(kv.second.device);
+        cudaFree(kv.second.ptr);
+        if (kv.second.device != current) cudaSetDevice(current);
+        gpu_total_ -= static_cast<long long>(kv.second.size);
+      }
+    }
+    cudaGetLastError();
+  }
+  gpu_free_.clear();
+  gpu_unused_ = 0;
+}
+
+static int Saturate(long long v) { return v > 0x7fffffffLL ? 0x7fffffff : static_cast<int>(v); }
+
+MemPoolState MemoryPool::GetState() const {
+  MemPoolState st;
+  st.cpu_mem = Saturate(cpu_total_);
+  st.gpu_mem = Saturate(gpu_total_);
+  st.unused_cpu_mem = Saturate(cpu_unused_);
+  st.unused_gpu_mem = Saturate(gpu_unused_);
+  return st;
+}
+
+void MemPoolClear() { MemoryPool::Get()->Clear(); }
+MemPoolState MemPoolGetState() { return MemoryPool::Get()->GetState(); }
+
+// ---------------------------------------------------------------- SyncedMemory
+
+SyncedMemory::SyncedMemory(size_t size)
+    : size_(size), valid_(0), nhwc_aliases_dev_(false), host_version_(1) {
+  dims_[0] = dims_[1] = dims_[2] = dims_[3] = 0;
+}
+
+SyncedMemory::~SyncedMemory() {
+  // Kernels queued on the stream may still use the device blocks; the pool
+  // hands them out again only to work queued on the same stream, which is
+  // ordered after those kernels.
+  MemoryPool* pool = MemoryPool::Get();
+  if (host_.ptr) {
+    // A pinned block may be the target of a copy that is still in flight.
+    if (valid_ & (kDevice | kDeviceNhwc)) {
+      try { Context::Get().Sync(); } catch (...) {}
+    }
+    pool->ReturnCPU(host_);
+  }
+  if (dev_.ptr) pool->ReturnGPU(dev_);
+  if (nhwc_.ptr) pool->ReturnGPU(nhwc_);
+}
+
+void SyncedMemory::EnsureHost() {
+  if (!host_.ptr) {
+    host_ = MemoryPool::Get()->RequestCPU(size_ ? size_ : 4);
+    if (!(valid_ & (kDevice | kDeviceNhwc))) {
+      std::memset(host_.ptr, 0, size_);  // same as the reference: fresh memory reads as zero
+      valid_ |= kHost;
+    }
+  }
+}
+
+void SyncedMemory::EnsureDevice() {
+  if (!dev_.ptr) {
+    Context& ctx = Context::Get();
+    ctx.Activate();
+    dev_ = MemoryPool::Get()->RequestGPU(size_ ? size_ : 4, ctx.device());
+    if (valid_ == 0) {
+      CUDA_CHECK(cudaMemsetAsync(dev_.ptr, 0, size_, ctx.stream()));
+      valid_ |= kDevice;
+    }
+  }
+}
+
+void SyncedMemory::EnsureNhwcBuffer() {
+  if (!nhwc_.ptr) {
+    Context& ctx = Context::Get();
+    ctx.Activate();
+    nhwc_ = MemoryPool::Get()->RequestGPU(size_ ? size_ : 4, ctx.device());
+  }
+}
+
+void SyncedMemory::DeviceFromFreshest() {
+  if (valid_ & kDevice) return;
+  EnsureDevice();
+  if (valid_ & kDevice) return;  // freshly zero-filled
+  Context& ctx = Context::Get();
+  if (valid_ & kDeviceNhwc) {
+    CHECK(!nhwc_aliases_dev_);
+    KERNEL_CHECK(mcb200_nhwc_to_nchw(static_cast<const float*>(nhwc_.ptr), static_cast<float*>(dev_.ptr), dims_[0],
+                                     dims_[1], dims_[2], dims_[3], dims_[1], ctx.stream_ptr()));
+  } else {
+    CHECK(valid_ & kHost);
+    CUDA_CHECK(cudaMemcpyAsync(dev_.ptr, host_.ptr, size_, cudaMemcpyHostToDevice, ctx.stream()));
+  }
+  valid_ |= kDevice;
+}
+
+const void* SyncedMemory::cpu_data() {
+  EnsureHost();
+  if (!(valid_ & kHost)) {
+    DeviceFromFreshest();
+    Context& ctx = Context::Get();
+    CUDA_CHECK(cudaMemcpyAsync(host_.ptr, dev_.ptr, size_, cudaMemcpyDeviceToHost, ctx.stream()));
+    ctx.SyncAndCheck();
+    valid_ |= kHost;
+  }
+  return host_.ptr;
+}
+
+void* SyncedMemory::mutable_cpu_data() {
+  cpu_data();
+  valid_ = kHost;
+  ++host_version_;
+  return host_.ptr;
+}
+
+const void* SyncedMemory::gpu_data() {
+  DeviceFromFreshest();
+  return dev_.ptr;
+}
+
+void* SyncedMemory::mutable_gpu_data() {
+  EnsureDevice();
+  valid_ = kDevice;
+  nhwc_aliases_dev_ = false;
+  return dev_.ptr;
+}
+
+const void* SyncedMemory::gpu_data_nhwc(int n, int c, int h, int w) {
+  CHECK_LE(static_cast<size_t>(n) * c * h * w * sizeof(float), size_);
+  if (OrdersCoincide(c, h, w)) return gpu_data();
+  if (valid_ & kDeviceNhwc) {
+    CHECK(dims_[0] == n && dims_[1] == c && dims_[2] == h && dims_[3] == w)
+        << "channels-last copy was written with another shape";
+    return nhwc_.ptr;
+  }
+  DeviceFromFreshest();
+  EnsureNhwcBuffer();
+  Context& ctx = Context::Get();
+  KERNEL_CHECK(mcb200_nchw_to_nhwc(static_cast<const float*>(dev_.ptr), static_cast<float*>(nhwc_.ptr), n, c, h, w, c,
+                                   ctx.stream_ptr()));
+  dims_[0] = n; dims_[1] = c; dims_[2] = h; dims_[3] = w;
+  nhwc_aliases_dev_ = false;
+  valid_ |= kDeviceNhwc;
+  return nhwc_.ptr;
+}
+
+void* SyncedMemory::mutable_gpu_data_nhwc(int n, int c, int h, int w) {
+  CHECK_LE(static_cast<size_t>(n) * c * h * w * sizeof(float), size_);
+  if (OrdersCoincide(c, h, w)) return mutable_gpu_data();
+  EnsureNhwcBuffer();
+  dims_[0] = n; dims_[1] = c; dims_[2] = h; dims_[3] = w;
+  nhwc_aliases_dev_ = false;
+  valid_ = kDeviceNhwc;
+  return nhwc_.ptr;
+}
+
+}  // namespace caffe

@@ -1,0 +1,105 @@
+"""End-to-end parity: generated networks run through libcaffe.so on the GPU and
+through the reference project's own CPU code (oracle/_ref), same weights, same
+inputs.  Tolerance for TF32 tensor-core layers: |a-b| <= 2e-2 + 1e-2*|b|."""
+import numpy as np
+import pytest
+
+from conftest import pkg
+from parity import assert_close, run_net
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu_engine(engine):
+    engine.set_mode(True, 0)
+    return engine
+
+
+@pytest.mark.parametrize("batch", [1, 32])
+def test_conv_relu_config(capi, gpu_engine, reflib, batch):
+    wl = pkg("workloads")
+    b = wl.conv_relu(batch)
+    weights = wl.init_params(b.params, seed=0)
+    inputs = wl.conv_relu_input(batch, seed=0)
+    got = run_net(capi, gpu_engine, b, weights, inputs, ["conv"])
+    want = run_net(capi, reflib, b, weights, inputs, ["conv"])
+    assert_close(got["conv"], want["conv"], "conv+relu b=%d" % batch)
+
+
+def small_residual_net(wl, batch, bn_identity):
+    b = wl.NetBuilder("mini_resnet")
+    b.input([("data", (batch, 3, 32, 32))])
+    b.conv_bn("stem", "data", "stem", 3, 32, 3, stride=1, pad=1, bn_prefix="bn_", scale_prefix="scale_")
+    b.pool("pool1", "stem", "pool1", "MAX", k=3, stride=2)
+    b.conv_bn("short", "pool1", "short", 32, 64, 1, relu=False, bn_prefix="bn_", scale_prefix="scale_")
+    b.conv_bn("a", "pool1", "a", 32, 16, 1, bn_prefix="bn_", scale_prefix="scale_")
+    b.conv_bn("b", "a", "b", 16, 16, 3, pad=1, bn_prefix="bn_", scale_prefix="scale_")
+    b.conv_bn("c", "b", "c", 16, 64, 1, relu=False, bn_prefix="bn_", scale_prefix="scale_")
+    b.eltwise_sum("res", ["short", "c"], "res")
+    b.relu("res_relu", "res")
+    b.pool("gap", "res", "gap", "AVE", global_pooling=True)
+    b.inner_product("fc", "gap", "fc", 64, 10)
+    b.softmax("prob", "fc", "prob")
+    return b
+
+
+@pytest.mark.parametrize("bn_identity", [True, False])
+def test_small_residual_net(capi, gpu_engine, reflib, bn_identity):
+    wl = pkg("workloads")
+    b = small_residual_net(wl, 4, bn_identity)
+    weights = wl.init_params(b.params, seed=3, bn_identity=bn_identity)
+    x = {"data": np.random.default_rng(5).standard_normal((4, 3, 32, 32)).astype(np.float32)}
+    outs = ["fc", "prob"]
+    got = run_net(capi, gpu_engine, b, weights, x, outs)
+    want = run_net(capi, reflib, b, weights, x, outs)
+    for name in outs:
+        assert_close(got[name], want[name], name)
+
+
+def test_marked_outputs_block_fusion(capi, gpu_engine, reflib):
+    """Marking an intermediate blob must keep it readable (no fusion through it)
+    and must not change any result."""
+    wl = pkg("workloads")
+    b = small_residual_net(wl, 2, False)
+    weights = wl.init_params(b.params, seed=4, bn_identity=False)
+    x = {"data": np.random.default_rng(6).standard_normal((2, 3, 32, 32)).astype(np.float32)}
+    marks = ["pool1", "c", "short", "res", "gap"]
+    got = run_net(capi, gpu_engine, b, weights, x, marks + ["prob"], marks=marks)
+    want = run_net(capi, reflib, b, weights, x, marks + ["prob"], marks=marks)
+    for name in marks + ["prob"]:
+        assert_close(got[name], want[name], name)
+
+
+def test_resnet50_batch2(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.resnet50(2)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.image_input(2, seed=0)
+    outs = ["fc1000", "prob"]
+    marks = ["pool1", "res2c", "res3d", "res4f", "res5c"]
+    got = run_net(capi, gpu_engine, b, weights, x, outs + marks, marks=marks)
+    want = run_net(capi, reflib, b, weights, x, outs + marks, marks=marks)
+    for name in marks + outs:
+        assert_close(got[name], want[name], name)
+
+
+def test_batch_invariance(capi, gpu_engine):
+    """Same image at batch 1, 2, 1: identical class scores in every slot (the one
+    numeric check the reference's own tests make, tests/run_net.cpp:274-321)."""
+    wl = pkg("workloads")
+    b = small_residual_net(wl, 1, False)
+    weights = wl.init_params(b.params, seed=9, bn_identity=False)
+    img = np.random.default_rng(10).standard_normal((1, 3, 32, 32)).astype(np.float32)
+    net = capi.Net(gpu_engine, b.text(), None, from_buffer=True)
+    net.set_params(weights)
+    net.forward(data=img)
+    p1 = net.blob("prob").data.copy()
+    net.forward(data=np.concatenate([img, img]))
+    p2 = net.blob("prob").data.copy()
+    net.forward(data=img)
+    p3 = net.blob("prob").data.copy()
+    assert p2.shape == (2, 10)
+    assert np.abs(p2[0] - p1[0]).max() < 1e-6
+    assert np.abs(p2[1] - p1[0]).max() < 1e-6
+    assert np.abs(p3[0] - p1[0]).max() < 1e-6
