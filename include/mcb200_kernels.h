@@ -166,6 +166,68 @@ int mcb200_permute(const float* in, float* out, int num_axes, const int* in_shap
 int mcb200_normalize_nhwc(const float* in, float* out, long long pixels, int channels, const float* scale,
                           int scale_shared, float eps, void* stream);
 
+/* ------------------------------------------------------------------ RPN proposals */
+typedef struct mcb200_proposal_params {
+  int num_anchors, height, width;  /* score map [2A, H, W], delta map [4A, H, W] per image */
+  int feat_stride;
+  int min_size;                    /* multiplied by im_info[2] on the device            */
+  int pre_nms_topn, post_nms_topn;
+  float nms_thresh;
+} mcb200_proposal_params;
+
+/* Bytes of device scratch mcb200_proposal_forward needs for `batch` images
+ * (0 if the parameters are rejected; pre_nms_topn is limited to 16384).      */
+size_t mcb200_proposal_workspace_bytes(const mcb200_proposal_params* p, int batch);
+
+/* ProposalLayer::Forward_cpu (src/layers/proposal_layer.cpp:261-320) for `batch`
+ * independent images: decode anchors + deltas, clip, zero the score of boxes
+ * below min_size, take the pre_nms_topn best by score, greedy NMS with the "+1
+ * pixel" IoU, keep at most post_nms_topn.
+ *   scores   [batch, 2A, H, W]   (foreground = channels A..2A-1)
+ *   deltas   [batch, 4A, H, W]
+ *   im_info  [batch, 3]          (height, width, scale)
+ *   anchors  [A, 4]              base anchors (x1, y1, x2, y2)
+ *   rois     [batch, post_nms_topn, 5]  rows (image index, x1, y1, x2, y2); the
+ *            first counts[b] rows of image b are valid
+ *   roi_scores [batch, post_nms_topn] or NULL
+ *   counts   [batch] ints (device)
+ * `workspace` must be 256-byte aligned.  Kept boxes match the CPU code bit for
+ * bit when no two scores among the pre_nms_topn best are equal (equal scores
+ * are ordered by proposal index here; the CPU order is unspecified).         */
+int mcb200_proposal_forward(const mcb200_proposal_params* p, int batch, const float* scores, const float* deltas,
+                            const float* im_info, const float* anchors, void* workspace, float* rois,
+                            float* roi_scores, int* counts, void* stream);
+
+/* ------------------------------------------------------------------ SSD detection output */
+typedef struct mcb200_detout_params {
+  int num_priors, num_classes;
+  int share_location;              /* 1: one box per prior for all classes              */
+  int background_label_id;         /* skipped class, -1 for none                        */
+  int code_type;                   /* 1 CORNER, 2 CENTER_SIZE, 3 CORNER_SIZE            */
+  int variance_encoded_in_target;
+  float confidence_threshold;
+  float nms_threshold;
+  float eta;                       /* < 1: the NMS threshold shrinks by eta per kept box while above 0.5 */
+  int top_k;                       /* per class, -1: all priors (at most 4096 here)     */
+  int keep_top_k;                  /* per image, -1: unlimited                          */
+} mcb200_detout_params;
+
+size_t mcb200_detout_workspace_bytes(const mcb200_detout_params* p, int batch);
+/* Rows per image the output buffer must hold. */
+int mcb200_detout_max_rows_per_image(const mcb200_detout_params* p);
+
+/* DetectionOutputLayer::Forward_cpu (src/layers/detection_output_layer.cpp:74-226
+ * with ApplyNMSFast / DecodeBBox / JaccardOverlap of src/util/bbox_util.cpp):
+ *   loc    [batch, num_priors * (share_location ? 1 : num_classes) * 4]
+ *   conf   [batch, num_priors * num_classes]     (prior-major)
+ *   prior  [2, num_priors * 4]                   (boxes, then variances)
+ *   out    [batch * max_rows_per_image, 7] rows (image, label, score, xmin, ymin,
+ *          xmax, ymax), images in order, labels ascending within an image, score
+ *          descending within a label; *total (device int) receives the row count.
+ * top_k (or num_priors when top_k is -1) may be at most 4096.                */
+int mcb200_detout_forward(const mcb200_detout_params* p, int batch, const float* loc, const float* conf,
+                          const float* prior, void* workspace, float* out, int* total, void* stream);
+
 /* Number of kernels launched by this library on the calling thread since the
  * last reset (bench.py reports it as gpu_launches).                          */
 long long mcb200_launch_count(void);

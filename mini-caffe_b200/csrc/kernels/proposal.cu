@@ -248,7 +248,8 @@ proposal_nms_scan_kernel(Workspace ws, int post_nms_topn, float* __restrict__ ro
     stop = 0;
   }
   __syncthreads();
-  for (int block = 0; block < cb && !stop; ++block) {
+  bool done = false;
+  for (int block = 0; block < cb && !done; ++block) {
     if (threadIdx.x == 0) {
       unsigned long long gone = removed[block];
       unsigned long long keep = 0;
@@ -277,7 +278,10 @@ proposal_nms_scan_kernel(Workspace ws, int post_nms_topn, float* __restrict__ ro
       kept_total = total;
     }
     __syncthreads();
-    if (!stop) {
+    // Everyone takes the same copy of the flag here; thread 0 writes it again
+    // only after the barrier that ends this iteration.
+    done = stop != 0;
+    if (!done) {
       const unsigned long long keep = keep_word;
       for (int w = block + 1 + threadIdx.x; w < cb; w += blockDim.x) {
         unsigned long long acc = removed[w];

@@ -325,6 +325,67 @@ class ConcatLayer : public Layer {
   int axis_ = 1;
 };
 
+// ---------------------------------------------------------------- detection
+
+// Prior (default) boxes of an SSD head: depends only on shapes and layer
+// parameters, so it is computed on the host when the shapes change and kept
+// on the device (src/layers/prior_box_layer.cpp:118-217).
+class PriorBoxLayer : public Layer {
+ public:
+  explicit PriorBoxLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "PriorBox"; }
+  int ExactNumBottomBlobs() const override { return 2; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Compute(int layer_h, int layer_w, int img_h, int img_w, float* out) const;
+  std::vector<float> min_sizes_, max_sizes_, aspect_ratios_, variance_;
+  bool flip_ = true, clip_ = false;
+  int num_priors_ = 0, img_h_ = 0, img_w_ = 0;
+  float step_h_ = 0, step_w_ = 0, offset_ = 0.5f;
+  std::vector<float> cached_;
+  int cached_key_[4] = {-1, -1, -1, -1};
+};
+
+// RPN proposals (src/layers/proposal_layer.cpp).  The reference accepts one
+// image per call; this layer also takes N > 1 and then puts the image index
+// in column 0 of each roi.
+class ProposalLayer : public Layer {
+ public:
+  explicit ProposalLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  // The reference reports this spelling (src/layers/proposal_layer.hpp:19).
+  const char* type() const override { return "ProposalLayer"; }
+  int ExactNumBottomBlobs() const override { return 3; }
+  int MinTopBlobs() const override { return 1; }
+  int MaxTopBlobs() const override { return 2; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  mcb200_proposal_params params_ = mcb200_proposal_params();
+  DeviceArray anchors_;
+  int num_anchors_ = 0;
+  std::unique_ptr<Blob> workspace_, staging_rois_, staging_scores_;
+  std::unique_ptr<BlobInt> counts_;
+};
+
+class DetectionOutputLayer : public Layer {
+ public:
+  explicit DetectionOutputLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "DetectionOutput"; }
+  int ExactNumBottomBlobs() const override { return 3; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  mcb200_detout_params params_ = mcb200_detout_params();
+  std::unique_ptr<Blob> workspace_;
+  std::unique_ptr<BlobInt> total_;
+};
+
 }  // namespace caffe
 
 #endif  // MCB200_LAYERS_H_

@@ -1,0 +1,163 @@
+"""Detection tail parity (Proposal + NMS, PriorBox, DetectionOutput) against the
+reference project's CPU code.  Index work is compared bit for bit: the kept
+boxes, their order and their float coordinates must be identical."""
+import numpy as np
+import pytest
+
+from conftest import pkg
+from parity import assert_close, run_net
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu_engine(engine):
+    engine.set_mode(True, 0)
+    return engine
+
+
+def test_exp_overload_recorded(reflib):
+    """The oracle was built with exp(float) bound to the double version in the box
+    decoders; the device code assumes exactly that."""
+    assert reflib.lib.OracleRefProposalExpIsDouble() == 1
+    assert reflib.lib.OracleRefBBoxExpIsDouble() == 1
+
+
+@pytest.mark.parametrize("anchors", [15, 9])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_proposal_config_bit_exact(capi, gpu_engine, reflib, anchors, seed):
+    wl = pkg("workloads")
+    b = wl.proposal(num_anchors=anchors, with_scores=True)
+    inputs, _ = wl.proposal_input(num_anchors=anchors, seed=seed)
+    got = run_net(capi, gpu_engine, b, {}, inputs, ["rois", "scores"])
+    want = run_net(capi, reflib, b, {}, inputs, ["rois", "scores"])
+    assert got["rois"].shape == want["rois"].shape
+    assert got["rois"].shape[0] > 0
+    assert np.array_equal(got["rois"].view(np.uint32), want["rois"].view(np.uint32))
+    assert np.array_equal(got["scores"].view(np.uint32), want["scores"].view(np.uint32))
+
+
+@pytest.mark.parametrize("case", [
+    # anchors, H, W, pre, post, thresh, min_size
+    (9, 5, 7, 6000, 300, 0.7, 16),       # fewer proposals than pre_nms_topn
+    (9, 20, 30, 100, 10, 0.5, 4),        # tight limits
+    (3, 1, 1, 6000, 300, 0.7, 16),       # a single cell
+    (9, 40, 25, 2000, 2000, 0.3, 0),     # post limit never reached
+])
+def test_proposal_edge_shapes(capi, gpu_engine, reflib, case):
+    wl = pkg("workloads")
+    anchors, h, w, pre, post, thr, min_size = case
+    scales = {9: (8, 16, 32), 3: (8,)}[anchors]
+    b = wl.NetBuilder("proposal_edge")
+    b.input([("rpn_cls_prob", (1, 2 * anchors, h, w)), ("rpn_bbox_pred", (1, 4 * anchors, h, w)), ("im_info", (1, 3))])
+    b.raw("proposal", "Proposal", ["rpn_cls_prob", "rpn_bbox_pred", "im_info"], ["rois", "scores"],
+          "proposal_param { feat_stride: 16 base_size: 16 min_size: %d pre_nms_topn: %d post_nms_topn: %d "
+          "nms_thresh: %g ratio: 0.5 ratio: 1 ratio: 2 %s }" % (min_size, pre, post, thr,
+                                                                 " ".join("scale: %d" % s for s in scales)))
+    inputs, _ = wl.proposal_input(num_anchors=anchors, height=h, width=w, seed=11, im_h=16.0 * h, im_w=16.0 * w)
+    got = run_net(capi, gpu_engine, b, {}, inputs, ["rois", "scores"])
+    want = run_net(capi, reflib, b, {}, inputs, ["rois", "scores"])
+    assert got["rois"].shape == want["rois"].shape
+    assert np.array_equal(got["rois"].view(np.uint32), want["rois"].view(np.uint32))
+    assert np.array_equal(got["scores"].view(np.uint32), want["scores"].view(np.uint32))
+
+
+def detection_head_net(wl, batch, num_priors, num_classes, conf_thr, nms_thr, top_k, keep_top_k, code_type="CENTER_SIZE",
+                       share_location=True):
+    loc_classes = 1 if share_location else num_classes
+    b = wl.NetBuilder("detout")
+    b.input([("loc", (batch, num_priors * loc_classes * 4)), ("conf", (batch, num_priors * num_classes)),
+             ("prior", (1, 2, num_priors * 4))])
+    b.raw("detection_out", "DetectionOutput", ["loc", "conf", "prior"], ["detection_out"],
+          "detection_output_param { num_classes: %d share_location: %s background_label_id: 0 "
+          "nms_param { nms_threshold: %g top_k: %d } code_type: %s keep_top_k: %d confidence_threshold: %g }" %
+          (num_classes, "true" if share_location else "false", nms_thr, top_k, code_type, keep_top_k, conf_thr))
+    return b
+
+
+def detection_inputs(batch, num_priors, num_classes, seed, share_location=True, peaked=False):
+    rng = np.random.default_rng(seed)
+    loc_classes = 1 if share_location else num_classes
+    loc = (rng.standard_normal((batch, num_priors * loc_classes * 4)) * 0.5).astype(np.float32)
+    logits = rng.standard_normal((batch, num_priors, num_classes)) * (3.0 if peaked else 0.3)
+    e = np.exp(logits - logits.max(axis=2, keepdims=True))
+    conf = (e / e.sum(axis=2, keepdims=True)).astype(np.float32).reshape(batch, -1)
+    cx = rng.uniform(0.1, 0.9, num_priors)
+    cy = rng.uniform(0.1, 0.9, num_priors)
+    w = rng.uniform(0.05, 0.4, num_priors)
+    h = rng.uniform(0.05, 0.4, num_priors)
+    boxes = np.stack([cx - w / 2, cy - h / 2, cx + w / 2, cy + h / 2], axis=1).astype(np.float32)
+    var = np.tile(np.array([0.1, 0.1, 0.2, 0.2], dtype=np.float32), (num_priors, 1))
+    prior = np.stack([boxes.reshape(-1), var.reshape(-1)])[None].astype(np.float32)
+    return {"loc": loc, "conf": conf, "prior": prior}
+
+
+def sort_rows(rows):
+    """Rows grouped by (image, label) keep their order inside the group; equal scores
+    across labels may be cut differently by keep_top_k (the CPU uses an unstable sort),
+    which the seeded inputs avoid."""
+    return rows
+
+
+@pytest.mark.parametrize("case", [
+    dict(batch=2, num_priors=500, num_classes=5, conf_thr=0.01, nms_thr=0.45, top_k=100, keep_top_k=50),
+    dict(batch=3, num_priors=2000, num_classes=21, conf_thr=0.01, nms_thr=0.45, top_k=400, keep_top_k=200),
+    dict(batch=1, num_priors=300, num_classes=3, conf_thr=0.3, nms_thr=0.6, top_k=400, keep_top_k=-1, peaked=True),
+    dict(batch=2, num_priors=400, num_classes=4, conf_thr=0.05, nms_thr=0.45, top_k=50, keep_top_k=20,
+         code_type="CORNER"),
+    dict(batch=2, num_priors=200, num_classes=4, conf_thr=0.05, nms_thr=0.45, top_k=50, keep_top_k=30,
+         share_location=False, peaked=True),
+])
+def test_detection_output_bit_exact(capi, gpu_engine, reflib, case):
+    wl = pkg("workloads")
+    case = dict(case)
+    peaked = case.pop("peaked", False)
+    b = detection_head_net(wl, **case)
+    inputs = detection_inputs(case["batch"], case["num_priors"], case["num_classes"], seed=21,
+                              share_location=case.get("share_location", True), peaked=peaked)
+    got = run_net(capi, gpu_engine, b, {}, inputs, ["detection_out"])["detection_out"]
+    want = run_net(capi, reflib, b, {}, inputs, ["detection_out"])["detection_out"]
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert got.shape[0] > 0
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_detection_output_no_detections(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = detection_head_net(wl, 2, 50, 3, conf_thr=2.0, nms_thr=0.45, top_k=10, keep_top_k=5)
+    inputs = detection_inputs(2, 50, 3, seed=3)
+    got = run_net(capi, gpu_engine, b, {}, inputs, ["detection_out"])["detection_out"]
+    want = run_net(capi, reflib, b, {}, inputs, ["detection_out"])["detection_out"]
+    assert got.shape == want.shape == (2, 7)
+    assert np.array_equal(got, want)
+
+
+def test_prior_box_values(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("priors")
+    b.input([("feat", (1, 8, 5, 7)), ("data", (1, 3, 300, 300))])
+    b.raw("pb", "PriorBox", ["feat", "data"], ["pb"],
+          "prior_box_param { min_size: 60 max_size: 111 aspect_ratio: 2 aspect_ratio: 3 flip: true clip: true "
+          "variance: 0.1 variance: 0.1 variance: 0.2 variance: 0.2 step: 16 offset: 0.5 }")
+    x = {"feat": np.zeros((1, 8, 5, 7), np.float32), "data": np.zeros((1, 3, 300, 300), np.float32)}
+    got = run_net(capi, gpu_engine, b, {}, x, ["pb"])["pb"]
+    want = run_net(capi, reflib, b, {}, x, ["pb"])["pb"]
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_ssd300_end_to_end(capi, gpu_engine, reflib):
+    """SSD300-VGG16, batch 1: the dense tensors within the TF32 contract; the
+    detections are compared as sets of (image, label) with scores within tolerance,
+    because a TF32-level change of a score or box can legitimately flip an NMS decision."""
+    wl = pkg("workloads")
+    b = wl.ssd300_vgg16(1)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.ssd_input(1, seed=0)
+    outs = ["mbox_loc", "mbox_conf_flatten", "mbox_priorbox", "detection_out"]
+    got = run_net(capi, gpu_engine, b, weights, x, outs, marks=outs[:3])
+    want = run_net(capi, reflib, b, weights, x, outs, marks=outs[:3])
+    assert np.array_equal(got["mbox_priorbox"].view(np.uint32), want["mbox_priorbox"].view(np.uint32))
+    assert_close(got["mbox_loc"], want["mbox_loc"], "mbox_loc")
+    assert_close(got["mbox_conf_flatten"], want["mbox_conf_flatten"], "mbox_conf")
+    assert got["detection_out"].shape[1] == 7
+    assert abs(got["detection_out"].shape[0] - want["detection_out"].shape[0]) <= 0.2 * want["detection_out"].shape[0] + 5
