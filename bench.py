@@ -1,0 +1,331 @@
+#!/usr/bin/env python3
+"""Headline benchmark: ResNet-50 forward, batch 64 per GPU, through libcaffe.so.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one Net::Forward over one batch of synthetic input (seeded
+U(0,255) minus the channel means; random He-normal weights, identity
+BatchNorm).  For N > 1 launch under torch.distributed.run: one process per
+GPU, each with a full weight replica and its own batch (weak scaling), no
+collective in the timed loop; only the final class scores are gathered, after
+timing.  Rank 0 prints one JSON line.
+
+  value      images/s with the input already resident in device memory
+             (CUDA events on the engine's stream, max over ranks)
+  e2e        images/s through the C API with the input in (pinned) host memory:
+             every step uploads the batch and downloads the class scores
+  roofline   the tensor-core convolution kernel, timed live with CUDA events
+             around every launch: algorithmic bytes / time against the measured
+             HBM copy bandwidth (the binding limit for fp32 activations; the
+             achieved TF32 rate is reported beside it)
+  cpu_baseline  mini-caffe's own CPU path (oracle/_ref, OpenBLAS threads = host
+             cores) on a bounded sample of the same workload
+
+--impl reference times that CPU path as the measured arm instead.
+"""
+import argparse
+import ctypes
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+ENGINE_LIB = os.path.join(ROOT, "mini-caffe_b200", "lib", "libcaffe.so")
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libcaffe_ref.so")
+BATCH_PER_GPU = 64
+METRIC = "resnet50_images_per_sec"
+UNIT = "images/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.stop_flag = threading.Event()
+        self.proc = None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.proc.stdout:
+            if self.stop_flag.is_set():
+                break
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                self.samples.append((float(parts[0]), float(parts[1])))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    self.reasons.add(name)
+
+    def finish(self):
+        self.stop_flag.set()
+        if self.proc is not None:
+            self.proc.terminate()   # the exact child started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        busy = [s for s, _ in self.samples]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(m for _, m in self.samples),
+                "reasons": sorted(self.reasons), "samples": len(busy)}
+
+
+def build_resnet(capi, wl, library, batch):
+    builder = wl.resnet50(batch)
+    net = capi.Net(library, builder.text(), None, from_buffer=True)
+    net.set_params(wl.init_params(builder.params, seed=0))
+    return net
+
+
+def cpu_reference_rate(capi, wl, steps, warmup, budget_s):
+    """images/s of the reference CPU build on a sample sized to fit `budget_s` seconds."""
+    if not os.path.isfile(REF_LIB):
+        return None
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OPENBLAS_NUM_THREADS", str(cores))
+    ref = capi.CaffeLibrary(REF_LIB)
+    probe_batch = 4
+    net = build_resnet(capi, wl, ref, probe_batch)
+    x = wl.image_input(probe_batch, seed=0)
+    net.forward(**x)
+    t0 = time.perf_counter()
+    net.forward()
+    probe_rate = probe_batch / (time.perf_counter() - t0)
+    net.close()
+    per_step = int(max(1, min(BATCH_PER_GPU, probe_rate * budget_s / max(1, steps + warmup))))
+    net = build_resnet(capi, wl, ref, per_step)
+    net.forward(**wl.image_input(per_step, seed=0))
+    for _ in range(max(0, warmup - 1)):
+        net.forward()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        net.forward()
+    dt = time.perf_counter() - t0
+    net.close()
+    return {"value": per_step * steps / dt, "unit": UNIT, "cores": cores, "kind": "reference",
+            "sample": "%d forward passes of ResNet-50 at batch %d (workload batch is %d) on %d OpenBLAS threads; only "
+                      "SGEMM is multi-threaded in the reference" % (steps, per_step, BATCH_PER_GPU, cores),
+            "ms_per_step": dt / steps * 1e3, "batch": per_step}
+
+
+def run_reference_arm(args, capi, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": "resnet50 forward, batch %d per GPU, 224x224" % BATCH_PER_GPU}}
+    res = cpu_reference_rate(capi, wl, args.steps, args.warmup, budget_s=150.0)
+    if res is None:
+        base["unavailable"] = "oracle/_ref/libcaffe_ref.so is not built (needs the reference checkout at build time)"
+        print(json.dumps(base))
+        return
+    base.update({"value": res["value"], "ms_per_step": res["ms_per_step"], "cpu_baseline": res, "gpu_launches": 0,
+                 "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    base["config"]["sample_batch"] = res["batch"]
+    print(json.dumps(base))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU,
+                    help="images per GPU (the headline metric is quoted at the default; smaller values are for "
+                         "profiler captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU reference leg (profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    capi = importlib.import_module("mini-caffe_b200.capi")
+    wl = importlib.import_module("mini-caffe_b200.workloads")
+    if args.impl == "reference":
+        run_reference_arm(args, capi, wl)
+        return
+
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE is %d: launch with torch.distributed.run" % (args.gpus, world))
+    if not torch.cuda.is_available():
+        raise SystemExit("no CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    engine = capi.CaffeLibrary(ENGINE_LIB)
+    L = engine.lib
+    L.mcb200_current_stream.restype = ctypes.c_void_p
+    L.mcb200_launch_count.restype = ctypes.c_longlong
+    L.mcb200_kernel_timing_end.restype = ctypes.c_longlong
+    L.mcb200_kernel_timing_end.argtypes = [ctypes.POINTER(ctypes.c_double)]
+    engine.set_mode(True, local_rank)
+    stream_ptr = L.mcb200_current_stream()
+    if not stream_ptr:
+        raise SystemExit("engine stream: " + L.CaffeGetLastError().decode())
+    stream = torch.cuda.ExternalStream(stream_ptr, device=torch.device("cuda", local_rank))
+
+    batch = args.batch
+    net = build_resnet(capi, wl, engine, batch)
+    x = wl.image_input(batch, seed=rank)["data"]
+    data_blob = net.blob("data")
+    data_blob.reshape(*x.shape)
+    data_blob.data[...] = x
+    prob_blob = net.blob("prob")
+
+    def forward():
+        engine.check(L.CaffeNetForward(net.handle))
+
+    # ---- device-resident throughput: the input blob's device copy stays valid ----
+    for _ in range(args.warmup):
+        forward()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    L.mcb200_launch_count_reset()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        forward()
+    ev1.record(stream)
+    barrier()
+    launches = int(L.mcb200_launch_count())
+    clocks = sampler.finish() if sampler else None
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_per_step = ms_total / args.steps
+    value = world * batch * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end: host input -> device, forward, scores -> host, every step ----
+    for _ in range(2):
+        data_blob.data  # marks the pinned host copy as the current one
+        forward()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        data_blob.data
+        forward()
+        prob_blob.data
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_value = world * batch * args.steps / e2e_s
+    h2d = int(np.prod(x.shape)) * 4
+    d2h = int(np.prod(prob_blob.shape)) * 4
+
+    # ---- the convolution kernel on its own clock ----
+    barrier()
+    L.mcb200_kernel_timing_begin()
+    timed_steps = min(args.steps, 10)
+    for _ in range(timed_steps):
+        forward()
+    conv_ms = ctypes.c_double(0.0)
+    conv_launches = int(L.mcb200_kernel_timing_end(ctypes.byref(conv_ms)))
+    peaks = load_peaks()
+    conv_bytes = wl.resnet50_conv_bytes(batch)          # per forward pass
+    conv_flops = wl.resnet50_flops_per_image() * batch
+    conv_s_per_step = conv_ms.value * 1e-3 / timed_steps
+    launches_per_step = conv_launches / timed_steps
+    achieved_gbs = conv_bytes / conv_s_per_step / 1e9
+    roofline = {
+        "kernel": "conv_tc_kernel (tcgen05 implicit GEMM, %d launches per forward)" % round(launches_per_step),
+        "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+        "algorithmic_bytes_per_launch": conv_bytes / launches_per_step,
+        "avg_launch_ms": conv_ms.value / max(1, conv_launches),
+        "tf32_tflops_achieved": conv_flops / conv_s_per_step / 1e12,
+        "tf32_peak_tflops_assumed": peaks["bf16_tflops"] / 2.0,
+        "share_of_step": conv_s_per_step * 1e3 / ms_per_step,
+    }
+
+    # ---- final output gather (outside the timed loops) ----
+    probs = torch.from_numpy(prob_blob.data.copy()).cuda()
+    if world > 1:
+        gathered = [torch.empty_like(probs) for _ in range(world)] if rank == 0 else None
+        dist.gather(probs, gathered, dst=0)
+        gathered_rows = sum(int(g.shape[0]) for g in gathered) if rank == 0 else 0
+    else:
+        gathered_rows = int(probs.shape[0])
+
+    if rank == 0:
+        cpu = None if args.no_cpu_baseline else cpu_reference_rate(capi, wl, steps=2, warmup=1, budget_s=20.0)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": "resnet50 forward (Caffe layout conv+BN+Scale+ReLU, Eltwise residuals), batch %d "
+                                   "per GPU, 3x224x224 fp32 input" % batch,
+                       "global_batch": world * batch, "parallelism": "replica per GPU, batch sharded, no collective",
+                       "l2": "activations of one pass (%.1f GB of convolution traffic) exceed the 126 MB L2"
+                             % (conv_bytes / 1e9),
+                       "flops_per_image": wl.resnet50_flops_per_image(), "gathered_output_rows": gathered_rows},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+            "cpu_baseline": cpu if cpu else {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                             "sample": "oracle/_ref not built"},
+        }
+        print(json.dumps(line))
+    net.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

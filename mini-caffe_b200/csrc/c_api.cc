@@ -9,7 +9,9 @@
 #include <vector>
 
 #include "caffe/caffe.hpp"
+#include "context.h"
 #include "io.h"
+#include "mcb200_runtime.h"
 
 namespace {
 
@@ -204,5 +206,22 @@ const char* CaffeGetLastError() { return Scratch().last_error.c_str(); }
 int CaffeMemoryPoolClear() {
   API_BEGIN();
   caffe::MemPoolClear();
+  API_END();
+}
+
+// ---- measurement helpers (include/mcb200_runtime.h) ----
+
+void* mcb200_current_stream(void) {
+  try {
+    return caffe::Context::Get().stream_ptr();
+  } catch (const std::exception& err) {
+    Fail(err);
+    return nullptr;
+  }
+}
+
+int mcb200_synchronize(void) {
+  API_BEGIN();
+  caffe::Context::Get().SyncAndCheck();
   API_END();
 }

@@ -28,6 +28,7 @@
 #include <mutex>
 
 #include "../../../include/mcb200_kernels.h"
+#include "kernel_timer.h"
 #include "launch_count.h"
 #include "sm100.cuh"
 
@@ -354,7 +355,10 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args,
   dim3 grid(static_cast<unsigned>(tiles), 1, 1);
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
-  conv_tc_kernel<BN, kIm2col><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, args);
+  {
+    TimedLaunch timed(stream);
+    conv_tc_kernel<BN, kIm2col><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, args);
+  }
   count_launch();
   return cudaGetLastError();
 }

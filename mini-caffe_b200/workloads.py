@@ -201,25 +201,41 @@ def image_input(batch, size=224, seed=0):
     return {"data": x.astype(np.float32)}
 
 
-def resnet50_flops_per_image():
-    """2 * MACs of every Convolution and the InnerProduct of resnet50()."""
-    total = 0
-    h = 112
-    total += 2 * 64 * h * h * 3 * 49
-    h = 56
-    cin = 64
+def resnet50_conv_table():
+    """One row per Convolution / InnerProduct of resnet50():
+    (name, cin, cout, kernel, stride, in_size, out_size, fused_residual)."""
+    rows = [("conv1", 3, 64, 7, 2, 224, 112, False)]
+    h, cin = 56, 64
     for stage, blocks, width in [(2, 3, 64), (3, 4, 128), (4, 6, 256), (5, 3, 512)]:
         for i in range(blocks):
+            tag = "%d%s" % (stage, "abcdefgh"[i])
             stride = 2 if (i == 0 and stage > 2) else 1
             ho = h // stride
             cout = width * 4
             if i == 0:
-                total += 2 * cout * ho * ho * cin
-            total += 2 * width * ho * ho * cin
-            total += 2 * width * ho * ho * width * 9
-            total += 2 * cout * ho * ho * width
+                rows.append(("res%s_branch1" % tag, cin, cout, 1, stride, h, ho, False))
+            rows.append(("res%s_branch2a" % tag, cin, width, 1, stride, h, ho, False))
+            rows.append(("res%s_branch2b" % tag, width, width, 3, 1, ho, ho, False))
+            rows.append(("res%s_branch2c" % tag, width, cout, 1, 1, ho, ho, True))
             h, cin = ho, cout
-    total += 2 * 1000 * cin
+    rows.append(("fc1000", cin, 1000, 1, 1, 1, 1, False))
+    return rows
+
+
+def resnet50_flops_per_image():
+    """2 * MACs of every Convolution and the InnerProduct of resnet50()."""
+    return sum(2 * cout * ho * ho * cin * k * k for _, cin, cout, k, _, _, ho, _ in resnet50_conv_table())
+
+
+def resnet50_conv_bytes(batch):
+    """Algorithmic bytes of the convolution / inner-product kernels of one forward pass:
+    4 * (input + output + weights + per-channel terms [+ residual input when fused]), each
+    tensor counted once per layer."""
+    total = 0
+    for _, cin, cout, k, _, hi, ho, res in resnet50_conv_table():
+        total += 4 * (batch * cin * hi * hi + batch * cout * ho * ho + cout * cin * k * k + cout)
+        if res:
+            total += 4 * batch * cout * ho * ho
     return total
 
 
