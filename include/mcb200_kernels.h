@@ -80,9 +80,13 @@ int mcb200_conv_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, fl
 typedef struct mcb200_conv_plan {
   uint64_t tma_a[16];
   uint64_t tma_b[16];
+  uint64_t tma_out[16];     /* output / residual tile maps, built on first launch  */
+  uint64_t tma_res[16];     /* and rebuilt when the pointers below change          */
   mcb200_conv_shape shape;
   int m, k_iters, c_blocks, block_n, im2col;
-  int reserved[3];
+  int out_ld, res_ld, reserved;
+  const float* out_ptr;
+  const float* res_ptr;
 } __attribute__((aligned(64))) mcb200_conv_plan;
 
 /* Implicit-GEMM convolution on the tensor cores (tcgen05.mma kind::tf32,
@@ -94,7 +98,9 @@ typedef struct mcb200_conv_plan {
  * (src/layers/inner_product_layer.cpp:80-93).                                */
 int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float* packed_w,
                         mcb200_conv_plan* plan);
-int mcb200_conv_tc_launch(const mcb200_conv_plan* plan, float* out, int out_ld,
+/* The plan is updated in place when `out` / the residual pointer differ from
+ * the previous launch (their tile maps are cached in it).                     */
+int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld,
                           const mcb200_epilogue* ep, int* status, void* stream);
 
 /* Direct convolution, one thread per output element, any group count; the

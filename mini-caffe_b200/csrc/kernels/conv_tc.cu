@@ -15,7 +15,11 @@
 //            shared-memory stage back to the producer.
 //   warps 2-5 read the accumulator out of tensor memory (tcgen05.ld), apply
 //            the fused tail (per-channel scale/shift, residual add, ReLU or
-//            PReLU) and store channels-last.
+//            PReLU) and store channels-last.  Each warp stages its 32 x 32
+//            sub-tiles in shared memory (128-byte swizzled, reusing the
+//            pipeline stages once the last MMA has retired) so that the
+//            residual comes in and the result goes out as whole 128-byte rows
+//            through TMA tile loads / stores, double buffered per warp.
 // Every barrier wait is bounded; a timed-out wait raises an abort flag, the
 // roles drain, tensor memory is freed and *status is set.
 //
@@ -55,6 +59,7 @@ struct ConvTcArgs {
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   mcb200_epilogue ep;
   int* status;
+  int tma_epilogue;  // output (and residual) meet the 16-byte rules of TMA tiles
 };
 
 template <int BN>
@@ -74,6 +79,7 @@ __device__ __forceinline__ float apply_act(float v, int act, float slope) {
 template <int BN, bool kIm2col>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
                const ConvTcArgs args) {
   using Plan = SmemPlan<BN>;
   constexpr int kStages = Plan::kStages;
@@ -82,6 +88,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ uint64_t full_bar[kStages];
   __shared__ uint64_t empty_bar[kStages];
   __shared__ uint64_t accum_bar;
+  __shared__ uint64_t res_bar[4][2];   // per epilogue warp, per staging buffer
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -106,6 +113,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&accum_bar, 1);
+    for (int w = 0; w < 4; ++w) {
+      mbar_init(&res_bar[w][0], 1);
+      mbar_init(&res_bar[w][1], 1);
+    }
     fence_barrier_init();
     tma_prefetch_descriptor(&map_a);
     tma_prefetch_descriptor(&map_b);
@@ -195,7 +206,89 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // tcgen05.ld is warp-collective: the whole warp takes the same branch.
     const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(&accum_bar, 0, abort, kWaitLimitCycles));
     tc_fence_after_sync();
-    if (ok) {
+    if (ok && args.tma_epilogue) {
+      // ---- staged path: TMA in (residual), TMA out ----
+      const mcb200_epilogue& ep = args.ep;
+      const int row0 = m0 + quad * 32;
+      uint8_t* staging = tiles + quad * 16384;           // 4 x 4 KiB, 1024-byte aligned
+      auto res_buf = [&](int b) { return reinterpret_cast<float*>(staging + b * 4096); };
+      auto out_buf = [&](int b) { return reinterpret_cast<float*>(staging + 8192 + b * 4096); };
+      const bool has_res = ep.residual != nullptr;
+      int chunks = (args.cout - n0 + 31) / 32;
+      if (chunks > BN / 32) chunks = BN / 32;
+      bool alive = true;
+      if (has_res && lane == 0 && chunks > 0) {
+        mbar_expect_tx(&res_bar[quad][0], 4096);
+        tma_load_2d(&map_res, &res_bar[quad][0], res_buf(0), n0, row0);
+      }
+#pragma unroll 1
+      for (int chunk = 0; chunk < chunks && alive; ++chunk) {
+        const int buf = chunk & 1;
+        const int col0 = n0 + chunk * 32;
+        __syncwarp();   // every lane is done with the buffers of chunk - 1
+        if (has_res && lane == 0 && chunk + 1 < chunks) {
+          mbar_expect_tx(&res_bar[quad][buf ^ 1], 4096);
+          tma_load_2d(&map_res, &res_bar[quad][buf ^ 1], res_buf(buf ^ 1), col0 + 32, row0);
+        }
+        uint32_t acc[32];
+        tmem_load_32x32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chunk * 32),
+                        acc);
+        tmem_load_wait();
+        if (has_res) {
+          alive = __all_sync(0xffffffffu, mbar_wait_bounded(&res_bar[quad][buf], static_cast<uint32_t>(chunk >> 1) & 1u,
+                                                            abort, kWaitLimitCycles));
+          if (!alive) break;
+        }
+        if (chunk >= 2) {
+          // The store issued two chunks ago must have finished reading out_buf[buf].
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
+        // piece j stored at position j ^ (row & 7) (the 128-byte swizzle).
+        const float* res_row = res_buf(buf) + lane * 32;
+        float* out_row = out_buf(buf) + lane * 32;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int piece = (j ^ (lane & 7)) * 4;
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = col0 + j * 4 + e;
+            float x = __uint_as_float(acc[j * 4 + e]);
+            if (c < args.cout) {
+              if (ep.scale) x *= __ldg(ep.scale + c);
+              if (ep.shift) x += __ldg(ep.shift + c);
+            }
+            v[e] = x;
+          }
+          if (has_res) {
+            const float4 rr = *reinterpret_cast<const float4*>(res_row + piece);
+            v[0] += ep.residual_coeff * rr.x;
+            v[1] += ep.residual_coeff * rr.y;
+            v[2] += ep.residual_coeff * rr.z;
+            v[3] += ep.residual_coeff * rr.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = col0 + j * 4 + e;
+            float slope = ep.slope;
+            if (ep.act == 2 && c < args.cout) slope = __ldg(ep.prelu + (ep.prelu_shared ? 0 : c));
+            v[e] = apply_act(v[e], ep.act, slope);
+            if (ep.round_tf32) v[e] = round_to_tf32(v[e]);
+          }
+          *reinterpret_cast<float4*>(out_row + piece) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&map_out, out_buf(buf), col0, row0);
+          tma_store_commit();
+        }
+      }
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+    } else if (ok) {
       const mcb200_epilogue& ep = args.ep;
       float* out_row = args.out + static_cast<size_t>(row) * args.out_ld;
       const float* res_row =
@@ -332,6 +425,19 @@ int pick_block_n(int cout) {
   return 256;
 }
 
+// Tile map over a row-major [rows, cols] fp32 matrix with row pitch `ld`,
+// 32 x 32 boxes, 128-byte swizzle: what the staged epilogue stores / loads.
+CUresult encode_tile_map(CUtensorMap* map, const float* base, int rows, int cols, int ld) {
+  const DriverApi& api = driver_api();
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return api.tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
 template <int BN, bool kIm2col>
 cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args, cudaStream_t stream) {
   using Plan = SmemPlan<BN>;
@@ -355,9 +461,11 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args,
   dim3 grid(static_cast<unsigned>(tiles), 1, 1);
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
+  const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);
+  const CUtensorMap* mr = reinterpret_cast<const CUtensorMap*>(plan->tma_res);
   {
     TimedLaunch timed(stream);
-    conv_tc_kernel<BN, kIm2col><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, args);
+    conv_tc_kernel<BN, kIm2col><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, *mo, *mr, args);
   }
   count_launch();
   return cudaGetLastError();
@@ -409,6 +517,9 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   if (!api.ok) return -5;
 
   plan->shape = *s;
+  plan->out_ptr = nullptr;
+  plan->res_ptr = nullptr;
+  plan->out_ld = plan->res_ld = plan->reserved = 0;
   if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
@@ -468,7 +579,7 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   return 0;
 }
 
-extern "C" int mcb200_conv_tc_launch(const mcb200_conv_plan* plan, float* out, int out_ld, const mcb200_epilogue* ep,
+extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld, const mcb200_epilogue* ep,
                                      int* status, void* stream) {
   if (!plan || !out || out_ld < plan->shape.cout) return -1;
   ConvTcArgs a;
@@ -495,6 +606,27 @@ extern "C" int mcb200_conv_tc_launch(const mcb200_conv_plan* plan, float* out, i
   }
   if (a.ep.act == 2 && !a.ep.prelu) return -2;
   a.status = status;
+  // The staged epilogue needs 16-byte aligned rows; otherwise plain stores are used.
+  const bool out_ok = (out_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  const bool res_ok = !a.ep.residual || ((a.ep.residual_ld % 4 == 0) && a.ep.residual_ld >= plan->shape.cout &&
+                                         ((reinterpret_cast<uintptr_t>(a.ep.residual) & 15) == 0));
+  a.tma_epilogue = (out_ok && res_ok) ? 1 : 0;
+  if (a.tma_epilogue) {
+    if (plan->out_ptr != out || plan->out_ld != out_ld) {
+      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_out), out, plan->m, plan->shape.cout, out_ld) !=
+          CUDA_SUCCESS)
+        return -4;
+      plan->out_ptr = out;
+      plan->out_ld = out_ld;
+    }
+    if (a.ep.residual && (plan->res_ptr != a.ep.residual || plan->res_ld != a.ep.residual_ld)) {
+      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_res), a.ep.residual, plan->m, plan->shape.cout,
+                          a.ep.residual_ld) != CUDA_SUCCESS)
+        return -5;
+      plan->res_ptr = a.ep.residual;
+      plan->res_ld = a.ep.residual_ld;
+    }
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   const bool im = plan->im2col != 0;

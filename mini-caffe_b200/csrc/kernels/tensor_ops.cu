@@ -53,6 +53,25 @@ __global__ void nchw_to_nhwc_kernel(const float* __restrict__ src, float* __rest
   }
 }
 
+// Up to four channels padded to four (e.g. colour planes in front of the first
+// convolution): one thread per pixel, one coalesced read per plane, one
+// 16-byte write.
+__global__ void nchw_to_nhwc4_kernel(const float* __restrict__ src, float4* __restrict__ dst, int c, int hw,
+                                     long long pixels) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pixels;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long n = i / hw;
+    const int p = static_cast<int>(i - n * hw);
+    const float* s = src + n * c * hw + p;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    v.x = s[0];
+    if (c > 1) v.y = s[hw];
+    if (c > 2) v.z = s[2 * static_cast<size_t>(hw)];
+    if (c > 3) v.w = s[3 * static_cast<size_t>(hw)];
+    dst[i] = v;
+  }
+}
+
 __global__ void nhwc_to_nchw_kernel(const float* __restrict__ src, float* __restrict__ dst, int c, int hw,
                                     int c_stride) {
   __shared__ float tile[32][33];
@@ -362,6 +381,13 @@ extern "C" int mcb200_nchw_to_nhwc(const float* src, float* dst, int n, int c, i
   if (!src || !dst || n < 0 || c < 1 || h < 1 || w < 1 || c_stride < c) return -1;
   if (n == 0) return 0;
   const int hw = h * w;
+  if (c <= 4 && c_stride == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    const long long pixels = static_cast<long long>(n) * hw;
+    nchw_to_nhwc4_kernel<<<grid_for(pixels, 256), 256, 0, as_stream(stream)>>>(src, reinterpret_cast<float4*>(dst), c,
+                                                                            hw, pixels);
+    count_launch();
+    return static_cast<int>(cudaGetLastError());
+  }
   dim3 grid((hw + 31) / 32, (c_stride + 31) / 32, n);
   if (grid.y > 65535 || grid.z > 65535) return -2;
   nchw_to_nhwc_kernel<<<grid, dim3(32, 8), 0, as_stream(stream)>>>(src, dst, c, hw, c_stride);

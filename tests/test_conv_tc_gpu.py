@@ -29,9 +29,12 @@ class Epilogue(ctypes.Structure):
 
 
 class ConvPlan(ctypes.Structure):
-    _fields_ = [("tma_a", ctypes.c_uint64 * 16), ("tma_b", ctypes.c_uint64 * 16), ("shape", ConvShape),
+    _fields_ = [("tma_a", ctypes.c_uint64 * 16), ("tma_b", ctypes.c_uint64 * 16),
+                ("tma_out", ctypes.c_uint64 * 16), ("tma_res", ctypes.c_uint64 * 16), ("shape", ConvShape),
                 ("m", ctypes.c_int), ("k_iters", ctypes.c_int), ("c_blocks", ctypes.c_int),
-                ("block_n", ctypes.c_int), ("im2col", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
+                ("block_n", ctypes.c_int), ("im2col", ctypes.c_int), ("out_ld", ctypes.c_int),
+                ("res_ld", ctypes.c_int), ("reserved", ctypes.c_int), ("out_ptr", ctypes.c_void_p),
+                ("res_ptr", ctypes.c_void_p)]
 
 
 def aligned_plan():
