@@ -66,9 +66,12 @@ template <int BN>
 struct SmemPlan {
   static constexpr int kTileBBytes = BN * kBlockK * 4;
   static constexpr int kStageBytes = kTileABytes + kTileBBytes;
-  // Two CTAs per SM: stay below ~110 KiB each.
-  static constexpr int kStages = (BN == 256) ? 2 : (BN == 128 ? 3 : 4);
-  static constexpr int kDynamicBytes = kStages * kStageBytes + 1024;  // + alignment slack
+  // One persistent CTA per SM.  Shared memory = operand ring + per-warp
+  // epilogue staging ring (kResSlots x 4 KiB for each of the four warps).
+  static constexpr int kStages = (BN == 256) ? 3 : (BN == 128 ? 4 : 6);
+  static constexpr int kResSlots = (BN == 128) ? 5 : 4;
+  static constexpr int kStagingBytes = 4 * kResSlots * 4096;
+  static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ float apply_act(float v, int act, float slope) {
@@ -76,6 +79,11 @@ __device__ __forceinline__ float apply_act(float v, int act, float slope) {
   return v;
 }
 
+// Persistent kernel: CTA b works on tiles b, b + gridDim.x, ... (n fastest, so
+// the CTAs running at one time share activation tiles through L2).  Two
+// accumulators in tensor memory let the tensor core start the next tile while
+// the epilogue warps drain the previous one; the TMA producer runs ahead across
+// tile boundaries.
 template <int BN, bool kIm2col>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -83,28 +91,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const ConvTcArgs args) {
   using Plan = SmemPlan<BN>;
   constexpr int kStages = Plan::kStages;
+  constexpr int kResSlots = Plan::kResSlots;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[kStages];
   __shared__ uint64_t empty_bar[kStages];
-  __shared__ uint64_t accum_bar;
-  __shared__ uint64_t res_bar[4][2];   // per epilogue warp, per staging buffer
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
+  __shared__ uint64_t res_bar[4][kResSlots];   // per epilogue warp, per staging slot
+  __shared__ uint64_t col_bar[2];              // per-column table of a tile is complete
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) float col_scale[2][BN];   // per-column constants of the current tiles
+  __shared__ __align__(16) float col_shift[2][BN];
+  __shared__ __align__(16) float col_slope[2][BN];
 
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
   const uint32_t raw_addr = smem_addr(smem_raw);
   uint8_t* tiles = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* staging_base = tiles + kStages * Plan::kStageBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // Tiles that share an activation tile (same m, different n) get adjacent
-  // block ids so they run together and the tile is fetched from HBM once.
   const int n_tiles = (args.cout + BN - 1) / BN;
-  const int n_tile = blockIdx.x % n_tiles;
-  const int m_tile = blockIdx.x / n_tiles;
-  const int m0 = m_tile * kBlockM;
-  const int n0 = n_tile * BN;
+  const int m_tiles = (args.m + kBlockM - 1) / kBlockM;
+  const int num_tiles = n_tiles * m_tiles;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -112,64 +123,70 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&accum_bar, 1);
-    for (int w = 0; w < 4; ++w) {
-      mbar_init(&res_bar[w][0], 1);
-      mbar_init(&res_bar[w][1], 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 4);   // one arrival per epilogue warp
+      mbar_init(&col_bar[b], 4);
     }
+    for (int w = 0; w < 4; ++w)
+      for (int r = 0; r < kResSlots; ++r) mbar_init(&res_bar[w][r], 1);
     fence_barrier_init();
     tma_prefetch_descriptor(&map_a);
     tma_prefetch_descriptor(&map_b);
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_base_slot, BN);
+    tmem_alloc(&tmem_base_slot, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_acc = tmem_base_slot;
+  const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort = &abort_flag;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      int base_w = 0, base_h = 0, base_n = 0;
-      if (kIm2col) {
-        const int q = m0 % args.wo;
-        const int p = (m0 / args.wo) % args.ho;
-        base_n = m0 / (args.wo * args.ho);
-        base_w = q * args.stride_w - args.pad_w;
-        base_h = p * args.stride_h - args.pad_h;
-      }
-      int issued = 0;
-      for (int it = 0; it < args.k_iters; ++it) {
-        const int s = it % kStages;
-        const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
-        if (!mbar_wait_bounded(&empty_bar[s], phase ^ 1u, abort, kWaitLimitCycles)) break;
-        uint8_t* a_dst = tiles + s * Plan::kStageBytes;
-        uint8_t* b_dst = a_dst + kTileABytes;
-        mbar_expect_tx(&full_bar[s], Plan::kStageBytes);
-        const int tap = it / args.c_blocks;
-        const int cb = it - tap * args.c_blocks;
+      int it = 0;   // k-iterations issued so far, over all tiles of this CTA
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * kBlockM;
+        const int n0 = (tile % n_tiles) * BN;
+        int base_w = 0, base_h = 0, base_n = 0;
         if (kIm2col) {
-          const int r = tap / args.kw;
-          const int sx = tap - r * args.kw;
-          tma_load_im2col_4d(&map_a, &full_bar[s], a_dst, cb * kBlockK, base_w, base_h, base_n,
-                             static_cast<uint16_t>(sx * args.dil_w), static_cast<uint16_t>(r * args.dil_h));
-        } else {
-          tma_load_2d(&map_a, &full_bar[s], a_dst, cb * kBlockK, m0);
+          const int q = m0 % args.wo;
+          const int p = (m0 / args.wo) % args.ho;
+          base_n = m0 / (args.wo * args.ho);
+          base_w = q * args.stride_w - args.pad_w;
+          base_h = p * args.stride_h - args.pad_h;
         }
-        tma_load_2d(&map_b, &full_bar[s], b_dst, it * kBlockK, n0);
-        issued = it + 1;
+        for (int k = 0; k < args.k_iters; ++k, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
+          if (!mbar_wait_bounded(&empty_bar[s], phase ^ 1u, abort, kWaitLimitCycles)) { alive = false; break; }
+          uint8_t* a_dst = tiles + s * Plan::kStageBytes;
+          uint8_t* b_dst = a_dst + kTileABytes;
+          mbar_expect_tx(&full_bar[s], Plan::kStageBytes);
+          const int tap = k / args.c_blocks;
+          const int cb = k - tap * args.c_blocks;
+          if (kIm2col) {
+            const int r = tap / args.kw;
+            const int sx = tap - r * args.kw;
+            tma_load_im2col_4d(&map_a, &full_bar[s], a_dst, cb * kBlockK, base_w, base_h, base_n,
+                               static_cast<uint16_t>(sx * args.dil_w), static_cast<uint16_t>(r * args.dil_h));
+          } else {
+            tma_load_2d(&map_a, &full_bar[s], a_dst, cb * kBlockK, m0);
+          }
+          tma_load_2d(&map_b, &full_bar[s], b_dst, k * kBlockK, n0);
+        }
       }
       if (*abort) {
         // Give copies that are still in flight a bounded time to land before
         // the CTA's shared memory is released.
-        const int first = issued > kStages ? issued - kStages : 0;
-        for (int it = first; it < issued; ++it) {
+        const int first = it > kStages ? it - kStages : 0;
+        for (int j = first; j < it; ++j) {
           const long long start = clock64();
-          while (!mbar_try_wait(&full_bar[it % kStages], static_cast<uint32_t>(it / kStages) & 1u)) {
+          while (!mbar_try_wait(&full_bar[j % kStages], static_cast<uint32_t>(j / kStages) & 1u)) {
             if (clock64() - start > kWaitLimitCycles / 8) break;
           }
         }
@@ -179,180 +196,227 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_tf32(kBlockM, BN);
-      bool ok = true;
-      for (int it = 0; it < args.k_iters; ++it) {
-        const int s = it % kStages;
-        const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
-        if (!mbar_wait_bounded(&full_bar[s], phase, abort, kWaitLimitCycles)) { ok = false; break; }
+      int it = 0;
+      int local = 0;   // tiles done by this CTA
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+        const int ab = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
+        // The epilogue must have drained this accumulator (first use passes).
+        if (!mbar_wait_bounded(&tmem_empty_bar[ab], use ^ 1u, abort, kWaitLimitCycles)) break;
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_addr(tiles + s * Plan::kStageBytes);
-        const uint32_t b_addr = a_addr + kTileABytes;
-        const uint64_t desc_a = umma_desc_k_sw128(a_addr);
-        const uint64_t desc_b = umma_desc_k_sw128(b_addr);
+        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN);
+        for (int k = 0; k < args.k_iters; ++k, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
+          if (!mbar_wait_bounded(&full_bar[s], phase, abort, kWaitLimitCycles)) { alive = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_addr(tiles + s * Plan::kStageBytes);
+          const uint32_t b_addr = a_addr + kTileABytes;
+          const uint64_t desc_a = umma_desc_k_sw128(a_addr);
+          const uint64_t desc_b = umma_desc_k_sw128(b_addr);
 #pragma unroll
-        for (int k = 0; k < kBlockK / 8; ++k) {
-          // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
-          // descriptor's 16-byte address units.
-          umma_tf32(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBlockK / 8; ++kk) {
+            // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
+            // descriptor's 16-byte address units.
+            umma_tf32(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
         }
-        umma_commit(&empty_bar[s]);
+        if (alive) umma_commit(&tmem_full_bar[ab]);
       }
-      if (ok) umma_commit(&accum_bar);
     }
   } else {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;                  // tensor-memory lanes [32*quad, 32*quad+32)
-    const int row = m0 + quad * 32 + lane;
-    // tcgen05.ld is warp-collective: the whole warp takes the same branch.
-    const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(&accum_bar, 0, abort, kWaitLimitCycles));
-    tc_fence_after_sync();
-    if (ok && args.tma_epilogue) {
-      // ---- staged path: TMA in (residual), TMA out ----
-      const mcb200_epilogue& ep = args.ep;
+    const mcb200_epilogue& ep = args.ep;
+    const bool has_res = ep.residual != nullptr;
+    uint8_t* staging = staging_base + quad * (kResSlots * 4096);
+    auto slot_ptr = [&](int slot) { return reinterpret_cast<float*>(staging + slot * 4096); };
+    const int chunks_full = BN / 32;
+    const int epi_tid = threadIdx.x - 64;       // 0..127 over the four epilogue warps
+    // 0: no activation, 1: plain ReLU, 2: per-column negative slope (leaky ReLU / PReLU)
+    const int act_mode = ep.act == 0 ? 0 : ((ep.act == 1 && ep.slope == 0.f) ? 1 : 2);
+
+    // Chunk sequence of this warp: for each of its CTA's tiles, the 32-column
+    // chunks that exist (the last n-tile may have fewer), left to right.  `seq`
+    // numbers them; chunk seq uses staging slot seq % kResSlots.  The residual
+    // prefetch cursor (lane 0 only) walks the same sequence kResSlots - 1 ahead.
+    int pre_local = 0, pre_chunk = 0, pre_seq = 0;
+    auto issue_residual = [&]() {
+      const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(pre_local) * gridDim.x;
+      if (tile >= num_tiles) return;
+      const int row0 = static_cast<int>(tile / n_tiles) * kBlockM + quad * 32;
+      const int tile_n0 = static_cast<int>(tile % n_tiles) * BN;
+      const int slot = pre_seq % kResSlots;
+      mbar_expect_tx(&res_bar[quad][slot], 4096);
+      tma_load_2d(&map_res, &res_bar[quad][slot], slot_ptr(slot), tile_n0 + pre_chunk * 32, row0);
+      ++pre_seq;
+      ++pre_chunk;
+      if (pre_chunk >= chunks_full || tile_n0 + pre_chunk * 32 >= args.cout) {
+        pre_chunk = 0;
+        ++pre_local;
+      }
+    };
+    const bool staged = args.tma_epilogue != 0;
+    if (staged && has_res && lane == 0) {
+      for (int i = 0; i < kResSlots - 1; ++i) issue_residual();
+    }
+
+    int seq = 0;
+    int local = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+      const int ab = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
+      const int m0 = (tile / n_tiles) * kBlockM;
+      const int n0 = (tile % n_tiles) * BN;
       const int row0 = m0 + quad * 32;
-      uint8_t* staging = tiles + quad * 16384;           // 4 x 4 KiB, 1024-byte aligned
-      auto res_buf = [&](int b) { return reinterpret_cast<float*>(staging + b * 4096); };
-      auto out_buf = [&](int b) { return reinterpret_cast<float*>(staging + 8192 + b * 4096); };
-      const bool has_res = ep.residual != nullptr;
-      int chunks = (args.cout - n0 + 31) / 32;
-      if (chunks > BN / 32) chunks = BN / 32;
-      bool alive = true;
-      if (has_res && lane == 0 && chunks > 0) {
-        mbar_expect_tx(&res_bar[quad][0], 4096);
-        tma_load_2d(&map_res, &res_bar[quad][0], res_buf(0), n0, row0);
+      // Per-column constants of this tile go to shared memory once, so that the
+      // inner loops are a broadcast 16-byte load and fused multiply-adds.  Two
+      // copies (tile parity): a warp may still be reading the previous tile's.
+      float* t_scale = col_scale[ab];
+      float* t_shift = col_shift[ab];
+      float* t_slope = col_slope[ab];
+      for (int c = epi_tid; c < BN; c += 128) {
+        const int cc = n0 + c;
+        const bool in = cc < args.cout;
+        t_scale[c] = (in && ep.scale) ? __ldg(ep.scale + cc) : 1.f;
+        t_shift[c] = (in && ep.shift) ? __ldg(ep.shift + cc) : 0.f;
+        t_slope[c] = ep.act == 2 ? ((in && ep.prelu) ? __ldg(ep.prelu + (ep.prelu_shared ? 0 : cc)) : 0.f) : ep.slope;
       }
-#pragma unroll 1
-      for (int chunk = 0; chunk < chunks && alive; ++chunk) {
-        const int buf = chunk & 1;
-        const int col0 = n0 + chunk * 32;
-        __syncwarp();   // every lane is done with the buffers of chunk - 1
-        if (has_res && lane == 0 && chunk + 1 < chunks) {
-          mbar_expect_tx(&res_bar[quad][buf ^ 1], 4096);
-          tma_load_2d(&map_res, &res_bar[quad][buf ^ 1], res_buf(buf ^ 1), col0 + 32, row0);
-        }
-        uint32_t acc[32];
-        tmem_load_32x32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chunk * 32),
-                        acc);
-        tmem_load_wait();
-        if (has_res) {
-          alive = __all_sync(0xffffffffu, mbar_wait_bounded(&res_bar[quad][buf], static_cast<uint32_t>(chunk >> 1) & 1u,
-                                                            abort, kWaitLimitCycles));
-          if (!alive) break;
-        }
-        if (chunk >= 2) {
-          // The store issued two chunks ago must have finished reading out_buf[buf].
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-        }
-        // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
-        // piece j stored at position j ^ (row & 7) (the 128-byte swizzle).
-        const float* res_row = res_buf(buf) + lane * 32;
-        float* out_row = out_buf(buf) + lane * 32;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int piece = (j ^ (lane & 7)) * 4;
-          float v[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = col0 + j * 4 + e;
-            float x = __uint_as_float(acc[j * 4 + e]);
-            if (c < args.cout) {
-              if (ep.scale) x *= __ldg(ep.scale + c);
-              if (ep.shift) x += __ldg(ep.shift + c);
-            }
-            v[e] = x;
-          }
-          if (has_res) {
-            const float4 rr = *reinterpret_cast<const float4*>(res_row + piece);
-            v[0] += ep.residual_coeff * rr.x;
-            v[1] += ep.residual_coeff * rr.y;
-            v[2] += ep.residual_coeff * rr.z;
-            v[3] += ep.residual_coeff * rr.w;
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = col0 + j * 4 + e;
-            float slope = ep.slope;
-            if (ep.act == 2 && c < args.cout) slope = __ldg(ep.prelu + (ep.prelu_shared ? 0 : c));
-            v[e] = apply_act(v[e], ep.act, slope);
-            if (ep.round_tf32) v[e] = round_to_tf32(v[e]);
-          }
-          *reinterpret_cast<float4*>(out_row + piece) = make_float4(v[0], v[1], v[2], v[3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&map_out, out_buf(buf), col0, row0);
-          tma_store_commit();
-        }
-      }
-      if (lane == 0) tma_store_wait_read<0>();
+      // Rendezvous of the four epilogue warps on the table (an mbarrier rather
+      // than a named barrier, so that the wait is bounded like every other one).
       __syncwarp();
-    } else if (ok) {
-      const mcb200_epilogue& ep = args.ep;
-      float* out_row = args.out + static_cast<size_t>(row) * args.out_ld;
-      const float* res_row =
-          ep.residual ? ep.residual + static_cast<size_t>(row) * ep.residual_ld : nullptr;
-      const bool row_ok = row < args.m;
-      const bool vec_ok = ((args.out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0) &&
-                          (!ep.residual || (((ep.residual_ld & 3) == 0) &&
-                                            ((reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0)));
+      if (lane == 0) mbar_arrive(&col_bar[ab]);
+      alive = __all_sync(0xffffffffu, mbar_wait_bounded(&col_bar[ab], use, abort, kWaitLimitCycles));
+      if (!alive) break;
+
+      // tcgen05.ld is warp-collective: the whole warp takes the same branch.
+      alive = __all_sync(0xffffffffu, mbar_wait_bounded(&tmem_full_bar[ab], use, abort, kWaitLimitCycles));
+      if (!alive) break;
+      tc_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN) + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+      for (int chunk = 0; chunk < chunks_full; ++chunk) {
         const int col0 = n0 + chunk * 32;
         if (col0 >= args.cout) break;          // uniform across the warp
+        const int g = seq++;
         uint32_t acc[32];
-        tmem_load_32x32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chunk * 32),
-                        acc);
+        tmem_load_32x32(tmem_acc + static_cast<uint32_t>(chunk * 32), acc);
         tmem_load_wait();
-        if (!row_ok) continue;
+        const float4* sc4 = reinterpret_cast<const float4*>(t_scale + chunk * 32);
+        const float4* sh4 = reinterpret_cast<const float4*>(t_shift + chunk * 32);
+        const float4* sl4 = reinterpret_cast<const float4*>(t_slope + chunk * 32);
+        // v = acc * scale + shift (+ coeff * residual), then the activation.
+        auto finish4 = [&](int j, float4 r, bool add_res) {
+          const float4 sc = sc4[j], sh = sh4[j];
+          float4 v;
+          v.x = fmaf(__uint_as_float(acc[j * 4 + 0]), sc.x, sh.x);
+          v.y = fmaf(__uint_as_float(acc[j * 4 + 1]), sc.y, sh.y);
+          v.z = fmaf(__uint_as_float(acc[j * 4 + 2]), sc.z, sh.z);
+          v.w = fmaf(__uint_as_float(acc[j * 4 + 3]), sc.w, sh.w);
+          if (add_res) {
+            v.x = fmaf(ep.residual_coeff, r.x, v.x);
+            v.y = fmaf(ep.residual_coeff, r.y, v.y);
+            v.z = fmaf(ep.residual_coeff, r.z, v.z);
+            v.w = fmaf(ep.residual_coeff, r.w, v.w);
+          }
+          if (act_mode == 1) {
+            v.x = fmaxf(v.x, 0.f);
+            v.y = fmaxf(v.y, 0.f);
+            v.z = fmaxf(v.z, 0.f);
+            v.w = fmaxf(v.w, 0.f);
+          } else if (act_mode == 2) {
+            const float4 sl = sl4[j];
+            v.x = v.x > 0.f ? v.x : v.x * sl.x;
+            v.y = v.y > 0.f ? v.y : v.y * sl.y;
+            v.z = v.z > 0.f ? v.z : v.z * sl.z;
+            v.w = v.w > 0.f ? v.w : v.w * sl.w;
+          }
+          if (ep.round_tf32) {
+            v.x = round_to_tf32(v.x);
+            v.y = round_to_tf32(v.y);
+            v.z = round_to_tf32(v.z);
+            v.w = round_to_tf32(v.w);
+          }
+          return v;
+        };
+        if (staged) {
+          const int slot = g % kResSlots;
+          float* buf = slot_ptr(slot) + lane * 32;
+          if (has_res) {
+            alive = __all_sync(0xffffffffu,
+                               mbar_wait_bounded(&res_bar[quad][slot], static_cast<uint32_t>(g / kResSlots) & 1u,
+                                                 abort, kWaitLimitCycles));
+            if (!alive) break;
+          } else if (g >= kResSlots) {
+            // The store that last used this slot must have finished reading it.
+            if (lane == 0) tma_store_wait_read<kResSlots - 1>();
+            __syncwarp();
+          }
+          // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
+          // piece j stored at position j ^ (row & 7) (the 128-byte swizzle).
+          // The result overwrites the residual in place.
+          const int swz = lane & 7;
+          if (has_res) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const int col = col0 + j;
-          if (col >= args.cout) break;
-          float v[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = col + e;
-            float x = __uint_as_float(acc[j + e]);
-            if (c < args.cout) {
-              if (ep.scale) x *= __ldg(ep.scale + c);
-              if (ep.shift) x += __ldg(ep.shift + c);
+            for (int j = 0; j < 8; ++j) {
+              float4* cell = reinterpret_cast<float4*>(buf + ((j ^ swz) << 2));
+              *cell = finish4(j, *cell, true);
             }
-            v[e] = x;
-          }
-          const bool full4 = vec_ok && (col + 3 < args.cout);
-          if (res_row) {
-            if (full4) {
-              const float4 rr = *reinterpret_cast<const float4*>(res_row + col);
-              v[0] += ep.residual_coeff * rr.x;
-              v[1] += ep.residual_coeff * rr.y;
-              v[2] += ep.residual_coeff * rr.z;
-              v[3] += ep.residual_coeff * rr.w;
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (col + e < args.cout) v[e] += ep.residual_coeff * res_row[col + e];
-            }
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = col + e;
-            float slope = ep.slope;
-            if (ep.act == 2 && c < args.cout) slope = __ldg(ep.prelu + (ep.prelu_shared ? 0 : c));
-            v[e] = apply_act(v[e], ep.act, slope);
-            if (ep.round_tf32) v[e] = round_to_tf32(v[e]);
-          }
-          if (full4) {
-            *reinterpret_cast<float4*>(out_row + col) = make_float4(v[0], v[1], v[2], v[3]);
           } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (col + e < args.cout) out_row[col + e] = v[e];
+            for (int j = 0; j < 8; ++j) {
+              float4* cell = reinterpret_cast<float4*>(buf + ((j ^ swz) << 2));
+              *cell = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_out, slot_ptr(slot), col0, row0);
+            tma_store_commit();
+            if (has_res) {
+              // The slot of the previous chunk is reloaded (for the chunk
+              // kResSlots - 1 ahead) once its store has finished reading it.
+              tma_store_wait_read<1>();
+              issue_residual();
+            }
+          }
+        } else {
+          // ---- plain stores (rows not 16-byte aligned) ----
+          const int row = row0 + lane;
+          if (row < args.m) {
+            float* out_row = args.out + static_cast<size_t>(row) * args.out_ld;
+            const float* res_row = has_res ? ep.residual + static_cast<size_t>(row) * ep.residual_ld : nullptr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int c = col0 + j * 4;
+              if (c >= args.cout) break;
+              float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (res_row) {
+                r.x = res_row[c];
+                if (c + 1 < args.cout) r.y = res_row[c + 1];
+                if (c + 2 < args.cout) r.z = res_row[c + 2];
+                if (c + 3 < args.cout) r.w = res_row[c + 3];
+              }
+              const float4 v = finish4(j, r, res_row != nullptr);
+              out_row[c] = v.x;
+              if (c + 1 < args.cout) out_row[c + 1] = v.y;
+              if (c + 2 < args.cout) out_row[c + 2] = v.z;
+              if (c + 3 < args.cout) out_row[c + 3] = v.w;
+            }
           }
         }
       }
+      // All of this warp's reads of the accumulator are complete: hand it back.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[ab]);
     }
+    if (staged && lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown
@@ -360,7 +424,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_acc, BN);
+    tmem_dealloc(tmem_base, 2 * BN);
   }
   if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 1);
 }
@@ -458,7 +522,15 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args,
   }
   const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * ((plan->m + kBlockM - 1) / kBlockM);
   if (tiles > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  dim3 grid(static_cast<unsigned>(tiles), 1, 1);
+  // One persistent CTA per SM (fewer when there are fewer tiles).
+  static int sm_count[64] = {0};
+  if (dev >= 0 && dev < 64 && sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+    sm_count[dev] = n;
+  }
+  const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
+  dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms), 1, 1);
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
   const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);

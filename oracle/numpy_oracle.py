@@ -1,0 +1,199 @@
+"""CPU restatement (numpy) of mini-caffe's forward arithmetic for the dense
+layers on the engine's hot path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing under oracle/ is part of the product: the
+engine never imports, links or calls it.  It exists so that tests can check the
+CUDA kernels against an independent statement of what the reference computes,
+also on machines where the compiled reference (oracle/_ref) is absent.
+
+Pinning: the reference project ships no golden vectors or known-answer tests
+for these layers, so this restatement is pinned against outputs of the
+reference itself: tests/golden/*.npz were produced by running the reference's
+unmodified CPU sources (oracle/_ref, built by oracle/Makefile) through
+tests/golden/make_golden.py, and tests/test_oracle_cpu.py checks every
+function here against them.
+
+Each function cites the reference code it follows (paths relative to the
+mini-caffe project).  All arithmetic is float32 like the reference; matrix
+products go through numpy (whose BLAS may sum in a different order than
+OpenBLAS does for the reference: agreement is to float32 rounding, about 1e-6
+relative).
+"""
+import numpy as np
+
+F = np.float32
+
+
+def conv_out_size(size, kernel, stride, pad, dilation=1):
+    """floor((in + 2p - (d(k-1)+1)) / s) + 1 -- src/layers/conv_layer.cpp:12-25."""
+    ext = dilation * (kernel - 1) + 1
+    return (size + 2 * pad - ext) // stride + 1
+
+
+def im2col(x, kh, kw, stride, pad, dilation=1):
+    """One image [C, H, W] -> [C*kh*kw, Ho*Wo]; zero padding.  src/util/im2col.cpp:19-55."""
+    c, h, w = x.shape
+    ho = conv_out_size(h, kh, stride, pad, dilation)
+    wo = conv_out_size(w, kw, stride, pad, dilation)
+    padded = np.zeros((c, h + 2 * pad, w + 2 * pad), dtype=F)
+    padded[:, pad:pad + h, pad:pad + w] = x
+    col = np.empty((c, kh, kw, ho, wo), dtype=F)
+    for r in range(kh):
+        for s in range(kw):
+            y0, x0 = r * dilation, s * dilation
+            col[:, r, s] = padded[:, y0:y0 + stride * (ho - 1) + 1:stride, x0:x0 + stride * (wo - 1) + 1:stride]
+    return col.reshape(c * kh * kw, ho * wo), ho, wo
+
+
+def convolution(x, weight, bias=None, stride=1, pad=0, dilation=1, group=1):
+    """Per image: im2col, then per group W[Cout/g, K] x col[K, HoWo], then bias added as a
+    rank-1 product.  src/layers/base_conv_layer.cpp:254-278."""
+    n, c, h, w = x.shape
+    cout, cin_g, kh, kw = weight.shape
+    assert cin_g * group == c and cout % group == 0
+    out = None
+    for i in range(n):
+        col, ho, wo = im2col(x[i], kh, kw, stride, pad, dilation)
+        if out is None:
+            out = np.empty((n, cout, ho, wo), dtype=F)
+        kg = cin_g * kh * kw
+        og = cout // group
+        y = np.empty((cout, ho * wo), dtype=F)
+        for g in range(group):
+            y[g * og:(g + 1) * og] = weight[g * og:(g + 1) * og].reshape(og, kg) @ col[g * kg:(g + 1) * kg]
+        if bias is not None:
+            y += bias.astype(F)[:, None]
+        out[i] = y.reshape(cout, ho, wo)
+    return out
+
+
+def inner_product(x, weight, bias=None, axis=1, transpose=False):
+    """Y = X W^T (+ 1 b^T) over the dims from `axis` flattened.  src/layers/inner_product_layer.cpp:80-93."""
+    m = int(np.prod(x.shape[:axis]))
+    xm = x.reshape(m, -1).astype(F)
+    y = xm @ (weight if transpose else weight.T)
+    if bias is not None:
+        y = y + bias.astype(F)[None, :]
+    return y.astype(F).reshape(x.shape[:axis] + (y.shape[1],))
+
+
+def batch_norm(x, mean, var, factor, eps=1e-5):
+    """mean = b0/f, var = b1/f (f = b2[0], 0 -> 0); y = (x - mean) / (var + eps)^0.5, all float.
+    src/layers/batch_norm_layer.cpp:83-135."""
+    f = F(0) if factor == 0 else F(1) / F(factor)
+    m = (mean.astype(F) * f).reshape(1, -1, *([1] * (x.ndim - 2)))
+    v = (var.astype(F) * f + F(eps)).reshape(1, -1, *([1] * (x.ndim - 2)))
+    return ((x - m) / np.power(v, F(0.5))).astype(F)
+
+
+def scale(x, gamma, beta=None):
+    """y = x * gamma[c] (+ beta[c]).  src/layers/scale_layer.cpp:96-113, bias_layer.cpp:68-83."""
+    shape = (1, -1) + (1,) * (x.ndim - 2)
+    y = x * gamma.astype(F).reshape(shape)
+    if beta is not None:
+        y = y + beta.astype(F).reshape(shape)
+    return y.astype(F)
+
+
+def relu(x, negative_slope=0.0):
+    """max(x, 0) + slope * min(x, 0).  src/layers/relu_layer.cpp:12-29."""
+    return (np.maximum(x, 0) + F(negative_slope) * np.minimum(x, 0)).astype(F)
+
+
+def prelu(x, slopes, channel_shared=False):
+    """max(x, 0) + slope[c] * min(x, 0).  src/layers/prelu_layer.cpp:52-84."""
+    s = slopes.astype(F).reshape(-1)
+    shape = (1, -1) + (1,) * (x.ndim - 2)
+    sl = s[0] if channel_shared else s.reshape(shape)
+    return (np.maximum(x, 0) + sl * np.minimum(x, 0)).astype(F)
+
+
+def eltwise(inputs, op="SUM", coeffs=None):
+    """SUM: 0 + sum coeff_i x_i in bottom order; PROD; MAX.  src/layers/eltwise_layer.cpp:37-78."""
+    if op == "SUM":
+        coeffs = coeffs or [1.0] * len(inputs)
+        y = np.zeros_like(inputs[0], dtype=F)
+        for c, x in zip(coeffs, inputs):
+            y = y + F(c) * x
+        return y.astype(F)
+    if op == "PROD":
+        y = inputs[0].astype(F)
+        for x in inputs[1:]:
+            y = y * x
+        return y.astype(F)
+    y = inputs[0]
+    for x in inputs[1:]:
+        y = np.maximum(y, x)
+    return y.astype(F)
+
+
+def pool_out_size(size, kernel, stride, pad):
+    """ceil((in + 2p - k) / s) + 1, minus one if the last window would start in the padding.
+    src/layers/pooling_layer.cpp:92-107."""
+    out = int(np.ceil(F(size + 2 * pad - kernel) / F(stride))) + 1
+    if pad and (out - 1) * stride >= size + pad:
+        out -= 1
+    return out
+
+
+def pooling(x, method, kernel, stride=1, pad=0, global_pooling=False):
+    """MAX over the window clipped to the image (start -FLT_MAX); AVE = sum over the clipped
+    window / area of the window clipped to the padded image.  src/layers/pooling_layer.cpp:124-181."""
+    n, c, h, w = x.shape
+    kh, kw = (h, w) if global_pooling else (kernel, kernel)
+    ho, wo = pool_out_size(h, kh, stride, pad), pool_out_size(w, kw, stride, pad)
+    out = np.empty((n, c, ho, wo), dtype=F)
+    for py in range(ho):
+        for px in range(wo):
+            y0, x0 = py * stride - pad, px * stride - pad
+            if method == "MAX":
+                y1, x1 = min(y0 + kh, h), min(x0 + kw, w)
+                out[:, :, py, px] = x[:, :, max(y0, 0):y1, max(x0, 0):x1].max(axis=(2, 3))
+            else:
+                y1, x1 = min(y0 + kh, h + pad), min(x0 + kw, w + pad)
+                area = F((y1 - y0) * (x1 - x0))
+                win = x[:, :, max(y0, 0):min(y1, h), max(x0, 0):min(x1, w)]
+                out[:, :, py, px] = win.sum(axis=(2, 3), dtype=F) / area
+    return out
+
+
+def softmax(x, axis=1):
+    """Subtract the max over `axis`, exp (float), divide by the sum.  src/layers/softmax_layer.cpp:29-63."""
+    m = x.max(axis=axis, keepdims=True)
+    e = np.exp((x - m).astype(F)).astype(F)
+    return (e / e.sum(axis=axis, keepdims=True, dtype=F)).astype(F)
+
+
+def concat(inputs, axis=1):
+    """src/layers/concat_layer.cpp:53-70."""
+    return np.concatenate(inputs, axis=axis).astype(F)
+
+
+def normalize(x, scale_values, eps=1e-10, channel_shared=False):
+    """across_spatial = false: y = x / (sum_c x^2 + eps)^0.5 * scale[c].  src/layers/normalize_layer.cpp:86-135."""
+    norm = np.power((x.astype(F) ** 2).sum(axis=1, keepdims=True, dtype=F) + F(eps), F(0.5))
+    s = scale_values.astype(F).reshape(-1)
+    sc = s[0] if channel_shared else s.reshape(1, -1, 1, 1)
+    return (x / norm * sc).astype(F)
+
+
+def permute(x, order):
+    """src/layers/permute_layer.cpp:8-22."""
+    return np.ascontiguousarray(np.transpose(x, order)).astype(F)
+
+
+def conv_relu(x, weight, bias, pad=1):
+    """The single Convolution + ReLU network of the first benchmark configuration."""
+    return relu(convolution(x, weight, bias, stride=1, pad=pad))
+
+
+def fold_batch_norm_scale(mean, var, factor, eps, gamma, beta, conv_bias=None):
+    """Per-channel (scale, shift) such that scale * conv + shift == Scale(BatchNorm(conv + bias)).
+    The folding algebra of tools/fuse_bn.py:34-38 with BatchNorm's scale factor blob
+    (src/layers/batch_norm_layer.cpp:85-90)."""
+    f = 0.0 if factor == 0 else 1.0 / float(factor)
+    inv_std = 1.0 / np.sqrt(var.astype(np.float64) * f + eps)
+    s = gamma.astype(np.float64) * inv_std
+    b0 = conv_bias.astype(np.float64) if conv_bias is not None else 0.0
+    t = (b0 - mean.astype(np.float64) * f) * s + beta.astype(np.float64)
+    return s, t
