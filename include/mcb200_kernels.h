@@ -83,7 +83,8 @@ typedef struct mcb200_conv_plan {
   uint64_t tma_out[16];     /* output / residual tile maps, built on first launch  */
   uint64_t tma_res[16];     /* and rebuilt when the pointers below change          */
   mcb200_conv_shape shape;
-  int m, k_iters, c_blocks, block_n, im2col;
+  int m, k_iters, c_blocks, block_n;
+  int im2col;               /* 0 matrix rows, 1 im2col tensor map, 2 row mode      */
   int out_ld, res_ld, reserved;
   const float* out_ptr;
   const float* res_ptr;
@@ -102,6 +103,25 @@ int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float
  * the previous launch (their tile maps are cached in it).                     */
 int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld,
                           const mcb200_epilogue* ep, int* status, void* stream);
+
+/* "Row mode" of the same kernel for layers with at most four input channels (the
+ * first layer of an image network), where 32-channel blocks would be almost all
+ * padding: the input is copied once into a zero-bordered channels-last image
+ * with 4 floats per pixel (mcb200_conv_rows_pad_input), and one k-iteration then
+ * covers a whole filter row: 8 neighbouring pixels x 4 channels = one 128-byte
+ * row per output pixel, fetched by a tiled tensor map whose pixel pitch is the
+ * convolution stride.  An M tile is one output row of one image.  Requires
+ * kw <= 8, dil_w == 1 and an output width of at most 128.
+ *   padded copy: [n, hp, wp, 4] floats with (hp, wp) from mcb200_conv_rows_padded_dims
+ *   weights:     [cout][kh][8 * 4] via mcb200_conv_rows_pack_weights
+ * Launch with mcb200_conv_tc_launch.                                            */
+int mcb200_conv_rows_supported(const mcb200_conv_shape* s);
+int mcb200_conv_rows_padded_dims(const mcb200_conv_shape* s, int* hp, int* wp);
+size_t mcb200_conv_rows_packed_weight_count(const mcb200_conv_shape* s);
+int mcb200_conv_rows_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed, void* stream);
+int mcb200_conv_rows_pad_input(const mcb200_conv_shape* s, const float* src_nchw, float* padded, void* stream);
+int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* padded_in, const float* packed_w,
+                          mcb200_conv_plan* plan);
 
 /* Direct convolution, one thread per output element, any group count; the
  * fallback for shapes the tensor-core path rejects.  Weights stay in Caffe

@@ -46,6 +46,10 @@ constexpr int kBlockK = 32;                            // fp32 elements = one 12
 constexpr int kTileABytes = kBlockM * kBlockK * 4;     // 16 KiB
 constexpr int kThreads = 192;
 constexpr long long kWaitLimitCycles = 2000000000LL;   // about one second
+// How the activation tile of a k-iteration is fetched.
+constexpr int kModeMatrix = 0;   // rows of a plain [m, c] matrix (1x1 convolution, inner product)
+constexpr int kModeIm2col = 1;   // im2col-mode tensor map: any filter, channels % 4 == 0
+constexpr int kModeRows = 2;     // <= 4 channels: one filter row of 8 pixels x 4 channels per k-iteration
 
 struct ConvTcArgs {
   float* out;
@@ -60,6 +64,8 @@ struct ConvTcArgs {
   mcb200_epilogue ep;
   int* status;
   int tma_epilogue;  // output (and residual) meet the 16-byte rules of TMA tiles
+  int tile_rows;     // valid rows of an M tile: 128, or the output width in row mode
+  int a_bytes;       // bytes one activation tile load delivers
 };
 
 template <int BN>
@@ -84,7 +90,7 @@ __device__ __forceinline__ float apply_act(float v, int act, float slope) {
 // accumulators in tensor memory let the tensor core start the next tile while
 // the epilogue warps drain the previous one; the TMA producer runs ahead across
 // tile boundaries.
-template <int BN, bool kIm2col>
+template <int BN, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
@@ -114,7 +120,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles = (args.cout + BN - 1) / BN;
-  const int m_tiles = (args.m + kBlockM - 1) / kBlockM;
+  // Row mode: an M tile is one output row of one image (tile_rows <= 128 pixels).
+  const int m_tiles = kMode == kModeRows ? args.m / args.tile_rows : (args.m + kBlockM - 1) / kBlockM;
   const int num_tiles = n_tiles * m_tiles;
 
   if (threadIdx.x == 0) {
@@ -150,10 +157,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0;   // k-iterations issued so far, over all tiles of this CTA
       bool alive = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * kBlockM;
+        const int mt = tile / n_tiles;
+        const int m0 = mt * kBlockM;
         const int n0 = (tile % n_tiles) * BN;
         int base_w = 0, base_h = 0, base_n = 0;
-        if (kIm2col) {
+        if (kMode == kModeRows) {
+          base_n = mt / args.ho;
+          base_h = (mt - base_n * args.ho) * args.stride_h;   // row in the spatially padded copy
+        }
+        if (kMode == kModeIm2col) {
           const int q = m0 % args.wo;
           const int p = (m0 / args.wo) % args.ho;
           base_n = m0 / (args.wo * args.ho);
@@ -166,10 +178,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (!mbar_wait_bounded(&empty_bar[s], phase ^ 1u, abort, kWaitLimitCycles)) { alive = false; break; }
           uint8_t* a_dst = tiles + s * Plan::kStageBytes;
           uint8_t* b_dst = a_dst + kTileABytes;
-          mbar_expect_tx(&full_bar[s], Plan::kStageBytes);
+          mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(args.a_bytes) + Plan::kTileBBytes);
           const int tap = k / args.c_blocks;
           const int cb = k - tap * args.c_blocks;
-          if (kIm2col) {
+          if (kMode == kModeRows) {
+            // k is the filter row: tile_rows pixels x (8 pixels x 4 channels) of input row base_h + k * dil_h.
+            tma_load_4d(&map_a, &full_bar[s], a_dst, 0, 0, base_h + k * args.dil_h, base_n);
+          } else if (kMode == kModeIm2col) {
             const int r = tap / args.kw;
             const int sx = tap - r * args.kw;
             tma_load_im2col_4d(&map_a, &full_bar[s], a_dst, cb * kBlockK, base_w, base_h, base_n,
@@ -246,11 +261,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto issue_residual = [&]() {
       const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(pre_local) * gridDim.x;
       if (tile >= num_tiles) return;
-      const int row0 = static_cast<int>(tile / n_tiles) * kBlockM + quad * 32;
+      const int mt = static_cast<int>(tile / n_tiles);
       const int tile_n0 = static_cast<int>(tile % n_tiles) * BN;
       const int slot = pre_seq % kResSlots;
       mbar_expect_tx(&res_bar[quad][slot], 4096);
-      tma_load_2d(&map_res, &res_bar[quad][slot], slot_ptr(slot), tile_n0 + pre_chunk * 32, row0);
+      if (kMode == kModeRows) {
+        tma_load_3d(&map_res, &res_bar[quad][slot], slot_ptr(slot), tile_n0 + pre_chunk * 32, quad * 32, mt);
+      } else {
+        tma_load_3d(&map_res, &res_bar[quad][slot], slot_ptr(slot), tile_n0 + pre_chunk * 32, mt * kBlockM + quad * 32,
+                    0);
+      }
       ++pre_seq;
       ++pre_chunk;
       if (pre_chunk >= chunks_full || tile_n0 + pre_chunk * 32 >= args.cout) {
@@ -269,9 +289,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
       const int ab = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
-      const int m0 = (tile / n_tiles) * kBlockM;
+      const int mt = tile / n_tiles;
       const int n0 = (tile % n_tiles) * BN;
-      const int row0 = m0 + quad * 32;
+      // First output row (pixel) of this warp's 32-row slice, and how many of the 32 exist.
+      const int row0 = (kMode == kModeRows ? mt * args.tile_rows : mt * kBlockM) + quad * 32;
+      const int rows_here = kMode == kModeRows ? args.tile_rows - quad * 32 : args.m - row0;
       // Per-column constants of this tile go to shared memory once, so that the
       // inner loops are a broadcast 16-byte load and fused multiply-adds.  Two
       // copies (tile parity): a warp may still be reading the previous tile's.
@@ -375,7 +397,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&map_out, slot_ptr(slot), col0, row0);
+            if (kMode == kModeRows) {
+              tma_store_3d(&map_out, slot_ptr(slot), col0, quad * 32, mt);
+            } else {
+              tma_store_3d(&map_out, slot_ptr(slot), col0, row0, 0);
+            }
             tma_store_commit();
             if (has_res) {
               // The slot of the previous chunk is reloaded (for the chunk
@@ -387,7 +413,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else {
           // ---- plain stores (rows not 16-byte aligned) ----
           const int row = row0 + lane;
-          if (row < args.m) {
+          if (lane < rows_here) {
             float* out_row = args.out + static_cast<size_t>(row) * args.out_ld;
             const float* res_row = has_res ? ep.residual + static_cast<size_t>(row) * ep.residual_ld : nullptr;
 #pragma unroll
@@ -489,20 +515,25 @@ int pick_block_n(int cout) {
   return 256;
 }
 
-// Tile map over a row-major [rows, cols] fp32 matrix with row pitch `ld`,
-// 32 x 32 boxes, 128-byte swizzle: what the staged epilogue stores / loads.
-CUresult encode_tile_map(CUtensorMap* map, const float* base, int rows, int cols, int ld) {
+// Tile map for the staged epilogue over a row-major fp32 matrix with row pitch
+// `ld`, 32 x 32 boxes, 128-byte swizzle.  The rows are split as (group, row in
+// group): ordinary tiles use one group of all rows; row mode uses one group per
+// output row of an image so that a tile never spills into the next row.
+CUresult encode_tile_map(CUtensorMap* map, const float* base, int cols, int ld, long long rows_per_group,
+                         long long groups) {
   const DriverApi& api = driver_api();
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
-  const cuuint32_t box[2] = {32, 32};
-  const cuuint32_t estr[2] = {1, 1};
-  return api.tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows_per_group),
+                              static_cast<cuuint64_t>(groups)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4,
+                                 static_cast<cuuint64_t>(ld) * 4 * static_cast<cuuint64_t>(rows_per_group)};
+  const cuuint32_t box[3] = {32, 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return api.tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <int BN, bool kIm2col>
+template <int BN, int kMode>
 cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args, cudaStream_t stream) {
   using Plan = SmemPlan<BN>;
   // The large-shared-memory opt-in is per device: do it once for each device
@@ -514,13 +545,15 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args,
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<BN, kIm2col>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<BN, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Plan::kDynamicBytes);
       if (e != cudaSuccess) return e;
       configured[dev] = true;
     }
   }
-  const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * ((plan->m + kBlockM - 1) / kBlockM);
+  const long long m_tiles = kMode == kModeRows ? static_cast<long long>(plan->shape.n) * plan->shape.ho
+                                               : (plan->m + kBlockM - 1) / kBlockM;
+  const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * m_tiles;
   if (tiles > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
   // One persistent CTA per SM (fewer when there are fewer tiles).
   static int sm_count[64] = {0};
@@ -537,7 +570,7 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args,
   const CUtensorMap* mr = reinterpret_cast<const CUtensorMap*>(plan->tma_res);
   {
     TimedLaunch timed(stream);
-    conv_tc_kernel<BN, kIm2col><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, *mo, *mr, args);
+    conv_tc_kernel<BN, kMode><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, *mo, *mr, args);
   }
   count_launch();
   return cudaGetLastError();
@@ -684,29 +717,177 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
                                          ((reinterpret_cast<uintptr_t>(a.ep.residual) & 15) == 0));
   a.tma_epilogue = (out_ok && res_ok) ? 1 : 0;
   if (a.tma_epilogue) {
+    const bool rows = plan->im2col == kModeRows;
+    const long long per_group = rows ? plan->shape.wo : plan->m;
+    const long long groups = rows ? static_cast<long long>(plan->shape.n) * plan->shape.ho : 1;
     if (plan->out_ptr != out || plan->out_ld != out_ld) {
-      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_out), out, plan->m, plan->shape.cout, out_ld) !=
-          CUDA_SUCCESS)
+      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_out), out, plan->shape.cout, out_ld, per_group,
+                          groups) != CUDA_SUCCESS)
         return -4;
       plan->out_ptr = out;
       plan->out_ld = out_ld;
     }
     if (a.ep.residual && (plan->res_ptr != a.ep.residual || plan->res_ld != a.ep.residual_ld)) {
-      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_res), a.ep.residual, plan->m, plan->shape.cout,
-                          a.ep.residual_ld) != CUDA_SUCCESS)
+      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_res), a.ep.residual, plan->shape.cout,
+                          a.ep.residual_ld, per_group, groups) != CUDA_SUCCESS)
         return -5;
       plan->res_ptr = a.ep.residual;
       plan->res_ld = a.ep.residual_ld;
     }
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e;
-  const bool im = plan->im2col != 0;
+  a.tile_rows = plan->im2col == kModeRows ? plan->shape.wo : kBlockM;
+  a.a_bytes = a.tile_rows * kBlockK * 4;
+  cudaError_t e = cudaErrorInvalidValue;
+  const int mode = plan->im2col;
+#define MCB200_DISPATCH(BN)                                                     \
+  e = mode == kModeRows     ? launch_variant<BN, kModeRows>(plan, a, st)        \
+      : mode == kModeIm2col ? launch_variant<BN, kModeIm2col>(plan, a, st)      \
+                            : launch_variant<BN, kModeMatrix>(plan, a, st)
   switch (plan->block_n) {
-    case 64: e = im ? launch_variant<64, true>(plan, a, st) : launch_variant<64, false>(plan, a, st); break;
-    case 128: e = im ? launch_variant<128, true>(plan, a, st) : launch_variant<128, false>(plan, a, st); break;
-    case 256: e = im ? launch_variant<256, true>(plan, a, st) : launch_variant<256, false>(plan, a, st); break;
+    case 64: MCB200_DISPATCH(64); break;
+    case 128: MCB200_DISPATCH(128); break;
+    case 256: MCB200_DISPATCH(256); break;
     default: return -3;
   }
+#undef MCB200_DISPATCH
   return static_cast<int>(e);
+}
+
+// ------------------------------------------------------------------ row mode (few input channels)
+
+namespace mcb200 {
+namespace {
+
+__global__ void pack_rows_weights_kernel(const float* __restrict__ w, float* __restrict__ packed, int cout, int c,
+                                         int kh, int kw) {
+  const int total = cout * kh * kBlockK;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int e = i % kBlockK;          // 8 pixels x 4 channels of one filter row
+    const int r = (i / kBlockK) % kh;
+    const int co = i / (kBlockK * kh);
+    const int sx = e >> 2, ch = e & 3;
+    float v = 0.f;
+    if (sx < kw && ch < c) v = round_to_tf32(w[((static_cast<size_t>(co) * c + ch) * kh + r) * kw + sx]);
+    packed[i] = v;
+  }
+}
+
+// (N, C<=4, H, W) -> zero-bordered channels-last copy with 4 floats per pixel.
+__global__ void pad_nhwc4_kernel(const float* __restrict__ src, float4* __restrict__ dst, int n, int c, int h, int w,
+                                 int pad_h, int pad_w, int hp, int wp) {
+  const long long total = static_cast<long long>(n) * hp * wp;
+  const size_t plane = static_cast<size_t>(h) * w;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int xp = static_cast<int>(i % wp);
+    const int yp = static_cast<int>((i / wp) % hp);
+    const int img = static_cast<int>(i / (static_cast<long long>(wp) * hp));
+    const int x = xp - pad_w, y = yp - pad_h;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (x >= 0 && x < w && y >= 0 && y < h) {
+      const float* s = src + static_cast<size_t>(img) * c * plane + static_cast<size_t>(y) * w + x;
+      v.x = s[0];
+      if (c > 1) v.y = s[plane];
+      if (c > 2) v.z = s[2 * plane];
+      if (c > 3) v.w = s[3 * plane];
+    }
+    dst[i] = v;
+  }
+}
+
+}  // namespace
+}  // namespace mcb200
+
+extern "C" int mcb200_conv_rows_supported(const mcb200_conv_shape* s) {
+  if (!s || s->group != 1 || s->c < 1 || s->c > 4 || s->kw > 8 || s->dil_w != 1) return 0;
+  mcb200_conv_shape t = *s;
+  if (mcb200_conv_out_shape(&t) != 0) return 0;
+  return t.wo >= 1 && t.wo <= kBlockM;
+}
+
+extern "C" int mcb200_conv_rows_padded_dims(const mcb200_conv_shape* s, int* hp, int* wp) {
+  if (!mcb200_conv_rows_supported(s) || !hp || !wp) return -1;
+  mcb200_conv_shape t = *s;
+  mcb200_conv_out_shape(&t);
+  *hp = t.h + 2 * t.pad_h;
+  const int reach = (t.wo - 1) * t.stride_w + 8;   // the last tile row reads 8 pixels
+  *wp = t.w + 2 * t.pad_w > reach ? t.w + 2 * t.pad_w : reach;
+  return 0;
+}
+
+extern "C" size_t mcb200_conv_rows_packed_weight_count(const mcb200_conv_shape* s) {
+  return static_cast<size_t>(s->cout) * s->kh * kBlockK;
+}
+
+extern "C" int mcb200_conv_rows_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed,
+                                             void* stream) {
+  if (!mcb200_conv_rows_supported(s) || !w_oihw || !packed) return -1;
+  const int total = s->cout * s->kh * kBlockK;
+  pack_rows_weights_kernel<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(w_oihw, packed, s->cout,
+                                                                                              s->c, s->kh, s->kw);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_conv_rows_pad_input(const mcb200_conv_shape* s, const float* src_nchw, float* padded,
+                                          void* stream) {
+  int hp = 0, wp = 0;
+  if (mcb200_conv_rows_padded_dims(s, &hp, &wp) != 0 || !src_nchw || !padded) return -1;
+  if (reinterpret_cast<uintptr_t>(padded) & 15) return -2;
+  const long long total = static_cast<long long>(s->n) * hp * wp;
+  if (total == 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  pad_nhwc4_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, wp);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* padded_in, const float* packed_w,
+                                     mcb200_conv_plan* plan) {
+  if (!padded_in || !packed_w || !plan) return -1;
+  int hp = 0, wp = 0;
+  if (mcb200_conv_rows_padded_dims(s, &hp, &wp) != 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(padded_in) & 15) || (reinterpret_cast<uintptr_t>(packed_w) & 15)) return -3;
+  const DriverApi& api = driver_api();
+  if (!api.ok) return -5;
+  plan->shape = *s;
+  plan->shape.c_stride = 4;
+  plan->out_ptr = nullptr;
+  plan->res_ptr = nullptr;
+  plan->out_ld = plan->res_ld = plan->reserved = 0;
+  if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
+  const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
+  if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
+  plan->m = static_cast<int>(m_ll);
+  plan->c_blocks = 1;
+  plan->k_iters = s->kh;
+  plan->block_n = pick_block_n(s->cout);
+  plan->im2col = kModeRows;
+  // Activation view: 32 floats (8 pixels x 4 channels) starting at padded pixel q * stride_w of padded row y.
+  // Consecutive q overlap (the pitch of dimension 1 is stride_w pixels, less than the 8-pixel extent).
+  CUtensorMap* ma = reinterpret_cast<CUtensorMap*>(plan->tma_a);
+  const cuuint64_t dims[4] = {kBlockK, static_cast<cuuint64_t>(plan->shape.wo), static_cast<cuuint64_t>(hp),
+                              static_cast<cuuint64_t>(s->n)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s->stride_w) * 16, static_cast<cuuint64_t>(wp) * 16,
+                                 static_cast<cuuint64_t>(wp) * 16 * hp};
+  const cuuint32_t box[4] = {kBlockK, static_cast<cuuint32_t>(plan->shape.wo), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(padded_in), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
+  CUtensorMap* mb = reinterpret_cast<CUtensorMap*>(plan->tma_b);
+  const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kBlockK;
+  const cuuint64_t bdims[2] = {kp, static_cast<cuuint64_t>(s->cout)};
+  const cuuint64_t bstrides[1] = {kp * 4};
+  const cuuint32_t bbox[2] = {kBlockK, static_cast<cuuint32_t>(plan->block_n)};
+  const cuuint32_t bestr[2] = {1, 1};
+  r = api.tiled(mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(packed_w), bdims, bstrides, bbox, bestr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -200 - static_cast<int>(r);
+  return 0;
 }

@@ -179,6 +179,12 @@ void ConvolutionLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>&
   shape_.h = bottom[0]->shape(2);
   shape_.w = bottom[0]->shape(3);
   CHECK_EQ(mcb200_conv_out_shape(&shape_), 0) << "convolution window larger than the padded input";
+  // Few input channels (an image in front of the first layer): one filter row per k-iteration.
+  const bool rows = path_ == kTensorCore && !rows_rejected_ && mcb200_conv_rows_supported(&shape_) != 0;
+  if (rows != use_rows_) {
+    use_rows_ = rows;
+    weight_version_ = 0;   // the packed weight image differs between the two modes
+  }
   for (size_t i = 0; i < top.size(); ++i) top[i]->Reshape(shape_.n, shape_.cout, shape_.ho, shape_.wo);
 }
 
@@ -186,7 +192,10 @@ void ConvolutionLayer::RefreshParameters() {
   Context& ctx = Context::Get();
   const unsigned long long wv = blobs_[0]->host_version();
   if (wv != weight_version_) {
-    if (path_ == kTensorCore) {
+    if (path_ == kTensorCore && use_rows_) {
+      float* packed = packed_weights_.Reserve(mcb200_conv_rows_packed_weight_count(&shape_));
+      KERNEL_CHECK(mcb200_conv_rows_pack_weights(&shape_, blobs_[0]->gpu_data(), packed, ctx.stream_ptr()));
+    } else if (path_ == kTensorCore) {
       float* packed = packed_weights_.Reserve(mcb200_conv_packed_weight_count(&shape_));
       KERNEL_CHECK(mcb200_conv_pack_weights(&shape_, blobs_[0]->gpu_data(), packed, ctx.stream_ptr()));
     } else if (path_ == kDepthwise) {
@@ -217,7 +226,14 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
   for (size_t i = 0; i < bottom.size(); ++i) {
     mcb200_conv_shape s = shape_;
     const float* in = nullptr;
-    if (shape_.c % 4 == 0) {
+    if (path_ == kTensorCore && use_rows_) {
+      int hp = 0, wp = 0;
+      CHECK_EQ(mcb200_conv_rows_padded_dims(&s, &hp, &wp), 0);
+      s.c_stride = 4;
+      float* padded = padded_input_.Reserve(static_cast<size_t>(s.n) * hp * wp * 4);
+      KERNEL_CHECK(mcb200_conv_rows_pad_input(&s, bottom[i]->gpu_data(), padded, ctx.stream_ptr()));
+      in = padded;
+    } else if (shape_.c % 4 == 0) {
       s.c_stride = s.c;
       in = bottom[i]->gpu_data_nhwc();
     } else {
@@ -245,7 +261,17 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
       PlanSlot& slot = *plans_[i];
       const float* w = packed_weights_.Reserve(0);
       if (!slot.valid || slot.in != in || slot.weights != w || std::memcmp(&slot.shape, &s, sizeof(s)) != 0) {
-        const int rc = mcb200_conv_tc_plan(&s, in, w, &slot.plan);
+        int rc = use_rows_ ? mcb200_conv_rows_plan(&s, in, w, &slot.plan) : mcb200_conv_tc_plan(&s, in, w, &slot.plan);
+        if (rc != 0 && use_rows_) {
+          // The driver refused the row-mode tensor map: use the general path from now on.
+          LOG(WARNING) << "layer " << layer_param_.name() << ": row-mode plan rejected (" << rc
+                       << "), using the im2col path";
+          rows_rejected_ = true;
+          use_rows_ = false;
+          weight_version_ = 0;
+          Forward_gpu(bottom, top);
+          return;
+        }
         CHECK_EQ(rc, 0) << "cannot build the tensor-core plan for layer " << layer_param_.name();
         slot.in = in;
         slot.weights = w;

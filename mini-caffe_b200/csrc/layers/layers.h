@@ -59,6 +59,8 @@ class ConvolutionLayer : public Layer {
   DeviceArray scale_, shift_;
   DeviceScratch packed_weights_, padded_input_;
   enum Path { kTensorCore, kDepthwise, kDirect } path_ = kDirect;
+  bool use_rows_ = false;       // tensor-core row mode (at most four input channels)
+  bool rows_rejected_ = false;
   struct PlanSlot {
     mcb200_conv_plan plan;
     const float* in = nullptr;
