@@ -509,10 +509,27 @@ const DriverApi& driver_api() {
   return api;
 }
 
-int pick_block_n(int cout) {
-  if (cout <= 64) return 64;
-  if (cout <= 128) return 128;
-  return 256;
+// Tile width.  The kernel is persistent (one CTA per SM), so a layer takes as
+// long as its busiest CTA: ceil(tiles / SMs) tiles, each costing its k-iterations
+// (operand bytes per iteration grow with BN) plus an epilogue proportional to BN.
+// Wide tiles re-read the activations less often, narrow tiles fill the machine
+// when there are few output pixels; take the cheapest of the three.
+int pick_block_n(int cout, long long m, int k_iters) {
+  const long long m_tiles = (m + kBlockM - 1) / kBlockM;
+  int best = 64;
+  double best_cost = 0.0;
+  for (int bn = 64; bn <= 256; bn *= 2) {
+    if (bn > 64 && bn / 2 >= cout) break;   // wider than the layer: only padding
+    const long long tiles = m_tiles * ((cout + bn - 1) / bn);
+    const long long waves = (tiles + 147) / 148;
+    const double per_tile = static_cast<double>(k_iters) * (kTileABytes + 128.0 * bn) + 8192.0 * (bn / 32);
+    const double cost = static_cast<double>(waves) * per_tile;
+    if (bn == 64 || cost < best_cost * 0.97) {   // prefer the narrower tile on near ties
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
 }
 
 // Tile map for the staged epilogue over a row-major fp32 matrix with row pitch
@@ -631,7 +648,7 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   plan->m = static_cast<int>(m_ll);
   plan->c_blocks = (s->c + kBlockK - 1) / kBlockK;
   plan->k_iters = s->kh * s->kw * plan->c_blocks;
-  plan->block_n = pick_block_n(s->cout);
+  plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
   const bool pointwise = s->kh == 1 && s->kw == 1 && s->stride_h == 1 && s->stride_w == 1 && s->pad_h == 0 &&
                          s->pad_w == 0;
   plan->im2col = pointwise ? 0 : 1;
@@ -864,7 +881,7 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   plan->m = static_cast<int>(m_ll);
   plan->c_blocks = 1;
   plan->k_iters = s->kh;
-  plan->block_n = pick_block_n(s->cout);
+  plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
   plan->im2col = kModeRows;
   // Activation view: 32 floats (8 pixels x 4 channels) starting at padded pixel q * stride_w of padded row y.
   // Consecutive q overlap (the pitch of dimension 1 is stride_w pixels, less than the 8-pixel extent).

@@ -1,0 +1,207 @@
+"""Per-layer parity on the GPU against the reference CPU build: the layers that
+are not exercised (or only in fused form) by the ResNet tests, edge shapes, and
+MobileNet-v1 end to end."""
+import numpy as np
+import pytest
+
+from conftest import pkg
+from parity import assert_close, run_net
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu_engine(engine):
+    engine.set_mode(True, 0)
+    return engine
+
+
+def both(capi, gpu_engine, reflib, b, weights, x, outs, marks=()):
+    got = run_net(capi, gpu_engine, b, weights, x, outs, marks=marks)
+    want = run_net(capi, reflib, b, weights, x, outs, marks=marks)
+    return got, want
+
+
+def test_depthwise_and_grouped_convolution(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("dw")
+    b.input([("data", (3, 32, 17, 19))])
+    b.conv("dw", "data", "dw", 32, 32, 3, stride=2, pad=1, group=32)          # depthwise kernel
+    b.relu("dw_relu", "dw")
+    b.conv("grp", "dw", "grp", 32, 48, 3, stride=1, pad=1, group=4)           # grouped: direct kernel
+    b.conv("odd", "grp", "odd", 48, 10, 1)                                    # 10 outputs: unaligned rows
+    b.conv("odd2", "odd", "odd2", 10, 6, 3, pad=1)                            # 10 input channels: direct kernel
+    weights = wl.init_params(b.params, seed=1)
+    x = {"data": np.random.default_rng(2).standard_normal((3, 32, 17, 19)).astype(np.float32)}
+    outs = ["dw", "grp", "odd", "odd2"]
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, outs, marks=outs)
+    for name in outs:
+        assert_close(got[name], want[name], name)
+
+
+@pytest.mark.parametrize("method,k,stride,pad,size", [
+    ("MAX", 3, 2, 0, (112, 112)), ("MAX", 2, 2, 0, (75, 75)), ("MAX", 3, 1, 1, (19, 19)),
+    ("AVE", 3, 2, 1, (14, 15)), ("AVE", 2, 2, 1, (9, 9)), ("MAX", 3, 2, 1, (13, 11)),
+])
+def test_pooling_variants(capi, gpu_engine, reflib, method, k, stride, pad, size):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("pool")
+    c = 24
+    b.input([("data", (2, c, size[0], size[1]))])
+    b.pool("p", "data", "p", method, k=k, stride=stride, pad=pad)
+    x = {"data": np.random.default_rng(3).standard_normal((2, c, size[0], size[1])).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, {}, x, ["p"])
+    assert got["p"].shape == want["p"].shape
+    assert np.abs(got["p"] - want["p"]).max() <= 1e-6
+
+
+def test_global_pooling_odd_channels(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("gap")
+    b.input([("data", (2, 7, 5, 6))])
+    b.pool("g", "data", "g", "AVE", global_pooling=True)
+    b.pool("m", "data", "m", "MAX", global_pooling=True)
+    x = {"data": np.random.default_rng(4).standard_normal((2, 7, 5, 6)).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, {}, x, ["g", "m"], marks=["g"])
+    assert np.abs(got["g"] - want["g"]).max() <= 1e-6
+    assert np.array_equal(got["m"], want["m"])
+
+
+def test_softmax_axes(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("sm")
+    b.input([("a", (4, 21, 5, 3)), ("b", (3, 50, 21))])
+    b.softmax("s1", "a", "s1", axis=1)
+    b.softmax("s2", "b", "s2", axis=2)
+    b.softmax("s3", "b", "s3", axis=1)
+    rng = np.random.default_rng(5)
+    x = {"a": rng.standard_normal((4, 21, 5, 3)).astype(np.float32) * 3,
+         "b": rng.standard_normal((3, 50, 21)).astype(np.float32) * 3}
+    got, want = both(capi, gpu_engine, reflib, b, {}, x, ["s1", "s2", "s3"], marks=["s1", "s2"])
+    for name in ("s1", "s2", "s3"):
+        assert np.abs(got[name] - want[name]).max() <= 2e-6, name
+
+
+def test_standalone_elementwise_layers(capi, gpu_engine, reflib):
+    """BatchNorm / Scale / Bias / ReLU / PReLU / Eltwise not behind a convolution (no fusion)."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("elt")
+    b.input([("x", (2, 12, 7, 9)), ("y", (2, 12, 7, 9))])
+    b.batch_norm("bn", "x", 12)
+    b.scale("sc", "x", 12)
+    b.raw("lrelu", "ReLU", ["x"], ["lrelu"], "relu_param { negative_slope: 0.1 }")
+    b.raw("pr", "PReLU", ["y"], ["pr"])
+    b.params.append(("pr_0", (12,), "he", 4))
+    b.raw("bias", "Bias", ["pr"], ["bias"], "bias_param { axis: 1 }")
+    b.params.append(("bias_0", (12,), "he", 4))
+    b.raw("sum", "Eltwise", ["lrelu", "bias"], ["sum"], "eltwise_param { operation: SUM coeff: 0.5 coeff: -2 }")
+    b.raw("prod", "Eltwise", ["lrelu", "bias"], ["prod"], "eltwise_param { operation: PROD }")
+    b.raw("mx", "Eltwise", ["lrelu", "bias", "sum"], ["mx"], "eltwise_param { operation: MAX }")
+    b.raw("cat", "Concat", ["sum", "prod", "mx"], ["cat"], "concat_param { axis: 1 }")
+    b.raw("cat2", "Concat", ["sum", "prod"], ["cat2"], "concat_param { axis: 2 }")
+    weights = wl.init_params(b.params, seed=6, bn_identity=False)
+    rng = np.random.default_rng(7)
+    x = {"x": rng.standard_normal((2, 12, 7, 9)).astype(np.float32),
+         "y": rng.standard_normal((2, 12, 7, 9)).astype(np.float32)}
+    outs = ["lrelu", "pr", "bias", "sum", "prod", "mx", "cat", "cat2"]
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, outs, marks=outs)
+    for name in outs:
+        assert np.abs(got[name] - want[name]).max() <= 1e-5, name
+
+
+def test_prelu_fused_behind_convolution(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("convprelu")
+    b.input([("data", (2, 16, 12, 12))])
+    b.conv("c", "data", "c", 16, 40, 3, pad=1)
+    b.raw("pr", "PReLU", ["c"], ["c"])
+    b.params.append(("pr_0", (40,), "he", 4))
+    b.raw("sh", "PReLU", ["c"], ["sh"], "prelu_param { channel_shared: true }")
+    b.params.append(("sh_0", (), "he", 4))
+    weights = wl.init_params(b.params, seed=8)
+    x = {"data": np.random.default_rng(9).standard_normal((2, 16, 12, 12)).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["c", "sh"], marks=["c"])
+    assert_close(got["c"], want["c"], "conv+prelu")
+    assert_close(got["sh"], want["sh"], "shared prelu")
+
+
+def test_normalize_permute_flatten_reshape(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("misc")
+    b.input([("data", (2, 20, 6, 5))])
+    b.raw("norm", "Normalize", ["data"], ["norm"], "norm_param { across_spatial: false channel_shared: false }")
+    b.params.append(("norm_0", (20,), "norm_scale", 0))
+    b.raw("perm", "Permute", ["norm"], ["perm"], "permute_param { order: 0 order: 2 order: 3 order: 1 }")
+    b.raw("perm2", "Permute", ["norm"], ["perm2"], "permute_param { order: 1 order: 0 order: 3 order: 2 }")
+    b.raw("flat", "Flatten", ["perm"], ["flat"], "flatten_param { axis: 1 }")
+    b.raw("resh", "Reshape", ["flat"], ["resh"], "reshape_param { shape { dim: 0 dim: -1 dim: 4 } }")
+    b.raw("split", "Split", ["norm"], ["s1", "s2"])
+    x = {"data": np.random.default_rng(10).standard_normal((2, 20, 6, 5)).astype(np.float32)}
+    outs = ["norm", "perm", "perm2", "flat", "resh", "s1", "s2"]
+    weights = wl.init_params(b.params, seed=1)
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, outs, marks=outs)
+    for name in outs:
+        assert got[name].shape == want[name].shape, name
+        assert np.abs(got[name] - want[name]).max() <= 2e-5, name
+
+
+def test_inner_product_variants(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("ip")
+    b.input([("data", (5, 8, 3, 4))])
+    b.inner_product("fc1", "data", "fc1", 96, 33)                 # flattens (C, H, W) in NCHW order
+    b.relu("fc1_relu", "fc1")
+    b.raw("fc2", "InnerProduct", ["fc1"], ["fc2"], "inner_product_param { num_output: 7 bias_term: false transpose: true }")
+    b.params.append(("fc2_0", (33, 7), "he", 33))
+    b.inner_product("fc3", "fc2", "fc3", 7, 5)                     # K = 7: not a multiple of four
+    weights = wl.init_params(b.params, seed=11)
+    x = {"data": np.random.default_rng(12).standard_normal((5, 8, 3, 4)).astype(np.float32)}
+    outs = ["fc1", "fc2", "fc3"]
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, outs, marks=outs)
+    for name in outs:
+        assert_close(got[name], want[name], name)
+
+
+def test_weights_can_change_between_passes(capi, gpu_engine, reflib):
+    """Folded scale/shift arrays and packed weights must follow writes through Net::params()."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("reload")
+    b.input([("data", (1, 8, 10, 10))])
+    b.conv_bn("c", "data", "c", 8, 16, 3, pad=1, bn_prefix="bn_", scale_prefix="scale_")
+    x = {"data": np.random.default_rng(13).standard_normal((1, 8, 10, 10)).astype(np.float32)}
+    eng = capi.Net(gpu_engine, b.text(), None, from_buffer=True)
+    ref = capi.Net(reflib, b.text(), None, from_buffer=True)
+    for seed in (1, 2):
+        w = wl.init_params(b.params, seed=seed, bn_identity=False)
+        eng.set_params(w)
+        ref.set_params(w)
+        eng.forward(**x)
+        ref.forward(**x)
+        assert_close(eng.blob("c").data.copy(), ref.blob("c").data.copy(), "pass %d" % seed)
+    eng.close()
+    ref.close()
+
+
+def test_mobilenet_v1_batch2(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.mobilenet_v1(2)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.normal_image_input(2, seed=0)
+    outs = ["fc7", "prob"]
+    marks = ["conv2_dw", "conv6_pw", "conv14_pw"]
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, outs + marks, marks=marks)
+    for name in marks + outs:
+        assert_close(got[name], want[name], name)
+
+
+def test_resnet50_batch16(capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.resnet50(16)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.image_input(16, seed=1)
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["fc1000"], marks=["res3d"])
+    assert_close(got["fc1000"], want["fc1000"], "fc1000")
+    # same top-1 class wherever the reference's margin between its two best logits is not tiny
+    top = np.sort(want["fc1000"], axis=1)
+    clear = (top[:, -1] - top[:, -2]) > 2e-2 * np.abs(top[:, -1])
+    assert (np.argmax(got["fc1000"], 1)[clear] == np.argmax(want["fc1000"], 1)[clear]).all()
