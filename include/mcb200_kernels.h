@@ -224,6 +224,33 @@ int mcb200_proposal_forward(const mcb200_proposal_params* p, int batch, const fl
                             const float* im_info, const float* anchors, void* workspace, float* rois,
                             float* roi_scores, int* counts, void* stream);
 
+/* The same computation as mcb200_proposal_forward for callers that cannot
+ * allocate device memory.  (It has no counterpart in mini-caffe.)
+ *
+ * Who needs it: code that runs inside a host program which has already handed
+ * all device memory to its own pool, so that a cudaMalloc of the workspace
+ * would fail or fight with that pool; and latency-critical loops that must not
+ * hit the device-wide synchronisation a cudaMalloc / cudaFree implies.  Such
+ * callers still own their inputs and outputs; only the scratch is taken off
+ * their hands.
+ *
+ * The scratch is a fixed 8 MiB array inside the library's device image (each
+ * GPU that loads the library holds it until the process exits).  That covers
+ * one image with up to 65536 proposals and pre_nms_topn up to 6000 (the stock
+ * R-FCN / Faster-RCNN settings need 6.5 MB); a request that needs more returns
+ * -20 and prints the required size.  The function calls no cudaMalloc, cudaFree
+ * or any other allocating routine.
+ *
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress) and keeps it; make that first call before starting any
+ * stream capture.  All calls share the one array: two calls whose kernels may
+ * overlap on the GPU (different streams, or different host threads without
+ * ordering) race on it -- serialise them.  Nothing in the array needs to be
+ * zero on entry, it is not cleared, and it keeps the last call's contents.     */
+int mcb200_proposal_forward_static(const mcb200_proposal_params* p, int batch, const float* scores,
+                                   const float* deltas, const float* im_info, const float* anchors, float* rois,
+                                   float* roi_scores, int* counts, void* stream);
+
 /* ------------------------------------------------------------------ SSD detection output */
 typedef struct mcb200_detout_params {
   int num_priors, num_classes;

@@ -17,6 +17,9 @@
 // proposal index (the CPU quicksort leaves that order unspecified).
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+
+#include <mutex>
 
 #include "../../../include/mcb200_kernels.h"
 #include "detection.cuh"
@@ -366,4 +369,54 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
     count_launch();
   }
   return static_cast<int>(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------ variant without allocation
+
+// Scratch of mcb200_proposal_forward_static.  It lives in the library's device
+// image: every GPU that loads the library carries these 8 MiB until the process
+// exits.  Enough for one image with up to 65536 proposals of which up to 6000
+// go to NMS (6.5 MB); larger requests are refused.
+static constexpr size_t kStaticScratchBytes = static_cast<size_t>(8) << 20;
+static __device__ __align__(256) unsigned char g_proposal_static_scratch[kStaticScratchBytes];
+
+extern "C" int mcb200_proposal_forward_static(const mcb200_proposal_params* p, int batch, const float* scores,
+                                              const float* deltas, const float* im_info, const float* anchors,
+                                              float* rois, float* roi_scores, int* counts, void* stream) {
+  const int rc = validate(p, batch);
+  if (rc != 0) return rc;
+  const size_t need = carve(*p, batch, nullptr, nullptr);
+  if (need > kStaticScratchBytes) {
+    fprintf(stderr,
+            "mcb200_proposal_forward_static: this request needs %zu bytes of scratch, the built-in buffer holds %zu; "
+            "use mcb200_proposal_forward with a caller-provided workspace\n",
+            need, kStaticScratchBytes);
+    return -20;
+  }
+  // In host code the array's name is only a handle; the device address has to be
+  // asked for, once per device, with that device current.
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -21;
+  static void* scratch_of_device[64] = {nullptr};
+  static std::mutex mu;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_proposal_static_scratch);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (!ptr) return -22;
+      scratch_of_device[dev] = ptr;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  // Every scratch word the kernels read is written earlier in the same call
+  // (keys, boxes and scores for all proposals, the sorted copies for the best
+  // pre_nms_topn, and the mask words on and above the diagonal, which are the
+  // only ones the scan reads), so nothing has to be cleared between calls.
+  return mcb200_proposal_forward(p, batch, scores, deltas, im_info, anchors, scratch, rois, roi_scores, counts,
+                                 stream);
 }
