@@ -80,11 +80,6 @@ struct SmemPlan {
   static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024;  // + alignment slack
 };
 
-__device__ __forceinline__ float apply_act(float v, int act, float slope) {
-  if (act != 0) v = v > 0.f ? v : v * slope;
-  return v;
-}
-
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ... (n fastest, so
 // the CTAs running at one time share activation tiles through L2).  Two
 // accumulators in tensor memory let the tensor core start the next tile while
