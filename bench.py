@@ -144,6 +144,54 @@ def cpu_reference_rate(capi, wl, steps, warmup, budget_s):
             "ms_per_step": dt / steps * 1e3, "batch": per_step}
 
 
+def secondary_figures(capi, wl, engine, L, stream, torch):
+    """The two other figures the benchmark definition names, measured after the headline:
+    NMS boxes/s of the RPN Proposal stress case (63x38 map, 15 anchors, pre-NMS 6000, 32 images in
+    one call) and the TF32 rate of the single 3x3 64->64 convolution at batch 32."""
+    out = {}
+    # Proposal: boxes/s := images * min(pre_nms_topn, A*H*W) / time of the whole layer forward
+    images = 32
+    b = wl.proposal(num_anchors=15)
+    text = b.text().replace("dim: 1 dim: 30", "dim: %d dim: 30" % images).replace(
+        "dim: 1 dim: 60", "dim: %d dim: 60" % images).replace("dim: 1 dim: 3 }", "dim: %d dim: 3 }" % images)
+    net = capi.Net(engine, text, None, from_buffer=True)
+    import numpy as np
+    batches = [wl.proposal_input(num_anchors=15, seed=i)[0] for i in range(images)]
+    feed = {k: np.concatenate([x[k] for x in batches], axis=0) for k in batches[0]}
+    net.forward(**feed)
+    for _ in range(3):
+        engine.check(L.CaffeNetForward(net.handle))
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    ev0.record(stream)
+    for _ in range(reps):
+        engine.check(L.CaffeNetForward(net.handle))
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / reps
+    n_all = 15 * 63 * 38
+    out["proposal"] = {"images_per_call": images, "ms_per_call": ms, "rois": int(net.blob("rois").shape[0]),
+                       "nms_boxes_per_s": images * min(6000, n_all) / (ms * 1e-3),
+                       "decoded_boxes_per_s": images * n_all / (ms * 1e-3),
+                       "iou_pairs_upper_bound_per_image": 6000 * 5999 // 2}
+    net.close()
+    # Config 1: Convolution(64, 3x3, pad 1) + ReLU on [32, 64, 56, 56]
+    cb = wl.conv_relu(32)
+    net = capi.Net(engine, cb.text(), None, from_buffer=True)
+    net.set_params(wl.init_params(cb.params, seed=0))
+    net.forward(**wl.conv_relu_input(32, seed=0))
+    L.mcb200_kernel_timing_begin()
+    for _ in range(20):
+        engine.check(L.CaffeNetForward(net.handle))
+    conv_ms = ctypes.c_double(0.0)
+    n = int(L.mcb200_kernel_timing_end(ctypes.byref(conv_ms)))
+    flops = 2 * 32 * 64 * 56 * 56 * 64 * 9
+    out["conv_relu_b32"] = {"kernel_ms": conv_ms.value / max(1, n), "tf32_tflops": flops / (conv_ms.value / max(1, n) * 1e-3) / 1e12,
+                            "algorithmic_bytes": 4 * (2 * 32 * 64 * 56 * 56 + 64 * 64 * 9 + 64)}
+    net.close()
+    return out
+
+
 def run_reference_arm(args, capi, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -294,6 +342,9 @@ def main():
         "share_of_step": conv_s_per_step * 1e3 / ms_per_step,
     }
 
+    # ---- secondary figures of the benchmark definition (rank 0, after the headline) ----
+    extras = secondary_figures(capi, wl, engine, L, stream, torch) if rank == 0 else None
+
     # ---- final output gather (outside the timed loops) ----
     probs = torch.from_numpy(prob_blob.data.copy()).cuda()
     if world > 1:
@@ -316,7 +367,7 @@ def main():
                              % (conv_bytes / 1e9),
                        "flops_per_image": wl.resnet50_flops_per_image(), "gathered_output_rows": gathered_rows},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "secondary": extras,
             "cpu_baseline": cpu if cpu else {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
                                              "sample": "oracle/_ref not built"},
         }
