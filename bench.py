@@ -65,7 +65,7 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.index = index
         self.samples = []
-        self.reasons = set()
+        self.first_sample = threading.Event()
         self.stop_flag = threading.Event()
         self.proc = None
 
@@ -73,7 +73,7 @@ class ClockSampler(threading.Thread):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -84,14 +84,19 @@ class ClockSampler(threading.Thread):
             if len(parts) < 7:
                 continue
             try:
-                self.samples.append((float(parts[0]), float(parts[1])))
+                sample = (time.monotonic(), float(parts[0]), float(parts[1]))
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[3:7]):
-                if flag.lower().startswith("active"):
-                    self.reasons.add(name)
+            active = [name for name, flag in zip(names, parts[3:7]) if flag.lower().startswith("active")]
+            self.samples.append(sample + (active,))
+            self.first_sample.set()
 
-    def finish(self):
+    def wait_ready(self, timeout=5.0):
+        """Blocks until nvidia-smi has delivered its first line (its start-up takes a while)."""
+        self.first_sample.wait(timeout)
+
+    def finish(self, windows):
+        """Summary over the samples that fall inside the timed windows [(t0, t1), ...] (time.monotonic)."""
         self.stop_flag.set()
         if self.proc is not None:
             self.proc.terminate()   # the exact child started above
@@ -100,10 +105,16 @@ class ClockSampler(threading.Thread):
             except subprocess.TimeoutExpired:
                 self.proc.kill()
         if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        busy = [s for s, _ in self.samples]
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(m for _, m in self.samples),
-                "reasons": sorted(self.reasons), "samples": len(busy)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        inside = [s for s in self.samples if any(t0 <= s[0] <= t1 for t0, t1 in windows)]
+        scope = "timed regions"
+        if not inside:   # regions shorter than the sampling period: take the samples around them
+            lo, hi = min(t0 for t0, _ in windows) - 0.05, max(t1 for _, t1 in windows) + 0.05
+            inside = [s for s in self.samples if lo <= s[0] <= hi] or self.samples
+            scope = "around the timed regions"
+        reasons = sorted({r for s in inside for r in s[3]})
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": max(s[2] for s in inside),
+                "reasons": reasons, "samples": len(inside), "scope": scope}
 
 
 def build_resnet(capi, wl, library, batch):
@@ -213,7 +224,7 @@ def run_reference_arm(args, capi, wl):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU,
@@ -286,17 +297,19 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-        time.sleep(0.3)
+        sampler.wait_ready()
+    windows = []
     barrier()
     L.mcb200_launch_count_reset()
+    w0 = time.monotonic()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
     for _ in range(args.steps):
         forward()
     ev1.record(stream)
     barrier()
+    windows.append((w0, time.monotonic()))
     launches = int(L.mcb200_launch_count())
-    clocks = sampler.finish() if sampler else None
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_per_step = ms_total / args.steps
     value = world * batch * args.steps / (ms_total * 1e-3)
@@ -306,6 +319,7 @@ def main():
         data_blob.data  # marks the pinned host copy as the current one
         forward()
     barrier()
+    w0 = time.monotonic()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         data_blob.data
@@ -313,6 +327,8 @@ def main():
         prob_blob.data
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    windows.append((w0, time.monotonic()))
+    clocks = sampler.finish(windows) if sampler else None
     e2e_value = world * batch * args.steps / e2e_s
     h2d = int(np.prod(x.shape)) * 4
     d2h = int(np.prod(prob_blob.shape)) * 4
@@ -369,7 +385,8 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "secondary": extras,
             "cpu_baseline": cpu if cpu else {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
-                                             "sample": "oracle/_ref not built"},
+                                             "sample": "skipped (--no-cpu-baseline)" if args.no_cpu_baseline
+                                             else "oracle/_ref not built"},
         }
         print(json.dumps(line))
     net.close()

@@ -3,23 +3,27 @@
 //   D[m, co] = sum over taps (r, s) and channels c of  X[pixel(m) + (r, s), c] * W[co, r, s, c]
 //
 // m runs over the N*Ho*Wo output pixels of a channels-last activation tensor.
-// One CTA computes a 128 x BN tile of D:
-//   warp 0   one elected thread issues the TMA loads.  The activation tile
-//            (128 pixels x 32 channels of one filter tap) comes through an
+// One CTA computes 128 x BN tiles of D, one after the other (persistent):
+//   warp 0   one elected thread issues the activation loads.  The tile (128
+//            pixels x 32 channels of one filter tap) comes through an
 //            im2col-mode tensor map, so the hardware walks the output pixels
-//            across image rows and images and zero-fills the padding; the
-//            weight tile (BN x 32) comes through a tiled map.  Both land in
-//            shared memory 128-byte swizzled, K-major.
+//            across image rows and images and zero-fills the padding.
+//   warp 2   one elected thread issues the weight loads (BN x 32, tiled map).
+//            Both operands land in shared memory 128-byte swizzled, K-major.
+//            Two issuing threads because a single thread's loop (wait, arm the
+//            barrier, issue) costs a few hundred cycles per k-iteration, which
+//            is as long as the copy itself takes.
 //   warp 1   one thread issues tcgen05.mma kind::tf32 (M=128, N=BN, K=8), four per
 //            stage, accumulating in tensor memory; tcgen05.commit hands each
-//            shared-memory stage back to the producer.
-//   warps 2-5 read the accumulator out of tensor memory (tcgen05.ld), apply
+//            shared-memory stage back to the producers.
+//   warps 3-10 read the accumulator out of tensor memory (tcgen05.ld), apply
 //            the fused tail (per-channel scale/shift, residual add, ReLU or
-//            PReLU) and store channels-last.  Each warp stages its 32 x 32
-//            sub-tiles in shared memory (128-byte swizzled, reusing the
-//            pipeline stages once the last MMA has retired) so that the
-//            residual comes in and the result goes out as whole 128-byte rows
-//            through TMA tile loads / stores, double buffered per warp.
+//            PReLU) and store channels-last.  Two warps share each 32-lane
+//            quadrant of tensor memory and take alternate 32-column chunks.
+//            Each warp stages its 32 x 32 sub-tiles in shared memory (128-byte
+//            swizzled) so that the residual comes in and the result goes out as
+//            whole 128-byte rows through TMA tile loads / stores, double
+//            buffered per warp.
 // Every barrier wait is bounded; a timed-out wait raises an abort flag, the
 // roles drain, tensor memory is freed and *status is set.
 //
@@ -44,7 +48,15 @@ using namespace sm100;
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 32;                            // fp32 elements = one 128-byte swizzle row
 constexpr int kTileABytes = kBlockM * kBlockK * 4;     // 16 KiB
-constexpr int kThreads = 192;
+// Warp roles.  A warp may only read the tensor-memory lanes [32 * (warp % 4), +32),
+// so the eight epilogue warps form four pairs that share a lane quadrant and split
+// the 32-column chunks of a tile between them (even / odd).
+constexpr int kWarpLoadA = 0;
+constexpr int kWarpMma = 1;
+constexpr int kWarpLoadB = 2;
+constexpr int kFirstEpilogueWarp = 3;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;   // 352
 constexpr long long kWaitLimitCycles = 2000000000LL;   // about one second
 // How the activation tile of a k-iteration is fetched.
 constexpr int kModeMatrix = 0;   // rows of a plain [m, c] matrix (1x1 convolution, inner product)
@@ -73,17 +85,32 @@ struct SmemPlan {
   static constexpr int kTileBBytes = BN * kBlockK * 4;
   static constexpr int kStageBytes = kTileABytes + kTileBBytes;
   // One persistent CTA per SM.  Shared memory = operand ring + per-warp
-  // epilogue staging ring (kResSlots x 4 KiB for each of the four warps).
+  // epilogue staging ring (kSlots x 4 KiB for each of the eight warps).
   static constexpr int kStages = (BN == 256) ? 3 : (BN == 128 ? 4 : 6);
-  static constexpr int kResSlots = (BN == 128) ? 5 : 4;
-  static constexpr int kStagingBytes = 4 * kResSlots * 4096;
+  static constexpr int kSlots = 2;
+  static constexpr int kStagingBytes = kEpilogueWarps * kSlots * 4096;
   static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024;  // + alignment slack
+};
+
+// Ring position of a k-iteration: stage index and the parity of its use.
+// Advancing it costs an increment and a compare; the single-thread loops
+// below are latency-bound on exactly this kind of scalar work.
+template <int kStages>
+struct RingPos {
+  int stage = 0;
+  uint32_t parity = 0;
+  __device__ __forceinline__ void advance() {
+    if (++stage == kStages) {
+      stage = 0;
+      parity ^= 1u;
+    }
+  }
 };
 
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ... (n fastest, so
 // the CTAs running at one time share activation tiles through L2).  Two
 // accumulators in tensor memory let the tensor core start the next tile while
-// the epilogue warps drain the previous one; the TMA producer runs ahead across
+// the epilogue warps drain the previous one; the TMA producers run ahead across
 // tile boundaries.
 template <int BN, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -92,14 +119,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const ConvTcArgs args) {
   using Plan = SmemPlan<BN>;
   constexpr int kStages = Plan::kStages;
-  constexpr int kResSlots = Plan::kResSlots;
+  constexpr int kSlots = Plan::kSlots;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[kStages];
-  __shared__ uint64_t empty_bar[kStages];
+  __shared__ uint64_t full_bar[kStages];       // both operand tiles of a stage have landed (two producers)
+  __shared__ uint64_t empty_bar[kStages];      // the MMAs reading a stage have retired
   __shared__ uint64_t tmem_full_bar[2];
   __shared__ uint64_t tmem_empty_bar[2];
-  __shared__ uint64_t res_bar[4][kResSlots];   // per epilogue warp, per staging slot
+  __shared__ uint64_t res_bar[kEpilogueWarps][kSlots];   // per epilogue warp, per staging slot
   __shared__ uint64_t col_bar[2];              // per-column table of a tile is complete
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -122,21 +149,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], 2);
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 4);   // one arrival per epilogue warp
-      mbar_init(&col_bar[b], 4);
+      mbar_init(&tmem_empty_bar[b], kEpilogueWarps);   // one arrival per epilogue warp
+      mbar_init(&col_bar[b], kEpilogueWarps);
     }
-    for (int w = 0; w < 4; ++w)
-      for (int r = 0; r < kResSlots; ++r) mbar_init(&res_bar[w][r], 1);
+    for (int w = 0; w < kEpilogueWarps; ++w)
+      for (int r = 0; r < kSlots; ++r) mbar_init(&res_bar[w][r], 1);
     fence_barrier_init();
     tma_prefetch_descriptor(&map_a);
     tma_prefetch_descriptor(&map_b);
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tmem_alloc(&tmem_base_slot, 2 * BN);
     tmem_relinquish();
   }
@@ -146,15 +173,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort = &abort_flag;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  // After an abort: give a producer's copies that are still in flight a bounded
+  // time to land before the CTA's shared memory is released.
+  auto drain_loads = [&](int issued) {
+    if (!*abort) return;
+    const int first = issued > kStages ? issued - kStages : 0;
+    for (int j = first; j < issued; ++j) {
+      const long long start = clock64();
+      while (!mbar_try_wait(&full_bar[j % kStages], static_cast<uint32_t>(j / kStages) & 1u)) {
+        if (clock64() - start > kWaitLimitCycles / 8) break;
+      }
+    }
+  };
+
+  if (warp == kWarpLoadA) {
+    // ------------------------------------------------------------ activation tiles
     if (elect_one()) {
-      int it = 0;   // k-iterations issued so far, over all tiles of this CTA
+      RingPos<kStages> pos;
+      int issued = 0;
       bool alive = true;
+      const uint32_t a_bytes = static_cast<uint32_t>(args.a_bytes);
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         const int mt = tile / n_tiles;
         const int m0 = mt * kBlockM;
-        const int n0 = (tile % n_tiles) * BN;
         int base_w = 0, base_h = 0, base_n = 0;
         if (kMode == kModeRows) {
           base_n = mt / args.ho;
@@ -167,48 +208,77 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           base_w = q * args.stride_w - args.pad_w;
           base_h = p * args.stride_h - args.pad_h;
         }
-        for (int k = 0; k < args.k_iters; ++k, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
-          if (!mbar_wait_bounded(&empty_bar[s], phase ^ 1u, abort, kWaitLimitCycles)) { alive = false; break; }
-          uint8_t* a_dst = tiles + s * Plan::kStageBytes;
-          uint8_t* b_dst = a_dst + kTileABytes;
-          mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(args.a_bytes) + Plan::kTileBBytes);
-          const int tap = k / args.c_blocks;
-          const int cb = k - tap * args.c_blocks;
+        // Position inside the filter, advanced incrementally: channel block,
+        // then tap column, then tap row.
+        int c0 = 0, sx = 0;
+        uint16_t off_w = 0, off_h = 0;
+        int row_h = base_h;
+        for (int k = 0; k < args.k_iters; ++k) {
+          if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
+            alive = false;
+            break;
+          }
+          uint8_t* a_dst = tiles + pos.stage * Plan::kStageBytes;
+          uint64_t* bar = &full_bar[pos.stage];
+          mbar_expect_tx(bar, a_bytes);
           if (kMode == kModeRows) {
             // k is the filter row: tile_rows pixels x (8 pixels x 4 channels) of input row base_h + k * dil_h.
-            tma_load_4d(&map_a, &full_bar[s], a_dst, 0, 0, base_h + k * args.dil_h, base_n);
+            tma_load_4d(&map_a, bar, a_dst, 0, 0, row_h, base_n);
+            row_h += args.dil_h;
           } else if (kMode == kModeIm2col) {
-            const int r = tap / args.kw;
-            const int sx = tap - r * args.kw;
-            tma_load_im2col_4d(&map_a, &full_bar[s], a_dst, cb * kBlockK, base_w, base_h, base_n,
-                               static_cast<uint16_t>(sx * args.dil_w), static_cast<uint16_t>(r * args.dil_h));
+            tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
+            c0 += kBlockK;
+            if (c0 >= args.c_blocks * kBlockK) {
+              c0 = 0;
+              off_w = static_cast<uint16_t>(off_w + args.dil_w);
+              if (++sx == args.kw) {
+                sx = 0;
+                off_w = 0;
+                off_h = static_cast<uint16_t>(off_h + args.dil_h);
+              }
+            }
           } else {
-            tma_load_2d(&map_a, &full_bar[s], a_dst, cb * kBlockK, m0);
+            tma_load_2d(&map_a, bar, a_dst, c0, m0);
+            c0 += kBlockK;
           }
-          tma_load_2d(&map_b, &full_bar[s], b_dst, k * kBlockK, n0);
+          ++issued;
+          pos.advance();
         }
       }
-      if (*abort) {
-        // Give copies that are still in flight a bounded time to land before
-        // the CTA's shared memory is released.
-        const int first = it > kStages ? it - kStages : 0;
-        for (int j = first; j < it; ++j) {
-          const long long start = clock64();
-          while (!mbar_try_wait(&full_bar[j % kStages], static_cast<uint32_t>(j / kStages) & 1u)) {
-            if (clock64() - start > kWaitLimitCycles / 8) break;
-          }
-        }
-      }
+      drain_loads(issued);
     }
-  } else if (warp == 1) {
+  } else if (warp == kWarpLoadB) {
+    // ------------------------------------------------------------ weight tiles
+    if (elect_one()) {
+      RingPos<kStages> pos;
+      int issued = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        const int n0 = (tile % n_tiles) * BN;
+        int k0 = 0;
+        for (int k = 0; k < args.k_iters; ++k) {
+          if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
+            alive = false;
+            break;
+          }
+          uint64_t* bar = &full_bar[pos.stage];
+          mbar_expect_tx(bar, Plan::kTileBBytes);
+          tma_load_2d(&map_b, bar, tiles + pos.stage * Plan::kStageBytes + kTileABytes, k0, n0);
+          k0 += kBlockK;
+          ++issued;
+          pos.advance();
+        }
+      }
+      drain_loads(issued);
+    }
+  } else if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_tf32(kBlockM, BN);
-      int it = 0;
+      RingPos<kStages> pos;
       int local = 0;   // tiles done by this CTA
       bool alive = true;
+      const uint32_t tiles_addr = smem_addr(tiles);
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
         const int ab = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
@@ -216,66 +286,97 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!mbar_wait_bounded(&tmem_empty_bar[ab], use ^ 1u, abort, kWaitLimitCycles)) break;
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN);
-        for (int k = 0; k < args.k_iters; ++k, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = static_cast<uint32_t>(it / kStages) & 1u;
-          if (!mbar_wait_bounded(&full_bar[s], phase, abort, kWaitLimitCycles)) { alive = false; break; }
+        uint32_t accumulate = 0;
+        for (int k = 0; k < args.k_iters; ++k) {
+          if (!mbar_wait_bounded(&full_bar[pos.stage], pos.parity, abort, kWaitLimitCycles)) {
+            alive = false;
+            break;
+          }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_addr(tiles + s * Plan::kStageBytes);
-          const uint32_t b_addr = a_addr + kTileABytes;
+          const uint32_t a_addr = tiles_addr + static_cast<uint32_t>(pos.stage * Plan::kStageBytes);
           const uint64_t desc_a = umma_desc_k_sw128(a_addr);
-          const uint64_t desc_b = umma_desc_k_sw128(b_addr);
+          const uint64_t desc_b = umma_desc_k_sw128(a_addr + kTileABytes);
 #pragma unroll
           for (int kk = 0; kk < kBlockK / 8; ++kk) {
             // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
             // descriptor's 16-byte address units.
-            umma_tf32(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            umma_tf32(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+            accumulate = 1u;
           }
-          umma_commit(&empty_bar[s]);
+          umma_commit(&empty_bar[pos.stage]);
+          pos.advance();
         }
         if (alive) umma_commit(&tmem_full_bar[ab]);
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    const int ew = warp - kFirstEpilogueWarp;   // 0..7: staging ring and barriers of this warp
     const int quad = warp & 3;                  // tensor-memory lanes [32*quad, 32*quad+32)
+    const int half = ew >> 2;                   // chunks half, half + 2, ... of every tile
     const mcb200_epilogue& ep = args.ep;
     const bool has_res = ep.residual != nullptr;
-    uint8_t* staging = staging_base + quad * (kResSlots * 4096);
+    uint8_t* staging = staging_base + ew * (kSlots * 4096);
     auto slot_ptr = [&](int slot) { return reinterpret_cast<float*>(staging + slot * 4096); };
     const int chunks_full = BN / 32;
-    const int epi_tid = threadIdx.x - 64;       // 0..127 over the four epilogue warps
+    const int epi_tid = threadIdx.x - kFirstEpilogueWarp * 32;   // 0..255 over the epilogue warps
     // 0: no activation, 1: plain ReLU, 2: per-column negative slope (leaky ReLU / PReLU)
     const int act_mode = ep.act == 0 ? 0 : ((ep.act == 1 && ep.slope == 0.f) ? 1 : 2);
 
     // Chunk sequence of this warp: for each of its CTA's tiles, the 32-column
-    // chunks that exist (the last n-tile may have fewer), left to right.  `seq`
-    // numbers them; chunk seq uses staging slot seq % kResSlots.  The residual
-    // prefetch cursor (lane 0 only) walks the same sequence kResSlots - 1 ahead.
-    int pre_local = 0, pre_chunk = 0, pre_seq = 0;
-    auto issue_residual = [&]() {
-      const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(pre_local) * gridDim.x;
-      if (tile >= num_tiles) return;
-      const int mt = static_cast<int>(tile / n_tiles);
-      const int tile_n0 = static_cast<int>(tile % n_tiles) * BN;
-      const int slot = pre_seq % kResSlots;
-      mbar_expect_tx(&res_bar[quad][slot], 4096);
-      if (kMode == kModeRows) {
-        tma_load_3d(&map_res, &res_bar[quad][slot], slot_ptr(slot), tile_n0 + pre_chunk * 32, quad * 32, mt);
-      } else {
-        tma_load_3d(&map_res, &res_bar[quad][slot], slot_ptr(slot), tile_n0 + pre_chunk * 32, mt * kBlockM + quad * 32,
-                    0);
+    // chunks it owns that exist (the last n-tile may have fewer), left to right.
+    // `seq` numbers them; chunk seq uses staging slot seq % kSlots.  Two cursors
+    // of lane 0 walk the same sequence ahead of the computation: `pf` asks L2 for
+    // the residual sub-tiles kResidualL2Ahead chunks early (the layers that add a
+    // residual stream it from DRAM exactly once, so nothing else would bring it
+    // close), `ld` copies the next chunk's sub-tile into its staging slot.
+    struct ChunkCursor {
+      int local;
+      int chunk;
+    };
+    auto cursor_next = [&](ChunkCursor& cur, int& mt, int& col) {
+      for (;;) {
+        const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(cur.local) * gridDim.x;
+        if (tile >= num_tiles) return false;
+        mt = static_cast<int>(tile / n_tiles);
+        col = static_cast<int>(tile - static_cast<long long>(mt) * n_tiles) * BN + cur.chunk * 32;
+        if (cur.chunk >= chunks_full || col >= args.cout) {   // this warp's chunks of the tile are done
+          cur.chunk = half;
+          ++cur.local;
+          continue;
+        }
+        cur.chunk += 2;
+        return true;
       }
-      ++pre_seq;
-      ++pre_chunk;
-      if (pre_chunk >= chunks_full || tile_n0 + pre_chunk * 32 >= args.cout) {
-        pre_chunk = 0;
-        ++pre_local;
+    };
+    constexpr int kResidualL2Ahead = 8;
+    ChunkCursor pf = {0, half}, ld = {0, half};
+    int ld_seq = 0;
+    auto prefetch_residual = [&]() {
+      int mt, col;
+      if (!cursor_next(pf, mt, col)) return;
+      if (kMode == kModeRows) {
+        tma_prefetch_l2_3d(&map_res, col, quad * 32, mt);
+      } else {
+        tma_prefetch_l2_3d(&map_res, col, mt * kBlockM + quad * 32, 0);
+      }
+    };
+    auto issue_residual = [&]() {
+      int mt, col;
+      if (!cursor_next(ld, mt, col)) return;
+      const int slot = ld_seq % kSlots;
+      ++ld_seq;
+      mbar_expect_tx(&res_bar[ew][slot], 4096);
+      if (kMode == kModeRows) {
+        tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, quad * 32, mt);
+      } else {
+        tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, mt * kBlockM + quad * 32, 0);
       }
     };
     const bool staged = args.tma_epilogue != 0;
     if (staged && has_res && lane == 0) {
-      for (int i = 0; i < kResSlots - 1; ++i) issue_residual();
+      for (int i = 0; i < kResidualL2Ahead; ++i) prefetch_residual();
+      issue_residual();
     }
 
     int seq = 0;
@@ -285,7 +386,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int ab = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
       const int mt = tile / n_tiles;
-      const int n0 = (tile % n_tiles) * BN;
+      const int n0 = (tile - mt * n_tiles) * BN;
       // First output row (pixel) of this warp's 32-row slice, and how many of the 32 exist.
       const int row0 = (kMode == kModeRows ? mt * args.tile_rows : mt * kBlockM) + quad * 32;
       const int rows_here = kMode == kModeRows ? args.tile_rows - quad * 32 : args.m - row0;
@@ -295,15 +396,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float* t_scale = col_scale[ab];
       float* t_shift = col_shift[ab];
       float* t_slope = col_slope[ab];
-      for (int c = epi_tid; c < BN; c += 128) {
+      for (int c = epi_tid; c < BN; c += kEpilogueWarps * 32) {
         const int cc = n0 + c;
         const bool in = cc < args.cout;
         t_scale[c] = (in && ep.scale) ? __ldg(ep.scale + cc) : 1.f;
         t_shift[c] = (in && ep.shift) ? __ldg(ep.shift + cc) : 0.f;
         t_slope[c] = ep.act == 2 ? ((in && ep.prelu) ? __ldg(ep.prelu + (ep.prelu_shared ? 0 : cc)) : 0.f) : ep.slope;
       }
-      // Rendezvous of the four epilogue warps on the table (an mbarrier rather
-      // than a named barrier, so that the wait is bounded like every other one).
+      // Rendezvous of the epilogue warps on the table (an mbarrier rather than a
+      // named barrier, so that the wait is bounded like every other one).
       __syncwarp();
       if (lane == 0) mbar_arrive(&col_bar[ab]);
       alive = __all_sync(0xffffffffu, mbar_wait_bounded(&col_bar[ab], use, abort, kWaitLimitCycles));
@@ -315,7 +416,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN) + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
-      for (int chunk = 0; chunk < chunks_full; ++chunk) {
+      for (int chunk = half; chunk < chunks_full; chunk += 2) {
         const int col0 = n0 + chunk * 32;
         if (col0 >= args.cout) break;          // uniform across the warp
         const int g = seq++;
@@ -360,16 +461,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           return v;
         };
         if (staged) {
-          const int slot = g % kResSlots;
+          const int slot = g % kSlots;
           float* buf = slot_ptr(slot) + lane * 32;
           if (has_res) {
+            if (lane == 0) {
+              // The other slot is free once the previous chunk's store has read
+              // it: start the next chunk's residual on its way before working
+              // on this one.
+              tma_store_wait_read<0>();
+              issue_residual();
+              prefetch_residual();
+            }
             alive = __all_sync(0xffffffffu,
-                               mbar_wait_bounded(&res_bar[quad][slot], static_cast<uint32_t>(g / kResSlots) & 1u,
-                                                 abort, kWaitLimitCycles));
+                               mbar_wait_bounded(&res_bar[ew][slot], static_cast<uint32_t>(g / kSlots) & 1u, abort,
+                                                 kWaitLimitCycles));
             if (!alive) break;
-          } else if (g >= kResSlots) {
+          } else if (g >= kSlots) {
             // The store that last used this slot must have finished reading it.
-            if (lane == 0) tma_store_wait_read<kResSlots - 1>();
+            if (lane == 0) tma_store_wait_read<kSlots - 1>();
             __syncwarp();
           }
           // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
@@ -398,12 +507,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tma_store_3d(&map_out, slot_ptr(slot), col0, row0, 0);
             }
             tma_store_commit();
-            if (has_res) {
-              // The slot of the previous chunk is reloaded (for the chunk
-              // kResSlots - 1 ahead) once its store has finished reading it.
-              tma_store_wait_read<1>();
-              issue_residual();
-            }
           }
         } else {
           // ---- plain stores (rows not 16-byte aligned) ----
@@ -443,7 +546,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // ------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 2 * BN);
   }
@@ -541,7 +644,7 @@ CUresult encode_tile_map(CUtensorMap* map, const float* base, int cols, int ld, 
   const cuuint32_t box[3] = {32, 32, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   return api.tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
