@@ -78,29 +78,39 @@ struct ConvTcArgs {
   int tma_epilogue;  // output (and residual) meet the 16-byte rules of TMA tiles
   int tile_rows;     // valid rows of an M tile: 128, or the output width in row mode
   int a_bytes;       // bytes one activation tile load delivers
+  int stages;        // depth of the operand ring (2 .. kMaxStages)
+  int slots;         // staging slots per epilogue warp (1 or 2)
 };
 
+constexpr int kMaxStages = 8;
+constexpr int kMaxSlots = 2;
+constexpr int kSharedLimit = 232448;   // 227 KiB: the most one CTA can have on sm_100
+
+// Shared memory of one persistent CTA = operand ring (`stages` x (A tile + B
+// tile)) + epilogue staging (`slots` x 4 KiB for each of the eight warps).  The
+// copies in flight are what hides the round trip of a stage (L2 -> shared
+// memory, barrier hop, MMA completion, barrier hop: about a microsecond), so
+// the ring takes every byte the epilogue can spare: launches that add a
+// residual, or whose tiles are short (few k-iterations per epilogue), double
+// buffer the staging; all others give that memory to the ring.
 template <int BN>
 struct SmemPlan {
   static constexpr int kTileBBytes = BN * kBlockK * 4;
   static constexpr int kStageBytes = kTileABytes + kTileBBytes;
-  // One persistent CTA per SM.  Shared memory = operand ring + per-warp
-  // epilogue staging ring (kSlots x 4 KiB for each of the eight warps).
-  static constexpr int kStages = (BN == 256) ? 3 : (BN == 128 ? 4 : 6);
-  static constexpr int kSlots = 2;
-  static constexpr int kStagingBytes = kEpilogueWarps * kSlots * 4096;
-  static constexpr int kDynamicBytes = kStages * kStageBytes + kStagingBytes + 1024;  // + alignment slack
+  static constexpr int staging_bytes(int slots) { return kEpilogueWarps * slots * 4096; }
+  static constexpr int dynamic_bytes(int stages, int slots) {
+    return stages * kStageBytes + staging_bytes(slots) + 1024;   // + alignment slack
+  }
 };
 
 // Ring position of a k-iteration: stage index and the parity of its use.
 // Advancing it costs an increment and a compare; the single-thread loops
 // below are latency-bound on exactly this kind of scalar work.
-template <int kStages>
 struct RingPos {
   int stage = 0;
   uint32_t parity = 0;
-  __device__ __forceinline__ void advance() {
-    if (++stage == kStages) {
+  __device__ __forceinline__ void advance(int stages) {
+    if (++stage == stages) {
       stage = 0;
       parity ^= 1u;
     }
@@ -118,15 +128,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
                const ConvTcArgs args) {
   using Plan = SmemPlan<BN>;
-  constexpr int kStages = Plan::kStages;
-  constexpr int kSlots = Plan::kSlots;
+  const int stages = args.stages;
+  const int slots = args.slots;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[kStages];       // both operand tiles of a stage have landed (two producers)
-  __shared__ uint64_t empty_bar[kStages];      // the MMAs reading a stage have retired
+  __shared__ uint64_t full_bar[kMaxStages];    // both operand tiles of a stage have landed (two producers)
+  __shared__ uint64_t empty_bar[kMaxStages];   // the MMAs reading a stage have retired
   __shared__ uint64_t tmem_full_bar[2];
   __shared__ uint64_t tmem_empty_bar[2];
-  __shared__ uint64_t res_bar[kEpilogueWarps][kSlots];   // per epilogue warp, per staging slot
+  __shared__ uint64_t res_bar[kEpilogueWarps][kMaxSlots];   // per epilogue warp, per staging slot
   __shared__ uint64_t col_bar[2];              // per-column table of a tile is complete
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -137,7 +147,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
   const uint32_t raw_addr = smem_addr(smem_raw);
   uint8_t* tiles = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint8_t* staging_base = tiles + kStages * Plan::kStageBytes;
+  uint8_t* staging_base = tiles + stages * Plan::kStageBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -148,7 +158,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 2);
       mbar_init(&empty_bar[s], 1);
     }
@@ -158,7 +168,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&col_bar[b], kEpilogueWarps);
     }
     for (int w = 0; w < kEpilogueWarps; ++w)
-      for (int r = 0; r < kSlots; ++r) mbar_init(&res_bar[w][r], 1);
+      for (int r = 0; r < kMaxSlots; ++r) mbar_init(&res_bar[w][r], 1);
     fence_barrier_init();
     tma_prefetch_descriptor(&map_a);
     tma_prefetch_descriptor(&map_b);
@@ -177,10 +187,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // time to land before the CTA's shared memory is released.
   auto drain_loads = [&](int issued) {
     if (!*abort) return;
-    const int first = issued > kStages ? issued - kStages : 0;
+    const int first = issued > stages ? issued - stages : 0;
     for (int j = first; j < issued; ++j) {
       const long long start = clock64();
-      while (!mbar_try_wait(&full_bar[j % kStages], static_cast<uint32_t>(j / kStages) & 1u)) {
+      while (!mbar_try_wait(&full_bar[j % stages], static_cast<uint32_t>(j / stages) & 1u)) {
         if (clock64() - start > kWaitLimitCycles / 8) break;
       }
     }
@@ -189,7 +199,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == kWarpLoadA) {
     // ------------------------------------------------------------ activation tiles
     if (elect_one()) {
-      RingPos<kStages> pos;
+      RingPos pos;
       int issued = 0;
       bool alive = true;
       const uint32_t a_bytes = static_cast<uint32_t>(args.a_bytes);
@@ -242,7 +252,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             c0 += kBlockK;
           }
           ++issued;
-          pos.advance();
+          pos.advance(stages);
         }
       }
       drain_loads(issued);
@@ -250,7 +260,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == kWarpLoadB) {
     // ------------------------------------------------------------ weight tiles
     if (elect_one()) {
-      RingPos<kStages> pos;
+      RingPos pos;
       int issued = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
@@ -266,7 +276,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tma_load_2d(&map_b, bar, tiles + pos.stage * Plan::kStageBytes + kTileABytes, k0, n0);
           k0 += kBlockK;
           ++issued;
-          pos.advance();
+          pos.advance(stages);
         }
       }
       drain_loads(issued);
@@ -275,7 +285,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_tf32(kBlockM, BN);
-      RingPos<kStages> pos;
+      RingPos pos;
       int local = 0;   // tiles done by this CTA
       bool alive = true;
       const uint32_t tiles_addr = smem_addr(tiles);
@@ -304,7 +314,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             accumulate = 1u;
           }
           umma_commit(&empty_bar[pos.stage]);
-          pos.advance();
+          pos.advance(stages);
         }
         if (alive) umma_commit(&tmem_full_bar[ab]);
       }
@@ -316,7 +326,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int half = ew >> 2;                   // chunks half, half + 2, ... of every tile
     const mcb200_epilogue& ep = args.ep;
     const bool has_res = ep.residual != nullptr;
-    uint8_t* staging = staging_base + ew * (kSlots * 4096);
+    uint8_t* staging = staging_base + ew * (slots * 4096);
     auto slot_ptr = [&](int slot) { return reinterpret_cast<float*>(staging + slot * 4096); };
     const int chunks_full = BN / 32;
     const int epi_tid = threadIdx.x - kFirstEpilogueWarp * 32;   // 0..255 over the epilogue warps
@@ -325,7 +335,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     // Chunk sequence of this warp: for each of its CTA's tiles, the 32-column
     // chunks it owns that exist (the last n-tile may have fewer), left to right.
-    // `seq` numbers them; chunk seq uses staging slot seq % kSlots.  Two cursors
+    // `seq` numbers them; chunk seq uses staging slot seq % 2 (residual launches
+    // always have two slots).  Two cursors
     // of lane 0 walk the same sequence ahead of the computation: `pf` asks L2 for
     // the residual sub-tiles kResidualL2Ahead chunks early (the layers that add a
     // residual stream it from DRAM exactly once, so nothing else would bring it
@@ -364,7 +375,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto issue_residual = [&]() {
       int mt, col;
       if (!cursor_next(ld, mt, col)) return;
-      const int slot = ld_seq % kSlots;
+      const int slot = ld_seq & 1;
       ++ld_seq;
       mbar_expect_tx(&res_bar[ew][slot], 4096);
       if (kMode == kModeRows) {
@@ -461,7 +472,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           return v;
         };
         if (staged) {
-          const int slot = g % kSlots;
+          const int slot = slots == 2 ? (g & 1) : 0;
           float* buf = slot_ptr(slot) + lane * 32;
           if (has_res) {
             if (lane == 0) {
@@ -473,12 +484,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               prefetch_residual();
             }
             alive = __all_sync(0xffffffffu,
-                               mbar_wait_bounded(&res_bar[ew][slot], static_cast<uint32_t>(g / kSlots) & 1u, abort,
+                               mbar_wait_bounded(&res_bar[ew][slot], static_cast<uint32_t>(g >> 1) & 1u, abort,
                                                  kWaitLimitCycles));
             if (!alive) break;
-          } else if (g >= kSlots) {
+          } else if (g >= slots) {
             // The store that last used this slot must have finished reading it.
-            if (lane == 0) tma_store_wait_read<kSlots - 1>();
+            if (lane == 0) {
+              if (slots == 2) {
+                tma_store_wait_read<1>();
+              } else {
+                tma_store_wait_read<0>();
+              }
+            }
             __syncwarp();
           }
           // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
@@ -649,23 +666,39 @@ CUresult encode_tile_map(CUtensorMap* map, const float* base, int cols, int ld, 
 }
 
 template <int BN, int kMode>
-cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args, cudaStream_t stream) {
+cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaStream_t stream) {
   using Plan = SmemPlan<BN>;
   // The large-shared-memory opt-in is per device: do it once for each device
-  // this process launches on.
+  // this process launches on.  What the ring may use is the CTA limit minus the
+  // kernel's static shared memory (barriers, per-column tables).
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured[64] = {false};
+  static int dynamic_limit = 0;
   static std::mutex mu;
   {
     std::lock_guard<std::mutex> lock(mu);
+    if (dynamic_limit == 0) {
+      cudaFuncAttributes attr;
+      cudaError_t e = cudaFuncGetAttributes(&attr, conv_tc_kernel<BN, kMode>);
+      if (e != cudaSuccess) return e;
+      dynamic_limit = kSharedLimit - static_cast<int>(attr.sharedSizeBytes);
+    }
     if (dev >= 0 && dev < 64 && !configured[dev]) {
       cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<BN, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           Plan::kDynamicBytes);
+                                           dynamic_limit);
       if (e != cudaSuccess) return e;
       configured[dev] = true;
     }
   }
+  // Two staging slots when the epilogue is the busy part (a residual to bring
+  // in, or few k-iterations per tile); otherwise one, and a deeper ring.
+  args.slots = (args.ep.residual != nullptr || args.k_iters < 16) ? 2 : 1;
+  int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots)) / Plan::kStageBytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  args.stages = stages;
+  const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots);
   const long long m_tiles = kMode == kModeRows ? static_cast<long long>(plan->shape.n) * plan->shape.ho
                                                : (plan->m + kBlockM - 1) / kBlockM;
   const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * m_tiles;
@@ -685,7 +718,7 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, const ConvTcArgs& args,
   const CUtensorMap* mr = reinterpret_cast<const CUtensorMap*>(plan->tma_res);
   {
     TimedLaunch timed(stream);
-    conv_tc_kernel<BN, kMode><<<grid, kThreads, Plan::kDynamicBytes, stream>>>(*ma, *mb, *mo, *mr, args);
+    conv_tc_kernel<BN, kMode><<<grid, kThreads, dynamic_bytes, stream>>>(*ma, *mb, *mo, *mr, args);
   }
   count_launch();
   return cudaGetLastError();
