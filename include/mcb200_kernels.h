@@ -85,7 +85,8 @@ typedef struct mcb200_conv_plan {
   mcb200_conv_shape shape;
   int m, k_iters, c_blocks, block_n;
   int im2col;               /* 0 matrix rows, 1 im2col tensor map, 2 row mode      */
-  int out_ld, res_ld, reserved;
+  int out_ld, res_ld;
+  int cta_pair;             /* 1: launched as two-CTA clusters (tcgen05 cta_group::2) */
   const float* out_ptr;
   const float* res_ptr;
 } __attribute__((aligned(64))) mcb200_conv_plan;

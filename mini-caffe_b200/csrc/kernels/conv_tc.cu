@@ -33,6 +33,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "../../../include/mcb200_kernels.h"
@@ -93,10 +95,17 @@ constexpr int kSharedLimit = 232448;   // 227 KiB: the most one CTA can have on 
 // the ring takes every byte the epilogue can spare: launches that add a
 // residual, or whose tiles are short (few k-iterations per epilogue), double
 // buffer the staging; all others give that memory to the ring.
-template <int BN>
+template <int BN, int kMode, bool kPair>
 struct SmemPlan {
-  static constexpr int kTileBBytes = BN * kBlockK * 4;
-  static constexpr int kStageBytes = kTileABytes + kTileBBytes;
+  static constexpr int kTileBRows = kPair ? BN / 2 : BN;   // a CTA of a pair holds half of the weight tile
+  static constexpr int kTileBBytes = kTileBRows * kBlockK * 4;
+  // K = 32 sub-tiles per stage.  Every stage costs each single-thread role a
+  // barrier wait and a signal (a few hundred cycles of pure latency), so where
+  // a K = 32 step is short (narrow tiles) a stage carries two of them.
+  // (Row mode has few, odd numbers of k-iterations per tile: single steps.)
+  static constexpr int kSub = (kMode != kModeRows && kTileABytes + kTileBBytes <= 24 * 1024) ? 2 : 1;
+  static constexpr int kStageBytes = kSub * (kTileABytes + kTileBBytes);
+  static constexpr int kStageBOffset = kSub * kTileABytes;   // [A sub-tiles][B sub-tiles]
   static constexpr int staging_bytes(int slots) { return kEpilogueWarps * slots * 4096; }
   static constexpr int dynamic_bytes(int stages, int slots) {
     return stages * kStageBytes + staging_bytes(slots) + 1024;   // + alignment slack
@@ -122,12 +131,22 @@ struct RingPos {
 // accumulators in tensor memory let the tensor core start the next tile while
 // the epilogue warps drain the previous one; the TMA producers run ahead across
 // tile boundaries.
-template <int BN, int kMode>
+//
+// kPair: the CTAs of a cluster of two share one tcgen05.mma.cta_group::2 per
+// K=8 step.  The pair works on 256 output pixels (128 per CTA) x BN channels;
+// each CTA fetches its own activation tile and only half of the weight tile, the
+// rank-0 CTA issues the MMAs for both, and each CTA drains its own half of the
+// result from its own tensor memory.  Weight bytes per MAC halve, which is what
+// bounds the layers whose operands come out of L2 faster than the ring can
+// turn over.  Barriers that both CTAs signal (stage full, accumulator drained)
+// live in rank 0; tcgen05.commit multicasts the arrivals that both CTAs wait on.
+template <int BN, int kMode, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
                const ConvTcArgs args) {
-  using Plan = SmemPlan<BN>;
+  static_assert(!(kPair && kMode == kModeRows), "row mode runs unpaired");
+  using Plan = SmemPlan<BN, kMode, kPair>;
   const int stages = args.stages;
   const int slots = args.slots;
 
@@ -154,17 +173,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int n_tiles = (args.cout + BN - 1) / BN;
   // Row mode: an M tile is one output row of one image (tile_rows <= 128 pixels).
   const int m_tiles = kMode == kModeRows ? args.m / args.tile_rows : (args.m + kBlockM - 1) / kBlockM;
-  const int num_tiles = n_tiles * m_tiles;
+  // A work unit is an M tile (or a pair of neighbouring M tiles) x an N tile;
+  // `worker` is the CTA (or pair) index among `workers`.
+  const uint32_t rank = kPair ? cluster_cta_rank() : 0u;
+  const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int m_units = kPair ? (m_tiles + 1) >> 1 : m_tiles;
+  const int num_tiles = n_tiles * m_units;
+  auto unit_to_mt = [&](int unit) { return kPair ? 2 * unit + static_cast<int>(rank) : unit; };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 2);
+      mbar_init(&full_bar[s], 2);                      // one arrival per producer thread of this CTA
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], kEpilogueWarps);   // one arrival per epilogue warp
+      mbar_init(&tmem_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);   // one arrival per epilogue warp
       mbar_init(&col_bar[b], kEpilogueWarps);
     }
     for (int w = 0; w < kEpilogueWarps; ++w)
@@ -178,10 +204,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (kPair) {
+    cluster_sync_all();   // the peer's barriers are initialised before anything signals them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort = &abort_flag;
+  // A paired MMA writes the same tensor-memory address in both CTAs.  Each CTA
+  // makes the first and only allocation of its SM, which starts at column 0;
+  // anything else is refused rather than computed wrongly.
+  const bool usable = !kPair || tmem_base == 0u;
+  if (!usable && threadIdx.x == 0) abort_flag = 1;
+  // Cluster-window addresses of rank 0's shared barriers.
+  const uint32_t full_bar_leader = kPair ? cluster_map(smem_addr(&full_bar[0]), 0u) : 0u;
+  const uint32_t tmem_empty_leader = kPair ? cluster_map(smem_addr(&tmem_empty_bar[0]), 0u) : 0u;
 
   // After an abort: give a producer's copies that are still in flight a bounded
   // time to land before the CTA's shared memory is released.
@@ -196,16 +234,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   };
 
-  if (warp == kWarpLoadA) {
+  if (!usable) {
+    // fall through to the teardown; the peer's waits run out and it follows
+  } else if (warp == kWarpLoadA) {
     // ------------------------------------------------------------ activation tiles
     if (elect_one()) {
       RingPos pos;
       int issued = 0;
       bool alive = true;
       const uint32_t a_bytes = static_cast<uint32_t>(args.a_bytes);
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const int mt = tile / n_tiles;
+      for (int tile = worker; tile < num_tiles && alive; tile += workers) {
+        const int mt = unit_to_mt(tile / n_tiles);
         const int m0 = mt * kBlockM;
+        // The odd M tile out at the end of a paired launch has no pixels: its
+        // CTA loads nothing, and the MMA computes rows nobody stores.
+        const bool live = !kPair || mt < m_tiles;
+        // Only rank 0's barrier counts bytes: its producers announce what both
+        // CTAs are about to fetch, the peer's copies just report completion
+        // there (a remote arrival per k-iteration would cost the peer's
+        // producer a cluster-scope release, about a microsecond each).
+        const uint32_t announce =
+            !kPair ? a_bytes : (rank != 0u ? 0u : (mt + 1 < m_tiles ? 2u * a_bytes : a_bytes));
         int base_w = 0, base_h = 0, base_n = 0;
         if (kMode == kModeRows) {
           base_n = mt / args.ho;
@@ -223,33 +272,48 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int c0 = 0, sx = 0;
         uint16_t off_w = 0, off_h = 0;
         int row_h = base_h;
-        for (int k = 0; k < args.k_iters; ++k) {
+        for (int k = 0; k < args.k_iters; k += Plan::kSub) {
           if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
             alive = false;
             break;
           }
+          const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
           uint8_t* a_dst = tiles + pos.stage * Plan::kStageBytes;
           uint64_t* bar = &full_bar[pos.stage];
-          mbar_expect_tx(bar, a_bytes);
-          if (kMode == kModeRows) {
-            // k is the filter row: tile_rows pixels x (8 pixels x 4 channels) of input row base_h + k * dil_h.
-            tma_load_4d(&map_a, bar, a_dst, 0, 0, row_h, base_n);
-            row_h += args.dil_h;
-          } else if (kMode == kModeIm2col) {
-            tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
-            c0 += kBlockK;
-            if (c0 >= args.c_blocks * kBlockK) {
-              c0 = 0;
-              off_w = static_cast<uint16_t>(off_w + args.dil_w);
-              if (++sx == args.kw) {
-                sx = 0;
-                off_w = 0;
-                off_h = static_cast<uint16_t>(off_h + args.dil_h);
+          const uint32_t bar_leader = full_bar_leader + static_cast<uint32_t>(pos.stage) * 8u;
+          if (rank == 0u) mbar_expect_tx(bar, announce * static_cast<uint32_t>(nsub));
+#pragma unroll
+          for (int j = 0; j < Plan::kSub; ++j) {
+            if (j >= nsub) break;
+            if (kMode == kModeRows) {
+              // A sub-tile is one filter row: tile_rows pixels x (8 pixels x 4 channels) of a padded input row.
+              tma_load_4d(&map_a, bar, a_dst, 0, 0, row_h, base_n);
+              row_h += args.dil_h;
+            } else if (kMode == kModeIm2col) {
+              if (kPair) {
+                if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
+              } else {
+                tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
               }
+              c0 += kBlockK;
+              if (c0 >= args.c_blocks * kBlockK) {
+                c0 = 0;
+                off_w = static_cast<uint16_t>(off_w + args.dil_w);
+                if (++sx == args.kw) {
+                  sx = 0;
+                  off_w = 0;
+                  off_h = static_cast<uint16_t>(off_h + args.dil_h);
+                }
+              }
+            } else {
+              if (kPair) {
+                if (live) tma_load_2d_pair(&map_a, bar_leader, a_dst, c0, m0);
+              } else {
+                tma_load_2d(&map_a, bar, a_dst, c0, m0);
+              }
+              c0 += kBlockK;
             }
-          } else {
-            tma_load_2d(&map_a, bar, a_dst, c0, m0);
-            c0 += kBlockK;
+            a_dst += kTileABytes;
           }
           ++issued;
           pos.advance(stages);
@@ -263,18 +327,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       RingPos pos;
       int issued = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const int n0 = (tile % n_tiles) * BN;
+      for (int tile = worker; tile < num_tiles && alive; tile += workers) {
+        // A CTA of a pair fetches the half of the weight tile that matches its rank.
+        const int n0 = (tile % n_tiles) * BN + static_cast<int>(rank) * Plan::kTileBRows;
         int k0 = 0;
-        for (int k = 0; k < args.k_iters; ++k) {
+        for (int k = 0; k < args.k_iters; k += Plan::kSub) {
           if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
             alive = false;
             break;
           }
+          const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
+          uint8_t* b_dst = tiles + pos.stage * Plan::kStageBytes + Plan::kStageBOffset;
           uint64_t* bar = &full_bar[pos.stage];
-          mbar_expect_tx(bar, Plan::kTileBBytes);
-          tma_load_2d(&map_b, bar, tiles + pos.stage * Plan::kStageBytes + kTileABytes, k0, n0);
-          k0 += kBlockK;
+          const uint32_t bar_leader = full_bar_leader + static_cast<uint32_t>(pos.stage) * 8u;
+          // Rank 0 announces both halves of a paired weight tile.
+          if (rank == 0u) mbar_expect_tx(bar, (kPair ? 2u : 1u) * Plan::kTileBBytes * static_cast<uint32_t>(nsub));
+#pragma unroll
+          for (int j = 0; j < Plan::kSub; ++j) {
+            if (j >= nsub) break;
+            if (kPair) {
+              tma_load_2d_pair(&map_b, bar_leader, b_dst, k0, n0);
+            } else {
+              tma_load_2d(&map_b, bar, b_dst, k0, n0);
+            }
+            k0 += kBlockK;
+            b_dst += Plan::kTileBBytes;
+          }
           ++issued;
           pos.advance(stages);
         }
@@ -283,13 +361,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_tf32(kBlockM, BN);
+    if ((!kPair || rank == 0u) && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_tf32(kPair ? 2 * kBlockM : kBlockM, BN);
       RingPos pos;
       int local = 0;   // tiles done by this CTA
       bool alive = true;
       const uint32_t tiles_addr = smem_addr(tiles);
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+      for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
         const int ab = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
         // The epilogue must have drained this accumulator (first use passes).
@@ -297,26 +375,47 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN);
         uint32_t accumulate = 0;
-        for (int k = 0; k < args.k_iters; ++k) {
+        for (int k = 0; k < args.k_iters; k += Plan::kSub) {
           if (!mbar_wait_bounded(&full_bar[pos.stage], pos.parity, abort, kWaitLimitCycles)) {
             alive = false;
             break;
           }
           tc_fence_after_sync();
+          const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
           const uint32_t a_addr = tiles_addr + static_cast<uint32_t>(pos.stage * Plan::kStageBytes);
-          const uint64_t desc_a = umma_desc_k_sw128(a_addr);
-          const uint64_t desc_b = umma_desc_k_sw128(a_addr + kTileABytes);
+          uint64_t desc_a = umma_desc_k_sw128(a_addr);
+          uint64_t desc_b = umma_desc_k_sw128(a_addr + Plan::kStageBOffset);
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / 8; ++kk) {
-            // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
-            // descriptor's 16-byte address units.
-            umma_tf32(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
-            accumulate = 1u;
+          for (int j = 0; j < Plan::kSub; ++j) {
+            if (j >= nsub) break;
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 8; ++kk) {
+              // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
+              // descriptor's 16-byte address units.
+              if (kPair) {
+                umma_tf32_pair(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+              } else {
+                umma_tf32(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+              }
+              accumulate = 1u;
+            }
+            desc_a += kTileABytes >> 4;            // next sub-tile (start address is in 16-byte units)
+            desc_b += Plan::kTileBBytes >> 4;
           }
-          umma_commit(&empty_bar[pos.stage]);
+          if (kPair) {
+            umma_commit_pair(&empty_bar[pos.stage], 3);   // both CTAs' producers wait on their own copy
+          } else {
+            umma_commit(&empty_bar[pos.stage]);
+          }
           pos.advance(stages);
         }
-        if (alive) umma_commit(&tmem_full_bar[ab]);
+        if (alive) {
+          if (kPair) {
+            umma_commit_pair(&tmem_full_bar[ab], 3);
+          } else {
+            umma_commit(&tmem_full_bar[ab]);
+          }
+        }
       }
     }
   } else {
@@ -347,10 +446,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     };
     auto cursor_next = [&](ChunkCursor& cur, int& mt, int& col) {
       for (;;) {
-        const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(cur.local) * gridDim.x;
+        const long long tile = static_cast<long long>(worker) + static_cast<long long>(cur.local) * workers;
         if (tile >= num_tiles) return false;
-        mt = static_cast<int>(tile / n_tiles);
-        col = static_cast<int>(tile - static_cast<long long>(mt) * n_tiles) * BN + cur.chunk * 32;
+        const int unit = static_cast<int>(tile / n_tiles);
+        mt = unit_to_mt(unit);
+        col = static_cast<int>(tile - static_cast<long long>(unit) * n_tiles) * BN + cur.chunk * 32;
         if (cur.chunk >= chunks_full || col >= args.cout) {   // this warp's chunks of the tile are done
           cur.chunk = half;
           ++cur.local;
@@ -393,11 +493,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int seq = 0;
     int local = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+    for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
       const int ab = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
-      const int mt = tile / n_tiles;
-      const int n0 = (tile - mt * n_tiles) * BN;
+      const int unit = tile / n_tiles;
+      const int mt = unit_to_mt(unit);
+      const int n0 = (tile - unit * n_tiles) * BN;
       // First output row (pixel) of this warp's 32-row slice, and how many of the 32 exist.
       const int row0 = (kMode == kModeRows ? mt * args.tile_rows : mt * kBlockM) + quad * 32;
       const int rows_here = kMode == kModeRows ? args.tile_rows - quad * 32 : args.m - row0;
@@ -554,15 +655,28 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // All of this warp's reads of the accumulator are complete: hand it back.
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty_bar[ab]);
+      if (lane == 0) {
+        if (kPair) {
+          mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(ab) * 8u);
+        } else {
+          mbar_arrive(&tmem_empty_bar[ab]);
+        }
+      }
     }
     if (staged && lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown
+  // A pair leaves together: until both CTAs are here, the peer may still
+  // signal this CTA's barriers or (rank 0's MMAs) write its tensor memory.
   tc_fence_before_sync();
-  __syncthreads();
+  __syncwarp();
+  if (kPair) {
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 2 * BN);
@@ -647,6 +761,18 @@ int pick_block_n(int cout, long long m, int k_iters) {
   return best;
 }
 
+// Whether two-CTA clusters run the layer.  Pairing halves the weight bytes each
+// SM pulls per MAC, which pays where the operand ring bounds the main loop (wide
+// tiles, long K) and there are at least two M tiles to pair up.  Short-K layers
+// are bound by their epilogue and only pay for the pair's extra synchronisation
+// (measured on ResNet-50: gains from 16 k-iterations up when no residual is
+// added, losses at 4-16 with one).
+int pick_cta_pair(int block_n, long long m, int k_iters) {
+  const char* force = getenv("MCB200_CTA_PAIR");   // "0" / "1": override for experiments
+  if (force && (force[0] == '0' || force[0] == '1')) return block_n >= 128 && force[0] == '1' ? 1 : 0;
+  return (block_n >= 128 && m > kBlockM && k_iters > 16) ? 1 : 0;
+}
+
 // Tile map for the staged epilogue over a row-major fp32 matrix with row pitch
 // `ld`, 32 x 32 boxes, 128-byte swizzle.  The rows are split as (group, row in
 // group): ordinary tiles use one group of all rows; row mode uses one group per
@@ -665,29 +791,33 @@ CUresult encode_tile_map(CUtensorMap* map, const float* base, int cols, int ld, 
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <int BN, int kMode>
+template <int BN, int kMode, bool kPair>
 cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaStream_t stream) {
-  using Plan = SmemPlan<BN>;
+  using Plan = SmemPlan<BN, kMode, kPair>;
+  auto kernel = conv_tc_kernel<BN, kMode, kPair>;
   // The large-shared-memory opt-in is per device: do it once for each device
   // this process launches on.  What the ring may use is the CTA limit minus the
   // kernel's static shared memory (barriers, per-column tables).
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured[64] = {false};
+  static int sm_count[64] = {0};
   static int dynamic_limit = 0;
   static std::mutex mu;
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dynamic_limit == 0) {
       cudaFuncAttributes attr;
-      cudaError_t e = cudaFuncGetAttributes(&attr, conv_tc_kernel<BN, kMode>);
+      cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
       if (e != cudaSuccess) return e;
       dynamic_limit = kSharedLimit - static_cast<int>(attr.sharedSizeBytes);
     }
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<BN, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           dynamic_limit);
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_limit);
       if (e != cudaSuccess) return e;
+      int n = 0;
+      if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+      sm_count[dev] = n;
       configured[dev] = true;
     }
   }
@@ -701,27 +831,42 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots);
   const long long m_tiles = kMode == kModeRows ? static_cast<long long>(plan->shape.n) * plan->shape.ho
                                                : (plan->m + kBlockM - 1) / kBlockM;
-  const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * m_tiles;
-  if (tiles > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  // One persistent CTA per SM (fewer when there are fewer tiles).
-  static int sm_count[64] = {0};
-  if (dev >= 0 && dev < 64 && sm_count[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
-    sm_count[dev] = n;
-  }
-  const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
-  dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms), 1, 1);
+  const long long m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
+  const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * m_units;
+  if (tiles > 0x3fffffffLL) return cudaErrorInvalidConfiguration;
+  // One persistent CTA per SM (fewer when there are fewer tiles); a paired
+  // launch is a grid of two-CTA clusters, one cluster per tile at a time.
+  const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
+  const long long workers_max = kPair ? sms / 2 : sms;
+  const unsigned workers = static_cast<unsigned>(tiles < workers_max ? tiles : workers_max);
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
   const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);
   const CUtensorMap* mr = reinterpret_cast<const CUtensorMap*>(plan->tma_res);
+  cudaError_t launched;
   {
     TimedLaunch timed(stream);
-    conv_tc_kernel<BN, kMode><<<grid, kThreads, dynamic_bytes, stream>>>(*ma, *mb, *mo, *mr, args);
+    if (kPair) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(workers * 2, 1, 1);
+      cfg.blockDim = dim3(kThreads, 1, 1);
+      cfg.dynamicSmemBytes = static_cast<size_t>(dynamic_bytes);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      launched = cudaLaunchKernelEx(&cfg, kernel, *ma, *mb, *mo, *mr, args);
+    } else {
+      kernel<<<dim3(workers, 1, 1), kThreads, dynamic_bytes, stream>>>(*ma, *mb, *mo, *mr, args);
+      launched = cudaGetLastError();
+    }
   }
   count_launch();
-  return cudaGetLastError();
+  return launched;
 }
 
 }  // namespace
@@ -772,7 +917,7 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   plan->shape = *s;
   plan->out_ptr = nullptr;
   plan->res_ptr = nullptr;
-  plan->out_ld = plan->res_ld = plan->reserved = 0;
+  plan->out_ld = plan->res_ld = plan->cta_pair = 0;
   if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
@@ -780,6 +925,7 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   plan->c_blocks = (s->c + kBlockK - 1) / kBlockK;
   plan->k_iters = s->kh * s->kw * plan->c_blocks;
   plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
+  plan->cta_pair = pick_cta_pair(plan->block_n, plan->m, plan->k_iters);
   const bool pointwise = s->kh == 1 && s->kw == 1 && s->stride_h == 1 && s->stride_w == 1 && s->pad_h == 0 &&
                          s->pad_w == 0;
   plan->im2col = pointwise ? 0 : 1;
@@ -822,7 +968,8 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
     const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kBlockK;
     const cuuint64_t dims[2] = {kp, static_cast<cuuint64_t>(s->cout)};
     const cuuint64_t strides[1] = {kp * 4};
-    const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(plan->block_n)};
+    // A CTA of a pair fetches half of the weight tile.
+    const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(plan->cta_pair ? plan->block_n / 2 : plan->block_n)};
     const cuuint32_t estr[2] = {1, 1};
     r = api.tiled(mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(packed_w), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -888,16 +1035,29 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
   a.a_bytes = a.tile_rows * kBlockK * 4;
   cudaError_t e = cudaErrorInvalidValue;
   const int mode = plan->im2col;
-#define MCB200_DISPATCH(BN)                                                     \
-  e = mode == kModeRows     ? launch_variant<BN, kModeRows>(plan, a, st)        \
-      : mode == kModeIm2col ? launch_variant<BN, kModeIm2col>(plan, a, st)      \
-                            : launch_variant<BN, kModeMatrix>(plan, a, st)
+#define MCB200_DISPATCH(BN)                                                            \
+  e = mode == kModeRows     ? launch_variant<BN, kModeRows, false>(plan, a, st)        \
+      : mode == kModeIm2col ? launch_variant<BN, kModeIm2col, false>(plan, a, st)      \
+                            : launch_variant<BN, kModeMatrix, false>(plan, a, st)
+#define MCB200_DISPATCH_PAIR(BN)                                                       \
+  e = mode == kModeIm2col ? launch_variant<BN, kModeIm2col, true>(plan, a, st)         \
+                          : launch_variant<BN, kModeMatrix, true>(plan, a, st)
+  if (plan->cta_pair) {
+    if (mode == kModeRows) return -3;
+    switch (plan->block_n) {
+      case 128: MCB200_DISPATCH_PAIR(128); break;
+      case 256: MCB200_DISPATCH_PAIR(256); break;
+      default: return -3;
+    }
+    return static_cast<int>(e);
+  }
   switch (plan->block_n) {
     case 64: MCB200_DISPATCH(64); break;
     case 128: MCB200_DISPATCH(128); break;
     case 256: MCB200_DISPATCH(256); break;
     default: return -3;
   }
+#undef MCB200_DISPATCH_PAIR
 #undef MCB200_DISPATCH
   return static_cast<int>(e);
 }
@@ -1005,7 +1165,7 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   plan->shape.c_stride = 4;
   plan->out_ptr = nullptr;
   plan->res_ptr = nullptr;
-  plan->out_ld = plan->res_ld = plan->reserved = 0;
+  plan->out_ld = plan->res_ld = plan->cta_pair = 0;
   if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;

@@ -33,7 +33,7 @@ class ConvPlan(ctypes.Structure):
                 ("tma_out", ctypes.c_uint64 * 16), ("tma_res", ctypes.c_uint64 * 16), ("shape", ConvShape),
                 ("m", ctypes.c_int), ("k_iters", ctypes.c_int), ("c_blocks", ctypes.c_int),
                 ("block_n", ctypes.c_int), ("im2col", ctypes.c_int), ("out_ld", ctypes.c_int),
-                ("res_ld", ctypes.c_int), ("reserved", ctypes.c_int), ("out_ptr", ctypes.c_void_p),
+                ("res_ld", ctypes.c_int), ("cta_pair", ctypes.c_int), ("out_ptr", ctypes.c_void_p),
                 ("res_ptr", ctypes.c_void_p)]
 
 
