@@ -215,6 +215,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // A paired MMA writes the same tensor-memory address in both CTAs.  Each CTA
   // makes the first and only allocation of its SM, which starts at column 0;
   // anything else is refused rather than computed wrongly.
+  // Up to here the CTA has only set itself up, which may overlap the tail of
+  // the previous launch of the stream; from here on it touches tensors.
+  grid_launch_dependents();
+  grid_dependency_wait();
   const bool usable = !kPair || tmem_base == 0u;
   if (!usable && threadIdx.x == 0) abort_flag = 1;
   // Cluster-window addresses of rank 0's shared barriers.
@@ -821,14 +825,6 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
       configured[dev] = true;
     }
   }
-  // Two staging slots when the epilogue is the busy part (a residual to bring
-  // in, or few k-iterations per tile); otherwise one, and a deeper ring.
-  args.slots = (args.ep.residual != nullptr || args.k_iters < 16) ? 2 : 1;
-  int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots)) / Plan::kStageBytes;
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) return cudaErrorInvalidConfiguration;
-  args.stages = stages;
-  const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots);
   const long long m_tiles = kMode == kModeRows ? static_cast<long long>(plan->shape.n) * plan->shape.ho
                                                : (plan->m + kBlockM - 1) / kBlockM;
   const long long m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
@@ -839,6 +835,15 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
   const long long workers_max = kPair ? sms / 2 : sms;
   const unsigned workers = static_cast<unsigned>(tiles < workers_max ? tiles : workers_max);
+  // Two staging slots when the epilogue is the busy or the exposed part (a
+  // residual to bring in, few k-iterations per tile, or a single tile per CTA
+  // so that no next main loop covers it); otherwise one, and a deeper ring.
+  args.slots = (args.ep.residual != nullptr || args.k_iters < 16 || tiles <= workers_max) ? 2 : 1;
+  int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots)) / Plan::kStageBytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  args.stages = stages;
+  const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots);
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
   const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);
@@ -846,24 +851,23 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   cudaError_t launched;
   {
     TimedLaunch timed(stream);
-    if (kPair) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(workers * 2, 1, 1);
-      cfg.blockDim = dim3(kThreads, 1, 1);
-      cfg.dynamicSmemBytes = static_cast<size_t>(dynamic_bytes);
-      cfg.stream = stream;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 2;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      launched = cudaLaunchKernelEx(&cfg, kernel, *ma, *mb, *mo, *mr, args);
-    } else {
-      kernel<<<dim3(workers, 1, 1), kThreads, dynamic_bytes, stream>>>(*ma, *mb, *mo, *mr, args);
-      launched = cudaGetLastError();
-    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kPair ? workers * 2 : workers, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(dynamic_bytes);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    // The kernel's set-up may overlap the end of the previous kernel in the
+    // stream; it orders itself with griddepcontrol.wait.
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = kPair ? 2 : 1;
+    launched = cudaLaunchKernelEx(&cfg, kernel, *ma, *mb, *mo, *mr, args);
   }
   count_launch();
   return launched;

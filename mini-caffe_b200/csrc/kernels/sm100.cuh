@@ -165,6 +165,21 @@ __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) 
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
+// ---------------------------------------------------------------- dependent launches
+// A kernel launched with the programmatic-stream-serialization attribute may
+// start before the previous kernel of its stream has finished.  It must call
+// grid_dependency_wait() before it reads anything that kernel wrote or writes
+// anything that kernel may still read; until then it can only set itself up.
+// grid_launch_dependents() tells the scheduler that the next such kernel may be
+// started (it still waits, in its own grid_dependency_wait(), for this one to
+// finish completely).
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- CTA pairs
 // Two CTAs of a cluster (ranks 0 and 1) that run one tcgen05.mma.cta_group::2
 // between them.  Rank 0 issues the MMAs; barriers that both CTAs signal live in

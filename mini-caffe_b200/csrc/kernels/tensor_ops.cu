@@ -271,6 +271,48 @@ __global__ void pool_nhwc_kernel(const float* __restrict__ in, float* __restrict
   }
 }
 
+// Max pooling with a K x K window (K = 2, 3), channels % 4 == 0: one thread per
+// output pixel and four channels.  All K*K loads are issued before the first
+// comparison (taps outside the image read nothing and count as -FLT_MAX), so
+// each thread has K*K independent 16-byte requests in flight instead of a
+// dependent loop; index arithmetic is 32-bit.
+template <int K>
+__global__ void pool_max_small_kernel(const float4* __restrict__ in, float4* __restrict__ out, PoolArgs a) {
+  const int cg = a.c >> 2;
+  const unsigned total = static_cast<unsigned>(a.n) * a.ho * a.wo * cg;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned g = i % cg;
+    unsigned t = i / cg;
+    const int ox = static_cast<int>(t % a.wo);
+    t /= a.wo;
+    const int oy = static_cast<int>(t % a.ho);
+    const unsigned n = t / a.ho;
+    const int y0 = oy * a.sh - a.ph;
+    const int x0 = ox * a.sw - a.pw;
+    const float4* base = in + static_cast<size_t>(n) * a.h * a.w * cg + g;
+    float4 v[K * K];
+#pragma unroll
+    for (int dy = 0; dy < K; ++dy) {
+#pragma unroll
+      for (int dx = 0; dx < K; ++dx) {
+        const int y = y0 + dy, x = x0 + dx;
+        const bool inside = y >= 0 && y < a.h && x >= 0 && x < a.w;
+        v[dy * K + dx] = inside ? __ldg(base + (static_cast<size_t>(y) * a.w + x) * cg)
+                                : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+      }
+    }
+    float4 m = v[0];
+#pragma unroll
+    for (int j = 1; j < K * K; ++j) {
+      m.x = fmaxf(m.x, v[j].x);
+      m.y = fmaxf(m.y, v[j].y);
+      m.z = fmaxf(m.z, v[j].z);
+      m.w = fmaxf(m.w, v[j].w);
+    }
+    out[i] = m;
+  }
+}
+
 // ---------------------------------------------------------------- softmax
 
 // inner == 1: one warp per row, the row is streamed three times from L1/L2
@@ -487,7 +529,17 @@ extern "C" int mcb200_pool_nhwc(const float* in, float* out, int n, int h, int w
   const int threads = 256;
   const bool vec = (c % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   const long long items = static_cast<long long>(n) * ho * wo * (vec ? c / 4 : c);
-  if (vec) {
+  const bool small_max = vec && method == MCB200_POOL_MAX && kh == kw && (kh == 2 || kh == 3) &&
+                         items < 0x7fffffffLL;
+  if (small_max) {
+    const float4* in4 = reinterpret_cast<const float4*>(in);
+    float4* out4 = reinterpret_cast<float4*>(out);
+    if (kh == 3) {
+      pool_max_small_kernel<3><<<grid_for(items, threads, 32), threads, 0, as_stream(stream)>>>(in4, out4, a);
+    } else {
+      pool_max_small_kernel<2><<<grid_for(items, threads, 32), threads, 0, as_stream(stream)>>>(in4, out4, a);
+    }
+  } else if (vec) {
     pool_nhwc_kernel<4><<<grid_for(items, threads), threads, 0, as_stream(stream)>>>(in, out, a);
   } else {
     pool_nhwc_kernel<1><<<grid_for(items, threads), threads, 0, as_stream(stream)>>>(in, out, a);
