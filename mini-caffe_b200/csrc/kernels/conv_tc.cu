@@ -139,7 +139,8 @@ struct RingPos {
 // result from its own tensor memory.  Weight bytes per MAC halve, which is what
 // bounds the layers whose operands come out of L2 faster than the ring can
 // turn over.  Barriers that both CTAs signal (stage full, accumulator drained)
-// live in rank 0; tcgen05.commit multicasts the arrivals that both CTAs wait on.
+// live in rank 0; tcgen05.commit delivers the arrivals that both CTAs wait on to
+// each CTA's own copy of the barrier.
 template <int BN, int kMode, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -748,6 +749,11 @@ const DriverApi& driver_api() {
 // Wide tiles re-read the activations less often, narrow tiles fill the machine
 // when there are few output pixels; take the cheapest of the three.
 int pick_block_n(int cout, long long m, int k_iters) {
+  const char* force = getenv("MCB200_BLOCK_N");   // "64" / "128" / "256": override for experiments and tests
+  if (force) {
+    const int bn = atoi(force);
+    if (bn == 64 || bn == 128 || bn == 256) return bn;
+  }
   const long long m_tiles = (m + kBlockM - 1) / kBlockM;
   int best = 64;
   double best_cost = 0.0;

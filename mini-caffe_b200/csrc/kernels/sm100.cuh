@@ -80,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 }
 
 // ---------------------------------------------------------------- TMA loads
-// None of these uses cluster multicast: every CTA fetches its own tiles.
+// Every CTA fetches its own tiles: each load below has exactly one destination CTA.
 
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
   asm volatile(
@@ -209,8 +209,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 }
 
 // TMA loads into this CTA's shared memory whose completion is signalled on a
-// barrier of either CTA of the pair (cluster-window address).  No multicast:
-// each CTA fetches what it needs itself.
+// barrier of either CTA of the pair (cluster-window address).  One destination
+// CTA per load: each CTA fetches what it needs itself.
 __device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t bar_cluster_addr, void* dst, int x,
                                                  int y) {
   asm volatile(

@@ -6,6 +6,7 @@ Tolerance: TF32 operands (10-bit mantissa) with fp32 accumulation; elementwise
 normalised by the output's largest magnitude must stay below 2e-3.
 """
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -153,3 +154,60 @@ def test_conv_tc_fused_tail(kernels):
         want = reference(x, wt, **kw)
         err = (got.cpu() - want).abs()
         assert (err <= 2e-2 + 1e-2 * want.abs()).all(), (act, slope, float(err.max()))
+
+
+def _with_planner(block_n, pairing, fn):
+    """Runs fn() with the planner's tile-width and CTA-pair overrides set."""
+    saved = {k: os.environ.get(k) for k in ("MCB200_BLOCK_N", "MCB200_CTA_PAIR")}
+    os.environ["MCB200_BLOCK_N"] = str(block_n)
+    os.environ["MCB200_CTA_PAIR"] = pairing
+    try:
+        return fn()
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                del os.environ[k]
+            else:
+                os.environ[k] = v
+
+
+@pytest.mark.parametrize("case", [
+    # name, N, C, H, W, Cout, k, tile width, with residual
+    ("odd_m_tiles_3x3", 1, 256, 19, 19, 256, 3, 256, False),     # 361 pixels: 3 M tiles, the last CTA of a pair idles
+    ("many_tiles_per_cluster", 16, 128, 56, 56, 128, 3, 128, False),  # 196 pair units over at most 74 clusters
+    ("pointwise_residual", 4, 512, 28, 28, 256, 1, 256, True),
+    ("wide_two_n_tiles", 2, 128, 28, 28, 512, 3, 256, True),
+    ("ragged_cout", 2, 64, 20, 20, 200, 3, 128, True),           # last N tile 72 columns wide
+], ids=lambda c: c[0])
+def test_cta_pairs_match_single_ctas(kernels, case):
+    """The two-CTA (tcgen05 cta_group::2) variant accumulates every output element over the same
+    K sequence as the one-CTA variant, so the two must agree bit for bit."""
+    name, n, c, h, w, cout, k, block_n, with_res = case
+    g = torch.Generator().manual_seed(99)
+    x = torch.randn((n, c, h, w), generator=g)
+    wt = torch.randn((cout, c, k, k), generator=g) * (2.0 / (c * k * k)) ** 0.5
+    res = torch.randn((n, cout, h, w), generator=g) if with_res else None
+    scale = torch.rand(cout, generator=g) + 0.5
+    shift = torch.randn(cout, generator=g)
+    kw = dict(stride=1, pad=k // 2, dil=1, scale=scale, shift=shift, residual=res, res_coeff=1.0, act=1, slope=0.0)
+    single, plan_single = _with_planner(block_n, "0", lambda: run_conv(kernels, x.cuda(), wt, **kw))
+    paired, plan_paired = _with_planner(block_n, "1", lambda: run_conv(kernels, x.cuda(), wt, **kw))
+    assert plan_single.block_n == block_n and plan_paired.block_n == block_n
+    assert plan_single.cta_pair == 0 and plan_paired.cta_pair == 1
+    assert torch.equal(single, paired)
+    want = reference(x, wt, prelu=None, **kw)
+    err = (paired.cpu() - want).abs()
+    assert (err <= 2e-2 + 1e-2 * want.abs()).all(), float(err.max())
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+def test_every_tile_width_gives_the_same_result(kernels, block_n):
+    """Tile width only changes how the output is cut up, not the arithmetic."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((2, 96, 24, 24), generator=g)
+    wt = torch.randn((320, 96, 3, 3), generator=g) * 0.03
+    kw = dict(stride=1, pad=1, dil=1, scale=None, shift=None, residual=None, res_coeff=1.0, act=0, slope=0.0)
+    base, _ = _with_planner(64, "0", lambda: run_conv(kernels, x.cuda(), wt, **kw))
+    got, plan = _with_planner(block_n, "0", lambda: run_conv(kernels, x.cuda(), wt, **kw))
+    assert plan.block_n == block_n
+    assert torch.equal(base, got)
