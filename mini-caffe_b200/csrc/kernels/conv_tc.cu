@@ -81,11 +81,11 @@ struct ConvTcArgs {
   int tile_rows;     // valid rows of an M tile: 128, or the output width in row mode
   int a_bytes;       // bytes one activation tile load delivers
   int stages;        // depth of the operand ring (2 .. kMaxStages)
-  int slots;         // staging slots per epilogue warp (1 or 2)
+  int slots;         // staging slots per epilogue warp: 1 or 2; 2 or 3 when a residual is added
 };
 
 constexpr int kMaxStages = 8;
-constexpr int kMaxSlots = 2;
+constexpr int kMaxSlots = 3;
 constexpr int kSharedLimit = 232448;   // 227 KiB: the most one CTA can have on sm_100
 
 // Shared memory of one persistent CTA = operand ring (`stages` x (A tile + B
@@ -439,35 +439,46 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     // Chunk sequence of this warp: for each of its CTA's tiles, the 32-column
     // chunks it owns that exist (the last n-tile may have fewer), left to right.
-    // `seq` numbers them; chunk seq uses staging slot seq % 2 (residual launches
-    // always have two slots).  Two cursors
-    // of lane 0 walk the same sequence ahead of the computation: `pf` asks L2 for
-    // the residual sub-tiles kResidualL2Ahead chunks early (the layers that add a
-    // residual stream it from DRAM exactly once, so nothing else would bring it
-    // close), `ld` copies the next chunk's sub-tile into its staging slot.
+    // `seq` numbers them.  With a residual the warp cycles through its staging
+    // slots, and two cursors of lane 0 walk the same sequence ahead of the
+    // computation: `pf` asks L2 for the residual sub-tiles kResidualL2Ahead
+    // chunks early (the layers that add a residual stream it from DRAM exactly
+    // once, so nothing else would bring it close); `ld` copies the next chunk's
+    // sub-tile into the slot that comes free next: with three slots the store
+    // that last read it (two chunks back) has had a whole chunk's time to
+    // finish, with two slots it is the previous chunk's store.
     struct ChunkCursor {
-      int local;
-      int chunk;
+      int local;   // how many of this CTA's tiles lie behind the cursor
+      int chunk;   // next chunk of the current tile
+      int mt;      // M tile and first column of the current tile (-1: not looked up yet)
+      int n0;
     };
     auto cursor_next = [&](ChunkCursor& cur, int& mt, int& col) {
       for (;;) {
-        const long long tile = static_cast<long long>(worker) + static_cast<long long>(cur.local) * workers;
-        if (tile >= num_tiles) return false;
-        const int unit = static_cast<int>(tile / n_tiles);
-        mt = unit_to_mt(unit);
-        col = static_cast<int>(tile - static_cast<long long>(unit) * n_tiles) * BN + cur.chunk * 32;
+        if (cur.mt < 0) {   // entering a tile: one division per tile, none per chunk
+          const int tile = worker + cur.local * workers;
+          if (tile >= num_tiles) return false;
+          const int unit = tile / n_tiles;
+          cur.mt = unit_to_mt(unit);
+          cur.n0 = (tile - unit * n_tiles) * BN;
+        }
+        col = cur.n0 + cur.chunk * 32;
         if (cur.chunk >= chunks_full || col >= args.cout) {   // this warp's chunks of the tile are done
           cur.chunk = half;
           ++cur.local;
+          cur.mt = -1;
           continue;
         }
+        mt = cur.mt;
         cur.chunk += 2;
         return true;
       }
     };
     constexpr int kResidualL2Ahead = 8;
-    ChunkCursor pf = {0, half}, ld = {0, half};
-    int ld_seq = 0;
+    ChunkCursor pf = {0, half, -1, 0}, ld = {0, half, -1, 0};
+    int ld_slot = 0;                     // slot of the next residual load
+    int cur_slot = 0;                    // slot of the chunk being finished (residual launches)
+    uint32_t cur_parity = 0;
     auto prefetch_residual = [&]() {
       int mt, col;
       if (!cursor_next(pf, mt, col)) return;
@@ -480,8 +491,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto issue_residual = [&]() {
       int mt, col;
       if (!cursor_next(ld, mt, col)) return;
-      const int slot = ld_seq & 1;
-      ++ld_seq;
+      const int slot = ld_slot;
+      if (++ld_slot == slots) ld_slot = 0;
       mbar_expect_tx(&res_bar[ew][slot], 4096);
       if (kMode == kModeRows) {
         tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, quad * 32, mt);
@@ -578,21 +589,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           return v;
         };
         if (staged) {
-          const int slot = slots == 2 ? (g & 1) : 0;
+          const int slot = has_res ? cur_slot : (slots == 2 ? (g & 1) : 0);
           float* buf = slot_ptr(slot) + lane * 32;
           if (has_res) {
             if (lane == 0) {
-              // The other slot is free once the previous chunk's store has read
-              // it: start the next chunk's residual on its way before working
-              // on this one.
-              tma_store_wait_read<0>();
+              // The next chunk's residual goes into the slot that comes free
+              // next; with three slots the latest store may still be reading.
+              if (slots == 3) {
+                tma_store_wait_read<1>();
+              } else {
+                tma_store_wait_read<0>();
+              }
               issue_residual();
               prefetch_residual();
             }
             alive = __all_sync(0xffffffffu,
-                               mbar_wait_bounded(&res_bar[ew][slot], static_cast<uint32_t>(g >> 1) & 1u, abort,
-                                                 kWaitLimitCycles));
+                               mbar_wait_bounded(&res_bar[ew][slot], cur_parity, abort, kWaitLimitCycles));
             if (!alive) break;
+            if (++cur_slot == slots) {
+              cur_slot = 0;
+              cur_parity ^= 1u;
+            }
           } else if (g >= slots) {
             // The store that last used this slot must have finished reading it.
             if (lane == 0) {
@@ -608,19 +625,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // piece j stored at position j ^ (row & 7) (the 128-byte swizzle).
           // The result overwrites the residual in place.
           const int swz = lane & 7;
+          // All reads of the chunk (residual cells, per-column tables) come
+          // before its first write: the loads are then independent of each other
+          // and overlap, where a read-modify-write per cell would expose one
+          // shared-memory round trip after the other (long ones while the
+          // tensor core and the TMA keep shared memory busy).
+          float4 v[8];
           if (has_res) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              float4* cell = reinterpret_cast<float4*>(buf + ((j ^ swz) << 2));
-              *cell = finish4(j, *cell, true);
+              v[j] = finish4(j, *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2)), true);
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4* cell = reinterpret_cast<float4*>(buf + ((j ^ swz) << 2));
-              *cell = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
-            }
+            for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
           }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -841,10 +862,13 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
   const long long workers_max = kPair ? sms / 2 : sms;
   const unsigned workers = static_cast<unsigned>(tiles < workers_max ? tiles : workers_max);
-  // Two staging slots when the epilogue is the busy or the exposed part (a
-  // residual to bring in, few k-iterations per tile, or a single tile per CTA
-  // so that no next main loop covers it); otherwise one, and a deeper ring.
-  args.slots = (args.ep.residual != nullptr || args.k_iters < 16 || tiles <= workers_max) ? 2 : 1;
+  // Staging slots per epilogue warp.  With a residual: three where tiles are so
+  // short that the ring needs little (load, work and store of consecutive
+  // chunks overlap), else two.  Without: two when the epilogue is the busy
+  // or the exposed part (few k-iterations per tile, or a single tile per CTA so
+  // that no next main loop covers it); otherwise one, and a deeper ring.
+  args.slots = args.ep.residual != nullptr ? (args.k_iters <= 4 ? 3 : 2)
+                                           : ((args.k_iters < 16 || tiles <= workers_max) ? 2 : 1);
   int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots)) / Plan::kStageBytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
