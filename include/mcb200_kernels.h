@@ -282,6 +282,27 @@ int mcb200_detout_max_rows_per_image(const mcb200_detout_params* p);
 int mcb200_detout_forward(const mcb200_detout_params* p, int batch, const float* loc, const float* conf,
                           const float* prior, void* workspace, float* out, int* total, void* stream);
 
+/* ROIPooling: max over an adaptive pooled_h x pooled_w grid laid on each region
+ * of interest (src/layers/roi_pooling_layer.cpp:37-109).  data_nchw is
+ * [batch, channels, height, width]; rois is [num_rois, 5] = (batch index, x1, y1,
+ * x2, y2) in image coordinates; out is [num_rois, channels, pooled_h, pooled_w].
+ * Bit-identical to the reference's CPU result.  A roi whose batch index is
+ * outside [0, batch) (a CHECK failure in the reference) yields zeros and sets
+ * *status to 3 when status is not null.                                       */
+int mcb200_roi_pool(const float* data_nchw, const float* rois, float* out, int num_rois, int batch, int channels,
+                    int height, int width, int pooled_h, int pooled_w, float spatial_scale, int* status,
+                    void* stream);
+
+/* PSROIPooling: position-sensitive average pooling of R-FCN
+ * (src/layers/psroi_pooling_layer.cpp:45-106).  data_nchw is
+ * [batch, output_dim * group_size^2, height, width]; out is
+ * [num_rois, output_dim, group_size, group_size]; bin (ph, pw) of output channel
+ * c averages score map (c * group_size + ph) * group_size + pw over the bin,
+ * summing in the reference's row-major order (bit-identical).                 */
+int mcb200_psroi_pool(const float* data_nchw, const float* rois, float* out, int num_rois, int batch,
+                      int output_dim, int group_size, int height, int width, float spatial_scale, int* status,
+                      void* stream);
+
 /* Number of kernels launched by this library on the calling thread since the
  * last reset (bench.py reports it as gpu_launches).                          */
 long long mcb200_launch_count(void);

@@ -82,6 +82,9 @@ void Context::SyncAndCheck() {
     const int code = *status_host_;
     *status_host_ = 0;
     CUDA_CHECK(cudaMemsetAsync(status_dev_, 0, sizeof(int), stream_));
+    // 3: a region-of-interest layer met a roi whose image index is outside the batch
+    // (the reference fails its CHECK_GE / CHECK_LT on roi_batch_ind at that point).
+    if (code == 3) LOG(FATAL) << "Check failed: roi_batch_ind is outside [0, batch_size)";
     LOG(FATAL) << "a kernel gave up waiting on a hardware barrier (status " << code
                << "); the results of this forward pass are invalid";
   }

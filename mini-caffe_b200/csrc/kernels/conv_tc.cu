@@ -440,13 +440,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Chunk sequence of this warp: for each of its CTA's tiles, the 32-column
     // chunks it owns that exist (the last n-tile may have fewer), left to right.
     // `seq` numbers them.  With a residual the warp cycles through its staging
-    // slots, and two cursors of lane 0 walk the same sequence ahead of the
-    // computation: `pf` asks L2 for the residual sub-tiles kResidualL2Ahead
-    // chunks early (the layers that add a residual stream it from DRAM exactly
-    // once, so nothing else would bring it close); `ld` copies the next chunk's
-    // sub-tile into the slot that comes free next: with three slots the store
-    // that last read it (two chunks back) has had a whole chunk's time to
-    // finish, with two slots it is the previous chunk's store.
+    // slots, and a cursor of lane 0 walks the same sequence one chunk ahead of
+    // the computation: it copies the next chunk's residual sub-tile into the
+    // slot that comes free next (with three slots the store that last read it,
+    // two chunks back, has had a whole chunk's time to finish; with two slots it
+    // is the previous chunk's store).  Asking L2 for the residual further ahead
+    // (cp.async.bulk.prefetch) was tried and removed: the lines were evicted by
+    // the output stream before use and DRAM reads grew by half.
     struct ChunkCursor {
       int local;   // how many of this CTA's tiles lie behind the cursor
       int chunk;   // next chunk of the current tile
@@ -474,20 +474,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         return true;
       }
     };
-    constexpr int kResidualL2Ahead = 8;
-    ChunkCursor pf = {0, half, -1, 0}, ld = {0, half, -1, 0};
+    ChunkCursor ld = {0, half, -1, 0};
     int ld_slot = 0;                     // slot of the next residual load
     int cur_slot = 0;                    // slot of the chunk being finished (residual launches)
     uint32_t cur_parity = 0;
-    auto prefetch_residual = [&]() {
-      int mt, col;
-      if (!cursor_next(pf, mt, col)) return;
-      if (kMode == kModeRows) {
-        tma_prefetch_l2_3d(&map_res, col, quad * 32, mt);
-      } else {
-        tma_prefetch_l2_3d(&map_res, col, mt * kBlockM + quad * 32, 0);
-      }
-    };
     auto issue_residual = [&]() {
       int mt, col;
       if (!cursor_next(ld, mt, col)) return;
@@ -501,10 +491,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     };
     const bool staged = args.tma_epilogue != 0;
-    if (staged && has_res && lane == 0) {
-      for (int i = 0; i < kResidualL2Ahead; ++i) prefetch_residual();
-      issue_residual();
-    }
+    if (staged && has_res && lane == 0) issue_residual();
 
     int seq = 0;
     int local = 0;
@@ -601,7 +588,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tma_store_wait_read<0>();
               }
               issue_residual();
-              prefetch_residual();
             }
             alive = __all_sync(0xffffffffu,
                                mbar_wait_bounded(&res_bar[ew][slot], cur_parity, abort, kWaitLimitCycles));

@@ -152,15 +152,6 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Asks L2 to fetch the tile a later load with the same coordinates will read;
-// nothing is written to shared memory and nothing signals completion.
-__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
-               :
-               : "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

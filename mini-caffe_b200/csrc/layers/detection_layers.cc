@@ -291,4 +291,57 @@ void DetectionOutputLayer::Forward_gpu(const vector<Blob*>& bottom, const vector
 }
 REGISTER_LAYER_CLASS(DetectionOutput);
 
+// ---------------------------------------------------------------- ROIPooling / PSROIPooling
+
+void ROIPoolingLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const ROIPoolingParameter& p = layer_param_.roi_pooling_param();
+  CHECK_GT(p.pooled_h(), 0u) << "pooled_h must be > 0";
+  CHECK_GT(p.pooled_w(), 0u) << "pooled_w must be > 0";
+  pooled_h_ = static_cast<int>(p.pooled_h());
+  pooled_w_ = static_cast<int>(p.pooled_w());
+  spatial_scale_ = p.spatial_scale();
+}
+
+void ROIPoolingLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  CHECK_EQ(bottom[0]->num_axes(), 4) << "ROIPooling: feature maps must be (N, C, H, W)";
+  CHECK_EQ(bottom[1]->count(1), 5) << "ROIPooling: rois must be rows of (batch index, x1, y1, x2, y2)";
+  top[0]->Reshape(bottom[1]->num(), bottom[0]->channels(), pooled_h_, pooled_w_);
+}
+
+void ROIPoolingLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  Context& ctx = Context::Get();
+  if (top[0]->count() == 0) return;
+  KERNEL_CHECK(mcb200_roi_pool(bottom[0]->gpu_data(), bottom[1]->gpu_data(), top[0]->mutable_gpu_data(),
+                               bottom[1]->num(), bottom[0]->num(), bottom[0]->channels(), bottom[0]->height(),
+                               bottom[0]->width(), pooled_h_, pooled_w_, spatial_scale_, ctx.status_word(),
+                               ctx.stream_ptr()));
+}
+REGISTER_LAYER_CLASS(ROIPooling);
+
+void PSROIPoolingLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const PSROIPoolingParameter& p = layer_param_.psroi_pooling_param();
+  CHECK_GT(p.output_dim(), 0) << "output_dim must be > 0";
+  CHECK_GT(p.group_size(), 0) << "group_size must be > 0";
+  output_dim_ = p.output_dim();
+  group_size_ = p.group_size();
+  spatial_scale_ = p.spatial_scale();
+}
+
+void PSROIPoolingLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  CHECK_EQ(bottom[0]->num_axes(), 4) << "PSROIPooling: score maps must be (N, C, H, W)";
+  CHECK_EQ(bottom[0]->channels(), output_dim_ * group_size_ * group_size_)
+      << "input channel number does not match layer parameters";
+  CHECK_EQ(bottom[1]->count(1), 5) << "PSROIPooling: rois must be rows of (batch index, x1, y1, x2, y2)";
+  top[0]->Reshape(bottom[1]->num(), output_dim_, group_size_, group_size_);
+}
+
+void PSROIPoolingLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  Context& ctx = Context::Get();
+  if (top[0]->count() == 0) return;
+  KERNEL_CHECK(mcb200_psroi_pool(bottom[0]->gpu_data(), bottom[1]->gpu_data(), top[0]->mutable_gpu_data(),
+                                 bottom[1]->num(), bottom[0]->num(), output_dim_, group_size_, bottom[0]->height(),
+                                 bottom[0]->width(), spatial_scale_, ctx.status_word(), ctx.stream_ptr()));
+}
+REGISTER_LAYER_CLASS(PSROIPooling);
+
 }  // namespace caffe

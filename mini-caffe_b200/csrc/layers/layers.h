@@ -388,6 +388,36 @@ class DetectionOutputLayer : public Layer {
   std::unique_ptr<BlobInt> total_;
 };
 
+// Region-of-interest pooling behind Proposal (Faster R-CNN / R-FCN heads).
+// bottom[0]: feature or score maps (N, C, H, W); bottom[1]: rois [R, 5].
+class ROIPoolingLayer : public Layer {
+ public:
+  explicit ROIPoolingLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "ROIPooling"; }
+  int ExactNumBottomBlobs() const override { return 2; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int pooled_h_ = 0, pooled_w_ = 0;
+  float spatial_scale_ = 1.f;
+};
+
+class PSROIPoolingLayer : public Layer {
+ public:
+  explicit PSROIPoolingLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "PSROIPooling"; }
+  int ExactNumBottomBlobs() const override { return 2; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int output_dim_ = 0, group_size_ = 0;
+  float spatial_scale_ = 1.f;
+};
+
 }  // namespace caffe
 
 #endif  // MCB200_LAYERS_H_

@@ -392,3 +392,51 @@ def proposal_input(num_anchors=15, height=63, width=38, seed=0, im_h=1000.0, im_
     scores[0, num_anchors:] = fg.reshape(num_anchors, height, width)
     return {"rpn_cls_prob": scores, "rpn_bbox_pred": deltas,
             "im_info": np.array([[im_h, im_w, 1.0]], dtype=np.float32)}, redraws
+
+
+# ----------------------------------------------------------------- region-of-interest pooling (R-FCN / Faster R-CNN heads)
+
+def roi_pooling(kind="PSROIPooling", batch=1, height=63, width=38, num_rois=300, output_dim=21, group_size=7,
+                channels=64, pooled_h=7, pooled_w=7, spatial_scale=1.0 / 16):
+    """Input maps + Input rois -> one pooling layer.  PSROIPooling takes output_dim * group_size^2 score
+    maps (R-FCN: 21 classes x 7 x 7 = 1029 maps); ROIPooling takes `channels` feature maps."""
+    b = NetBuilder(kind.lower())
+    c = output_dim * group_size * group_size if kind == "PSROIPooling" else channels
+    b.input([("maps", (batch, c, height, width)), ("rois", (num_rois, 5))])
+    if kind == "PSROIPooling":
+        body = "psroi_pooling_param { spatial_scale: %.10g output_dim: %d group_size: %d }" % (
+            spatial_scale, output_dim, group_size)
+    else:
+        body = "roi_pooling_param { pooled_h: %d pooled_w: %d spatial_scale: %.10g }" % (
+            pooled_h, pooled_w, spatial_scale)
+    b.raw("pool", kind, ["maps", "rois"], ["pooled"], body)
+    return b
+
+
+def roi_pooling_input(batch, channels, height, width, num_rois, seed=0, feat_stride=16.0):
+    """Maps ~ N(0, 1).  Rois in image coordinates (the map times feat_stride): mostly boxes inside the image,
+    plus the shapes the layers special-case: boxes hanging over every border, boxes smaller than a bin,
+    degenerate boxes (x2 < x1), boxes entirely outside, and half-integer corners (round() half away from
+    zero).  Column 0 is the image index."""
+    rng = np.random.default_rng(seed + 9000)
+    maps = rng.standard_normal((batch, channels, height, width)).astype(np.float32)
+    im_w, im_h = width * feat_stride, height * feat_stride
+    rois = np.zeros((num_rois, 5), dtype=np.float32)
+    for r in range(num_rois):
+        kind = r % 8
+        x1, y1 = rng.uniform(0, im_w - 32), rng.uniform(0, im_h - 32)
+        w, h = rng.uniform(8, im_w / 2), rng.uniform(8, im_h / 2)
+        if kind == 1:      # over the right / bottom border
+            x1, y1 = im_w - w / 2, im_h - h / 2
+        elif kind == 2:    # over the left / top border
+            x1, y1 = -w / 2, -h / 2
+        elif kind == 3:    # smaller than one bin
+            w, h = rng.uniform(0, 6), rng.uniform(0, 6)
+        elif kind == 4:    # degenerate
+            w, h = -rng.uniform(1, 40), rng.uniform(8, 100)
+        elif kind == 5:    # outside the image
+            x1, y1 = im_w + 50, im_h + 50
+        elif kind == 6:    # corners on half integers
+            x1, y1, w, h = np.floor(x1) + 0.5, np.floor(y1) + 0.5, np.floor(w) + 0.5, np.floor(h)
+        rois[r] = (rng.integers(0, batch), x1, y1, x1 + w, y1 + h)
+    return {"maps": maps, "rois": rois}

@@ -197,3 +197,66 @@ def fold_batch_norm_scale(mean, var, factor, eps, gamma, beta, conv_bias=None):
     b0 = conv_bias.astype(np.float64) if conv_bias is not None else 0.0
     t = (b0 - mean.astype(np.float64) * f) * s + beta.astype(np.float64)
     return s, t
+
+
+def _round_half_away(x):
+    """C round(): halves go away from zero (numpy's rint goes to even)."""
+    x = F(x)
+    return F(np.floor(np.abs(x) + F(0.5)) * np.sign(x)) if np.isfinite(x) else x
+
+
+def roi_pooling(maps, rois, pooled_h, pooled_w, spatial_scale):
+    """Max over an adaptive grid per roi; corners scaled then rounded; an empty bin gives 0.
+    src/layers/roi_pooling_layer.cpp:37-109.  Loops in Python: small cases only."""
+    n, c, h, w = maps.shape
+    out = np.zeros((rois.shape[0], c, pooled_h, pooled_w), dtype=F)
+    s = F(spatial_scale)
+    for r, roi in enumerate(rois.astype(F)):
+        b = int(roi[0])
+        assert 0 <= b < n
+        sw, sh, ew, eh = (int(_round_half_away(F(roi[i]) * s)) for i in (1, 2, 3, 4))
+        rh, rw = max(eh - sh + 1, 1), max(ew - sw + 1, 1)
+        bh, bw = F(rh) / F(pooled_h), F(rw) / F(pooled_w)
+        for ph in range(pooled_h):
+            hs = min(max(int(np.floor(F(ph) * bh)) + sh, 0), h)
+            he = min(max(int(np.ceil(F(ph + 1) * bh)) + sh, 0), h)
+            for pw in range(pooled_w):
+                ws = min(max(int(np.floor(F(pw) * bw)) + sw, 0), w)
+                we = min(max(int(np.ceil(F(pw + 1) * bw)) + sw, 0), w)
+                if he > hs and we > ws:
+                    out[r, :, ph, pw] = maps[b, :, hs:he, ws:we].max(axis=(1, 2))
+    return out
+
+
+def psroi_pooling(maps, rois, output_dim, group_size, spatial_scale):
+    """Position-sensitive average: bin (ph, pw) of channel c averages score map (c*G + ph)*G + pw over
+    the bin, summed row by row in float; corners rounded then scaled, far corner + 1; an empty bin gives 0.
+    src/layers/psroi_pooling_layer.cpp:45-106.  Loops in Python: small cases only."""
+    n, c, h, w = maps.shape
+    g = group_size
+    assert c == output_dim * g * g
+    out = np.zeros((rois.shape[0], output_dim, g, g), dtype=F)
+    s = F(spatial_scale)
+    for r, roi in enumerate(rois.astype(F)):
+        b = int(roi[0])
+        assert 0 <= b < n
+        sw, sh = F(_round_half_away(roi[1]) * s), F(_round_half_away(roi[2]) * s)
+        ew, eh = F(_round_half_away(F(roi[3] + F(1))) * s), F(_round_half_away(F(roi[4] + F(1))) * s)
+        rh, rw = max(F(eh - sh), F(0.1)), max(F(ew - sw), F(0.1))
+        bh, bw = F(rh / F(g)), F(rw / F(g))
+        for ph in range(g):
+            hs = min(max(int(np.floor(F(F(ph) * bh) + sh)), 0), h)
+            he = min(max(int(np.ceil(F(F(ph + 1) * bh) + sh)), 0), h)
+            for pw in range(g):
+                ws = min(max(int(np.floor(F(F(pw) * bw) + sw)), 0), w)
+                we = min(max(int(np.ceil(F(F(pw + 1) * bw) + sw)), 0), w)
+                if he <= hs or we <= ws:
+                    continue
+                for ch in range(output_dim):
+                    plane = maps[b, (ch * g + ph) * g + pw]
+                    acc = F(0)
+                    for y in range(hs, he):
+                        for x in range(ws, we):
+                            acc = F(acc + plane[y, x])
+                    out[r, ch, ph, pw] = F(acc / F((he - hs) * (we - ws)))
+    return out

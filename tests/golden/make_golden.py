@@ -130,8 +130,22 @@ def prior_box_case():
     save("prior_box", out=run(b, {}, x, ["pb"])["pb"])
 
 
+def roi_pooling_cases():
+    for kind, kw in [("PSROIPooling", dict(batch=2, height=9, width=7, num_rois=48, output_dim=3, group_size=3)),
+                     ("ROIPooling", dict(batch=2, height=9, width=7, num_rois=48, channels=5, pooled_h=3,
+                                         pooled_w=2))]:
+        b = wl.roi_pooling(kind, spatial_scale=1.0 / 16, **kw)
+        channels = kw["output_dim"] * kw["group_size"] ** 2 if kind == "PSROIPooling" else kw["channels"]
+        inputs = wl.roi_pooling_input(kw["batch"], channels, kw["height"], kw["width"], kw["num_rois"], seed=3)
+        res = run(b, {}, inputs, ["pooled"])
+        save(kind.lower(), maps=inputs["maps"], rois=inputs["rois"], out=res["pooled"],
+             params=np.array([kw.get("output_dim", 0), kw.get("group_size", 0), kw.get("pooled_h", 0),
+                              kw.get("pooled_w", 0), 1.0 / 16], np.float64))
+
+
 if __name__ == "__main__":
     dense_layers()
+    roi_pooling_cases()
     proposal_cases()
     detection_cases()
     prior_box_case()

@@ -110,3 +110,16 @@ def test_anchor_generation(port):
     assert np.allclose(a[3], [-56.0, -56.0, 71.0, 71.0])
     # widths and heights are symmetric about the centre
     assert np.allclose((a[:, 0] + a[:, 2]) / 2, 7.5) and np.allclose((a[:, 1] + a[:, 3]) / 2, 7.5)
+
+
+def test_roi_pooling_restatements_bit_exact(no):
+    g = load("roipooling")
+    p = g["params"]
+    got = no.roi_pooling(g["maps"], g["rois"], int(p[2]), int(p[3]), np.float32(p[4]))
+    assert np.array_equal(got.view(np.uint32), g["out"].view(np.uint32))
+    g = load("psroipooling")
+    p = g["params"]
+    got = no.psroi_pooling(g["maps"], g["rois"], int(p[0]), int(p[1]), np.float32(p[4]))
+    assert np.array_equal(got.view(np.uint32), g["out"].view(np.uint32))
+    # the fixtures hold the special cases: empty bins give exactly 0, and some bins are not empty
+    assert (g["out"] == 0).any() and (g["out"] != 0).any()
