@@ -42,6 +42,10 @@ ENGINE_LIB = os.path.join(ROOT, "mini-caffe_b200", "lib", "libcaffe.so")
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libcaffe_ref.so")
 BATCH_PER_GPU = 64
 E2E_THREADS = 2        # host threads per GPU in the end-to-end leg, each with its own Net
+# DRAM bytes per convolution launch (read + write, averaged over the 54 launches of one pass at
+# batch 64) from one ncu capture of this workload: 3589 MB read + 1139 MB written per pass.  Below
+# the algorithmic 126 MB per launch because small activations stay in L2 between layers.
+CONV_DRAM_BYTES_PER_LAUNCH = 87.56e6
 METRIC = "resnet50_images_per_sec"
 UNIT = "images/s"
 
@@ -412,7 +416,10 @@ def main():
     roofline = {
         "kernel": "conv_tc_kernel (tcgen05 implicit GEMM, %d launches per forward)" % round(launches_per_step),
         "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-        "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+        "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
+        "traffic": CONV_DRAM_BYTES_PER_LAUNCH if batch == BATCH_PER_GPU else None,
+        "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum averaged over the 54 launches of a pass, from "
+                        "the ncu capture summarised in profiles/conv_tc_kernel_resnet50_b64.md (same workload)",
         "algorithmic_bytes_per_launch": conv_bytes / launches_per_step,
         "avg_launch_ms": conv_ms.value / max(1, conv_launches),
         "tf32_tflops_achieved": conv_flops / conv_s_per_step / 1e12,

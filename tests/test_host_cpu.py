@@ -228,3 +228,20 @@ def test_text_format_quirks(capi, engine):
     assert blobs["data"].shape == (1, 3, 8, 8)      # legacy input fields became an Input layer
     assert blobs["p"].shape == (1, 2, 4, 4)
     net.close()
+
+
+def test_cli_built_on_public_headers_fails_loudly_without_a_device(tmp_path):
+    """mini-caffe_b200/cli/benchmark.cc sees include/caffe/*.hpp only (the counterpart of mini-caffe's
+    tools/benchmark.cpp).  Without a GPU it must stop with the engine's error, not compute on the host."""
+    import subprocess
+    exe = os.path.join(ROOT, "mini-caffe_b200", "lib", "benchmark")
+    if not os.path.isfile(exe):
+        pytest.skip("command-line tool not built")
+    wl = pkg("workloads")
+    proto = tmp_path / "net.prototxt"
+    proto.write_text(wl.conv_relu(1).text())
+    run = subprocess.run([exe, str(proto), "1", "-1"], capture_output=True, text=True, cwd=str(tmp_path), timeout=120)
+    assert run.returncode == 1
+    assert "no CPU compute path" in run.stderr
+    usage = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert usage.returncode == 2 and "Usage" in usage.stderr

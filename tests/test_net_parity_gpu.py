@@ -103,3 +103,22 @@ def test_batch_invariance(capi, gpu_engine):
     assert np.abs(p2[0] - p1[0]).max() < 1e-6
     assert np.abs(p2[1] - p1[0]).max() < 1e-6
     assert np.abs(p3[0] - p1[0]).max() < 1e-6
+
+
+def test_cli_on_public_headers_runs_a_net(tmp_path):
+    """The command-line tool written against the public C++ headers builds a net from a prototxt
+    file, runs it on GPU 0 and writes the profile, like mini-caffe's tools/benchmark."""
+    import json
+    import os
+    import subprocess
+    wl = pkg("workloads")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "mini-caffe_b200", "lib", "benchmark")
+    assert os.path.isfile(exe), "run __graft_entry__.build() first"
+    proto = tmp_path / "resnet.prototxt"
+    proto.write_text(wl.resnet50(2).text())
+    run = subprocess.run([exe, str(proto), "3", "0"], capture_output=True, text=True, cwd=str(tmp_path), timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert run.stderr.count("Forward costs") == 3
+    events = json.load(open(tmp_path / "profile.json"))["traceEvents"]
+    assert any(e["name"] == "res2a_branch2b" for e in events)
