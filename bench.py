@@ -160,37 +160,74 @@ def cpu_reference_rate(capi, wl, steps, warmup, budget_s):
             "ms_per_step": dt / steps * 1e3, "batch": per_step}
 
 
-def secondary_figures(capi, wl, engine, L, stream, torch):
-    """The two other figures the benchmark definition names, measured after the headline:
-    NMS boxes/s of the RPN Proposal stress case (63x38 map, 15 anchors, pre-NMS 6000, 32 images in
-    one call) and the TF32 rate of the single 3x3 64->64 convolution at batch 32."""
-    out = {}
-    # Proposal: boxes/s := images * min(pre_nms_topn, A*H*W) / time of the whole layer forward
-    images = 32
-    b = wl.proposal(num_anchors=15)
-    text = b.text().replace("dim: 1 dim: 30", "dim: %d dim: 30" % images).replace(
-        "dim: 1 dim: 60", "dim: %d dim: 60" % images).replace("dim: 1 dim: 3 }", "dim: %d dim: 3 }" % images)
-    net = capi.Net(engine, text, None, from_buffer=True)
-    import numpy as np
-    batches = [wl.proposal_input(num_anchors=15, seed=i)[0] for i in range(images)]
-    feed = {k: np.concatenate([x[k] for x in batches], axis=0) for k in batches[0]}
-    net.forward(**feed)
-    for _ in range(3):
+def time_forwards(engine, L, net, stream, torch, reps, warmup=3):
+    """Milliseconds per CaffeNetForward (inputs resident on the device), CUDA events on the engine's stream."""
+    for _ in range(warmup):
         engine.check(L.CaffeNetForward(net.handle))
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 10
     ev0.record(stream)
     for _ in range(reps):
         engine.check(L.CaffeNetForward(net.handle))
     ev1.record(stream)
     torch.cuda.synchronize()
-    ms = ev0.elapsed_time(ev1) / reps
+    return ev0.elapsed_time(ev1) / reps
+
+
+def proposal_figure(capi, wl, engine, L, stream, torch, reps=10, images=32):
+    """RPN Proposal stress case: 63x38 map, 15 anchors, pre-NMS 6000, post-NMS 300, `images` images in one
+    call.  boxes/s := images * min(pre_nms_topn, A*H*W) / time of the whole layer forward (decode, top-k,
+    NMS, gather, counts back to the host)."""
+    import numpy as np
+    b = wl.proposal(num_anchors=15)
+    text = b.text().replace("dim: 1 dim: 30", "dim: %d dim: 30" % images).replace(
+        "dim: 1 dim: 60", "dim: %d dim: 60" % images).replace("dim: 1 dim: 3 }", "dim: %d dim: 3 }" % images)
+    net = capi.Net(engine, text, None, from_buffer=True)
+    batches = [wl.proposal_input(num_anchors=15, seed=i)[0] for i in range(images)]
+    feed = {k: np.concatenate([x[k] for x in batches], axis=0) for k in batches[0]}
+    net.forward(**feed)
+    ms = time_forwards(engine, L, net, stream, torch, reps)
     n_all = 15 * 63 * 38
-    out["proposal"] = {"images_per_call": images, "ms_per_call": ms, "rois": int(net.blob("rois").shape[0]),
-                       "nms_boxes_per_s": images * min(6000, n_all) / (ms * 1e-3),
-                       "decoded_boxes_per_s": images * n_all / (ms * 1e-3),
-                       "iou_pairs_upper_bound_per_image": 6000 * 5999 // 2}
+    out = {"images_per_call": images, "ms_per_call": ms, "rois": int(net.blob("rois").shape[0]),
+           "nms_boxes_per_s": images * min(6000, n_all) / (ms * 1e-3),
+           "decoded_boxes_per_s": images * n_all / (ms * 1e-3),
+           "iou_pairs_upper_bound_per_image": 6000 * 5999 // 2,
+           "algorithmic_bytes_per_image": 4 * n_all + 16 * n_all + 12 + 24 * 300}
     net.close()
+    return out
+
+
+def detection_output_figure(capi, wl, engine, L, stream, torch, reps=10, images=32):
+    """SSD300 post-processing: 8732 priors, 21 classes, confidence 0.01, NMS 0.45, top_k 400, keep 200,
+    near-uniform class scores (what random-init heads give: every class of every prior passes the
+    threshold, the top_k cut does the work).  boxes/s := 8732 * 20 * images / time."""
+    b = wl.detection_head(batch=images, num_priors=8732, num_classes=21, conf_thr=0.01, nms_thr=0.45, top_k=400,
+                          keep_top_k=200)
+    net = capi.Net(engine, b.text(), None, from_buffer=True)
+    net.forward(**wl.detection_head_input(images, 8732, 21, seed=0))
+    ms = time_forwards(engine, L, net, stream, torch, reps)
+    out = {"images_per_call": images, "ms_per_call": ms, "rows": int(net.blob("detection_out").shape[0]),
+           "boxes_per_s": 8732 * 20 * images / (ms * 1e-3),
+           "algorithmic_bytes_per_image": 4 * (8732 * 4 + 8732 * 21) + 28 * 200}
+    net.close()
+    return out
+
+
+def roi_pooling_figure(capi, wl, engine, L, stream, torch, reps=20):
+    """R-FCN head: 300 rois over 21 x 7 x 7 position-sensitive score maps of 63 x 38."""
+    b = wl.roi_pooling("PSROIPooling", batch=1, height=63, width=38, num_rois=300, output_dim=21, group_size=7)
+    net = capi.Net(engine, b.text(), None, from_buffer=True)
+    net.forward(**wl.roi_pooling_input(1, 21 * 49, 63, 38, 300, seed=0))
+    ms = time_forwards(engine, L, net, stream, torch, reps)
+    out = {"rois": 300, "ms_per_call": ms, "rois_per_s": 300 / (ms * 1e-3),
+           "algorithmic_bytes": 4 * (21 * 49 * 63 * 38 + 300 * 5 + 300 * 21 * 49)}
+    net.close()
+    return out
+
+
+def secondary_figures(capi, wl, engine, L, stream, torch):
+    """The other figures the benchmark definition names, measured after the headline: NMS boxes/s of
+    the RPN Proposal stress case and the TF32 rate of the single 3x3 64->64 convolution at batch 32."""
+    out = {"proposal": proposal_figure(capi, wl, engine, L, stream, torch)}
     # Config 1: Convolution(64, 3x3, pad 1) + ReLU on [32, 64, 56, 56]
     cb = wl.conv_relu(32)
     net = capi.Net(engine, cb.text(), None, from_buffer=True)
@@ -206,6 +243,26 @@ def secondary_figures(capi, wl, engine, L, stream, torch):
                             "algorithmic_bytes": 4 * (2 * 32 * 64 * 56 * 56 + 64 * 64 * 9 + 64)}
     net.close()
     return out
+
+
+def run_tail_workload(args, capi, wl):
+    """`--workload proposal | detection_output | psroi_pooling`: the detection-tail layers on their own
+    (one GPU), for profiler captures and the figures in profiles/.  Prints one JSON line."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("no CUDA device: the engine has no CPU path")
+    engine = capi.CaffeLibrary(ENGINE_LIB)
+    L = engine.lib
+    L.mcb200_current_stream.restype = ctypes.c_void_p
+    L.mcb200_launch_count.restype = ctypes.c_longlong
+    engine.set_mode(True, 0)
+    stream = torch.cuda.ExternalStream(L.mcb200_current_stream(), device=torch.device("cuda", 0))
+    fn = {"proposal": proposal_figure, "detection_output": detection_output_figure,
+          "psroi_pooling": roi_pooling_figure}[args.workload]
+    L.mcb200_launch_count_reset()
+    res = fn(capi, wl, engine, L, stream, torch, reps=args.steps)
+    res.update({"workload": args.workload, "steps": args.steps, "gpu_launches": int(L.mcb200_launch_count())})
+    print(json.dumps(res))
 
 
 def run_reference_arm(args, capi, wl):
@@ -236,6 +293,9 @@ def main():
                     help="images per GPU (the headline metric is quoted at the default; smaller values are for "
                          "profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU reference leg (profiler captures)")
+    ap.add_argument("--workload", default="resnet50",
+                    choices=["resnet50", "proposal", "detection_output", "psroi_pooling"],
+                    help="resnet50 is the benchmark; the others time one detection-tail layer on its own")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -243,6 +303,9 @@ def main():
     wl = importlib.import_module("mini-caffe_b200.workloads")
     if args.impl == "reference":
         run_reference_arm(args, capi, wl)
+        return
+    if args.workload != "resnet50":
+        run_tail_workload(args, capi, wl)
         return
 
     import numpy as np

@@ -238,7 +238,7 @@ int mcb200_proposal_forward(const mcb200_proposal_params* p, int batch, const fl
  * The scratch is a fixed 8 MiB array inside the library's device image (each
  * GPU that loads the library holds it until the process exits).  That covers
  * one image with up to 65536 proposals and pre_nms_topn up to 6000 (the stock
- * R-FCN / Faster-RCNN settings need 6.5 MB); a request that needs more returns
+ * R-FCN / Faster-RCNN settings need 1.1 MB per image); a request that needs more returns
  * -20 and prints the required size.  The function calls no cudaMalloc, cudaFree
  * or any other allocating routine.
  *

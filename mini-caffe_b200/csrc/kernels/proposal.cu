@@ -2,10 +2,10 @@
 //   1. decode      anchor + deltas -> clipped box, min-size filter, sort key
 //   2. top-k sort  per image: radix-select the pre_nms_topn best keys, bitonic
 //                  sort them in shared memory, gather boxes in score order
-//   3. nms mask    64 x 64 IoU tiles of the upper triangle, one 64-bit word per
-//                  (row, column block), built with warp ballots
-//   4. nms scan    per image: greedy pass over the mask, 64 boxes at a time,
-//                  stops at post_nms_topn; writes rois (+ scores) and the count
+//   3. greedy NMS  per image: one block walks the boxes 64 at a time and evaluates
+//                  overlaps only for rows that are kept against columns that are
+//                  still alive; stops at post_nms_topn; writes rois (+ scores)
+//                  and the count
 // The host only reads the per-image counts back.
 //
 // Every float operation that decides which boxes are kept is done with the
@@ -36,7 +36,6 @@ struct Workspace {
   unsigned long long* keys;      // [batch][n]
   float4* sorted_boxes;          // [batch][k]        score order
   float* sorted_scores;          // [batch][k]
-  unsigned long long* mask;      // [batch][k][col_blocks]
   int n, k, col_blocks;
 };
 
@@ -61,7 +60,6 @@ size_t carve(const mcb200_proposal_params& p, int batch, char* base, Workspace* 
   w.keys = reinterpret_cast<unsigned long long*>(take(8 * static_cast<size_t>(n) * batch));
   w.sorted_boxes = reinterpret_cast<float4*>(take(sizeof(float4) * k * static_cast<size_t>(batch)));
   w.sorted_scores = reinterpret_cast<float*>(take(sizeof(float) * k * static_cast<size_t>(batch)));
-  w.mask = reinterpret_cast<unsigned long long*>(take(8 * static_cast<size_t>(k) * cb * batch));
   if (ws) *ws = w;
   return off;
 }
@@ -166,7 +164,7 @@ proposal_topk_sort_kernel(Workspace ws, int padded) {
   }
 }
 
-// ---------------------------------------------------------------- 3. NMS mask
+// ---------------------------------------------------------------- 3a. overlap test
 
 // IoU with the "+1 pixel" convention; areas[i] + areas[j] - inter, IEEE division.
 __device__ __forceinline__ bool suppresses(const float4& a, float area_a, const float4& b, float area_b,
@@ -186,83 +184,103 @@ __device__ __forceinline__ float box_area(const float4& b) {
   return fmul(fadd(fsub(b.z, b.x), 1.f), fadd(fsub(b.w, b.y), 1.f));
 }
 
-// grid: (column block, row block, image); 256 threads = 8 warps, 8 rows each.
-__global__ void __launch_bounds__(256)
-proposal_nms_mask_kernel(Workspace ws, float threshold) {
-  const int col_block = blockIdx.x, row_block = blockIdx.y, image = blockIdx.z;
-  if (col_block < row_block) return;   // only pairs (i, j) with j > i matter
-  __shared__ float4 row_box[64], col_box[64];
-  __shared__ float row_area[64], col_area[64];
-  const int k = ws.k;
-  const float4* boxes = ws.sorted_boxes + static_cast<size_t>(image) * k;
-  const int t = threadIdx.x;
-  if (t < 64) {
-    const int i = row_block * 64 + t;
-    const float4 b = i < k ? boxes[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    row_box[t] = b;
-    row_area[t] = box_area(b);
-  } else if (t < 128) {
-    const int j = col_block * 64 + (t - 64);
-    const float4 b = j < k ? boxes[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-    col_box[t - 64] = b;
-    col_area[t - 64] = box_area(b);
-  }
-  __syncthreads();
-  const int warp = t >> 5, lane = t & 31;
-  for (int r = warp * 8; r < warp * 8 + 8; ++r) {
-    const int i = row_block * 64 + r;
-    if (i >= k) break;
-    unsigned long long word = 0;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int c = half * 32 + lane;
-      const int j = col_block * 64 + c;
-      const bool hit = (j < k) && (j > i) && suppresses(row_box[r], row_area[r], col_box[c], col_area[c], threshold);
-      const unsigned bits = __ballot_sync(0xffffffffu, hit);
-      word |= static_cast<unsigned long long>(bits) << (half * 32);
-    }
-    if (lane == 0) ws.mask[(static_cast<size_t>(image) * k + i) * ws.col_blocks + col_block] = word;
-  }
+// ---------------------------------------------------------------- 3b. greedy suppression + output
+
+constexpr int kNmsThreads = 1024;
+// Boxes of one image are staged in shared memory when they fit (20 bytes each).
+constexpr int kNmsStagedBoxes = 8192;
+// Bytes of the removed set (two 32-bit words per block of 64 boxes), rounded up
+// so that the float4 array behind it starts on a 16-byte boundary.
+__host__ __device__ constexpr size_t nms_removed_bytes(int col_blocks) {
+  return (static_cast<size_t>(col_blocks) * 8 + 15) & ~static_cast<size_t>(15);
 }
 
-// ---------------------------------------------------------------- 4. scan + output
-
-// One block per image.  Boxes are taken 64 at a time: thread 0 resolves the
-// block's own 64 x 64 diagonal word chain in registers, then every thread
-// ORs the kept rows' words of "its" later column block into the removed set.
-__global__ void __launch_bounds__(256)
-proposal_nms_scan_kernel(Workspace ws, int post_nms_topn, float* __restrict__ rois, float* __restrict__ roi_scores,
-                         int* __restrict__ counts) {
-  extern __shared__ unsigned long long removed[];   // col_blocks words
+// One block per image walks the score-ordered boxes 64 at a time.  Per step:
+//   1. all threads: the 64 x 64 overlaps inside the step's block (bit c of
+//      diag[r] = "row r suppresses column c", c > r);
+//   2. thread 0: resolves the block in order (a box is kept unless an earlier
+//      kept box suppresses it), writes the kept boxes out, stops at post_nms_topn;
+//   3. all threads: overlaps of the rows kept in this step with every later box
+//      that is still alive; hits go into the removed set (one 32-bit word per
+//      warp-wide group of columns, so no atomics).
+// Overlaps are evaluated only for rows that are kept and columns that are
+// still alive: a few hundred kept rows x pre_nms_topn columns per image instead
+// of the pre_nms_topn^2 / 2 pairs of a full suppression matrix.  The kept set
+// is the one of the sequential algorithm (src/layers/proposal_layer.cpp:161-186).
+__global__ void __launch_bounds__(kNmsThreads)
+proposal_nms_kernel(Workspace ws, float threshold, int post_nms_topn, int staged, float* __restrict__ rois,
+                    float* __restrict__ roi_scores, int* __restrict__ counts) {
+  extern __shared__ __align__(16) unsigned char nms_smem[];
+  __shared__ unsigned long long diag[64];
   __shared__ unsigned long long keep_word;
   __shared__ int kept_total;
   __shared__ int stop;
   const int image = blockIdx.x;
   const int k = ws.k, cb = ws.col_blocks;
-  const unsigned long long* mask = ws.mask + static_cast<size_t>(image) * k * cb;
-  const float4* boxes = ws.sorted_boxes + static_cast<size_t>(image) * k;
+  const int kpad = cb * 64;
+  const float4* g_boxes = ws.sorted_boxes + static_cast<size_t>(image) * k;
   const float* scores = ws.sorted_scores + static_cast<size_t>(image) * k;
   float* out = rois + static_cast<size_t>(image) * post_nms_topn * 5;
   float* out_scores = roi_scores ? roi_scores + static_cast<size_t>(image) * post_nms_topn : nullptr;
 
-  for (int w = threadIdx.x; w < cb; w += blockDim.x) removed[w] = 0;
-  if (threadIdx.x == 0) {
+  // Shared memory: removed set (2 words per block of 64), then, if staged, boxes and areas.
+  unsigned* removed = reinterpret_cast<unsigned*>(nms_smem);
+  float4* s_boxes = reinterpret_cast<float4*>(nms_smem + nms_removed_bytes(cb));   // 16-byte aligned
+  float* s_area = reinterpret_cast<float*>(s_boxes + kpad);
+  const int t = threadIdx.x;
+  for (int w = t; w < cb * 2; w += kNmsThreads) removed[w] = 0u;
+  if (staged) {
+    for (int i = t; i < kpad; i += kNmsThreads) {
+      const float4 b = i < k ? g_boxes[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      s_boxes[i] = b;
+      s_area[i] = box_area(b);
+    }
+  }
+  if (t == 0) {
     kept_total = 0;
     stop = 0;
   }
   __syncthreads();
+  auto box_at = [&](int i) { return staged ? s_boxes[i] : g_boxes[i]; };
+  auto area_at = [&](int i, const float4& b) { return staged ? s_area[i] : box_area(b); };
+
+  const int warp = t >> 5, lane = t & 31;
   bool done = false;
   for (int block = 0; block < cb && !done; ++block) {
-    if (threadIdx.x == 0) {
-      unsigned long long gone = removed[block];
-      unsigned long long keep = 0;
+    const int base = block * 64;
+    const int rows = min(64, k - base);
+    // ---- 1. overlaps inside the block: thread = (row, group of four columns)
+    if (t < 64) diag[t] = 0ull;
+    __syncthreads();
+    {
+      const int r = t >> 4;
+      const int c0 = (t & 15) * 4;
+      if (r < rows && c0 + 3 > r) {
+        const float4 a = box_at(base + r);
+        const float area_a = area_at(base + r, a);
+        unsigned long long bits = 0ull;
+#pragma unroll
+        for (int c = c0; c < c0 + 4; ++c) {
+          if (c > r && c < rows) {
+            const float4 b = box_at(base + c);
+            if (suppresses(a, area_a, b, area_at(base + c, b), threshold)) bits |= 1ull << c;
+          }
+        }
+        if (bits) atomicOr(&diag[r], bits);
+      }
+    }
+    __syncthreads();
+    // ---- 2. resolve the block in score order
+    if (t == 0) {
+      unsigned long long gone = static_cast<unsigned long long>(removed[2 * block]) |
+                                (static_cast<unsigned long long>(removed[2 * block + 1]) << 32);
+      unsigned long long keep = 0ull;
       int total = kept_total;
-      const int rows = min(64, k - block * 64);
       for (int r = 0; r < rows; ++r) {
         if (!((gone >> r) & 1ull)) {
           keep |= 1ull << r;
-          const int i = block * 64 + r;
-          const float4 b = boxes[i];
+          const int i = base + r;
+          const float4 b = g_boxes[i];
           out[total * 5 + 0] = static_cast<float>(image);
           out[total * 5 + 1] = b.x;
           out[total * 5 + 2] = b.y;
@@ -274,7 +292,7 @@ proposal_nms_scan_kernel(Workspace ws, int post_nms_topn, float* __restrict__ ro
             stop = 1;
             break;
           }
-          gone |= mask[static_cast<size_t>(i) * cb + block];
+          gone |= diag[r];
         }
       }
       keep_word = keep;
@@ -284,22 +302,31 @@ proposal_nms_scan_kernel(Workspace ws, int post_nms_topn, float* __restrict__ ro
     // Everyone takes the same copy of the flag here; thread 0 writes it again
     // only after the barrier that ends this iteration.
     done = stop != 0;
-    if (!done) {
+    // ---- 3. the kept rows against every later box that is still alive
+    if (!done && keep_word != 0ull) {
       const unsigned long long keep = keep_word;
-      for (int w = block + 1 + threadIdx.x; w < cb; w += blockDim.x) {
-        unsigned long long acc = removed[w];
-        unsigned long long bits = keep;
-        while (bits) {
-          const int r = __ffsll(static_cast<long long>(bits)) - 1;
-          bits &= bits - 1;
-          acc |= mask[static_cast<size_t>(block * 64 + r) * cb + w];
+      for (int group = 2 * (block + 1) + warp; group < 2 * cb; group += kNmsThreads / 32) {
+        const int j = group * 32 + lane;
+        const unsigned word = removed[group];
+        bool hit = false;
+        if (j < k && !((word >> lane) & 1u)) {
+          const float4 b = box_at(j);
+          const float area_b = area_at(j, b);
+          unsigned long long bits = keep;
+          while (bits && !hit) {
+            const int r = __ffsll(static_cast<long long>(bits)) - 1;
+            bits &= bits - 1;
+            const float4 a = box_at(base + r);
+            hit = suppresses(a, area_at(base + r, a), b, area_b, threshold);
+          }
         }
-        removed[w] = acc;
+        const unsigned hits = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0 && hits) removed[group] = word | hits;
       }
     }
     __syncthreads();
   }
-  if (threadIdx.x == 0) counts[image] = kept_total;
+  if (t == 0) counts[image] = kept_total;
 }
 
 }  // namespace
@@ -359,13 +386,20 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
     count_launch();
   }
   {
-    dim3 grid(ws.col_blocks, ws.col_blocks, batch);
-    proposal_nms_mask_kernel<<<grid, 256, 0, st>>>(ws, p->nms_thresh);
-    count_launch();
-  }
-  {
-    proposal_nms_scan_kernel<<<batch, 256, static_cast<size_t>(ws.col_blocks) * 8, st>>>(ws, p->post_nms_topn, rois,
-                                                                                          roi_scores, counts);
+    // Boxes and areas of an image go to shared memory when they fit.
+    const int staged = ws.col_blocks * 64 <= kNmsStagedBoxes ? 1 : 0;
+    const size_t smem = nms_removed_bytes(ws.col_blocks) + (staged ? static_cast<size_t>(ws.col_blocks) * 64 * 20 : 0);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    static bool configured[64] = {false};
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(proposal_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kNmsStagedBoxes * 20 + static_cast<int>(nms_removed_bytes(16384 / 64)));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[dev] = true;
+    }
+    proposal_nms_kernel<<<batch, kNmsThreads, smem, st>>>(ws, p->nms_thresh, p->post_nms_topn, staged, rois, roi_scores,
+                                                           counts);
     count_launch();
   }
   return static_cast<int>(cudaGetLastError());
@@ -376,7 +410,7 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
 // Scratch of mcb200_proposal_forward_static.  It lives in the library's device
 // image: every GPU that loads the library carries these 8 MiB until the process
 // exits.  Enough for one image with up to 65536 proposals of which up to 6000
-// go to NMS (6.5 MB); larger requests are refused.
+// go to NMS (1.9 MB); larger requests are refused.
 static constexpr size_t kStaticScratchBytes = static_cast<size_t>(8) << 20;
 static __device__ __align__(256) unsigned char g_proposal_static_scratch[kStaticScratchBytes];
 
@@ -415,8 +449,7 @@ extern "C" int mcb200_proposal_forward_static(const mcb200_proposal_params* p, i
   }
   // Every scratch word the kernels read is written earlier in the same call
   // (keys, boxes and scores for all proposals, the sorted copies for the best
-  // pre_nms_topn, and the mask words on and above the diagonal, which are the
-  // only ones the scan reads), so nothing has to be cleared between calls.
+  // pre_nms_topn), so nothing has to be cleared between calls.
   return mcb200_proposal_forward(p, batch, scores, deltas, im_info, anchors, scratch, rois, roi_scores, counts,
                                  stream);
 }

@@ -440,3 +440,39 @@ def roi_pooling_input(batch, channels, height, width, num_rois, seed=0, feat_str
             x1, y1, w, h = np.floor(x1) + 0.5, np.floor(y1) + 0.5, np.floor(w) + 0.5, np.floor(h)
         rois[r] = (rng.integers(0, batch), x1, y1, x1 + w, y1 + h)
     return {"maps": maps, "rois": rois}
+
+
+# ----------------------------------------------------------------- DetectionOutput alone (the SSD post-processing step)
+
+def detection_head(batch, num_priors, num_classes, conf_thr, nms_thr, top_k, keep_top_k, code_type="CENTER_SIZE",
+                   share_location=True):
+    """Input loc / conf / prior -> DetectionOutput, with the layer's parameters spelled out."""
+    loc_classes = 1 if share_location else num_classes
+    b = NetBuilder("detout")
+    b.input([("loc", (batch, num_priors * loc_classes * 4)), ("conf", (batch, num_priors * num_classes)),
+             ("prior", (1, 2, num_priors * 4))])
+    b.raw("detection_out", "DetectionOutput", ["loc", "conf", "prior"], ["detection_out"],
+          "detection_output_param { num_classes: %d share_location: %s background_label_id: 0 "
+          "nms_param { nms_threshold: %g top_k: %d } code_type: %s keep_top_k: %d confidence_threshold: %g }" %
+          (num_classes, "true" if share_location else "false", nms_thr, top_k, code_type, keep_top_k, conf_thr))
+    return b
+
+
+def detection_head_input(batch, num_priors, num_classes, seed, share_location=True, peaked=False):
+    """loc ~ N(0, 0.5^2); conf = softmax of N(0, s^2) logits (s = 3 "peaked": a few classes pass the
+    threshold per prior; s = 0.3: near-uniform scores, every class passes, the top_k cut does the work);
+    priors uniform in the unit square with SSD's variances (0.1, 0.1, 0.2, 0.2)."""
+    rng = np.random.default_rng(seed)
+    loc_classes = 1 if share_location else num_classes
+    loc = (rng.standard_normal((batch, num_priors * loc_classes * 4)) * 0.5).astype(np.float32)
+    logits = rng.standard_normal((batch, num_priors, num_classes)) * (3.0 if peaked else 0.3)
+    e = np.exp(logits - logits.max(axis=2, keepdims=True))
+    conf = (e / e.sum(axis=2, keepdims=True)).astype(np.float32).reshape(batch, -1)
+    cx = rng.uniform(0.1, 0.9, num_priors)
+    cy = rng.uniform(0.1, 0.9, num_priors)
+    w = rng.uniform(0.05, 0.4, num_priors)
+    h = rng.uniform(0.05, 0.4, num_priors)
+    boxes = np.stack([cx - w / 2, cy - h / 2, cx + w / 2, cy + h / 2], axis=1).astype(np.float32)
+    var = np.tile(np.array([0.1, 0.1, 0.2, 0.2], dtype=np.float32), (num_priors, 1))
+    prior = np.stack([boxes.reshape(-1), var.reshape(-1)])[None].astype(np.float32)
+    return {"loc": loc, "conf": conf, "prior": prior}

@@ -62,34 +62,12 @@ def test_proposal_edge_shapes(capi, gpu_engine, reflib, case):
     assert np.array_equal(got["scores"].view(np.uint32), want["scores"].view(np.uint32))
 
 
-def detection_head_net(wl, batch, num_priors, num_classes, conf_thr, nms_thr, top_k, keep_top_k, code_type="CENTER_SIZE",
-                       share_location=True):
-    loc_classes = 1 if share_location else num_classes
-    b = wl.NetBuilder("detout")
-    b.input([("loc", (batch, num_priors * loc_classes * 4)), ("conf", (batch, num_priors * num_classes)),
-             ("prior", (1, 2, num_priors * 4))])
-    b.raw("detection_out", "DetectionOutput", ["loc", "conf", "prior"], ["detection_out"],
-          "detection_output_param { num_classes: %d share_location: %s background_label_id: 0 "
-          "nms_param { nms_threshold: %g top_k: %d } code_type: %s keep_top_k: %d confidence_threshold: %g }" %
-          (num_classes, "true" if share_location else "false", nms_thr, top_k, code_type, keep_top_k, conf_thr))
-    return b
+def detection_head_net(wl, **case):
+    return wl.detection_head(**case)
 
 
 def detection_inputs(batch, num_priors, num_classes, seed, share_location=True, peaked=False):
-    rng = np.random.default_rng(seed)
-    loc_classes = 1 if share_location else num_classes
-    loc = (rng.standard_normal((batch, num_priors * loc_classes * 4)) * 0.5).astype(np.float32)
-    logits = rng.standard_normal((batch, num_priors, num_classes)) * (3.0 if peaked else 0.3)
-    e = np.exp(logits - logits.max(axis=2, keepdims=True))
-    conf = (e / e.sum(axis=2, keepdims=True)).astype(np.float32).reshape(batch, -1)
-    cx = rng.uniform(0.1, 0.9, num_priors)
-    cy = rng.uniform(0.1, 0.9, num_priors)
-    w = rng.uniform(0.05, 0.4, num_priors)
-    h = rng.uniform(0.05, 0.4, num_priors)
-    boxes = np.stack([cx - w / 2, cy - h / 2, cx + w / 2, cy + h / 2], axis=1).astype(np.float32)
-    var = np.tile(np.array([0.1, 0.1, 0.2, 0.2], dtype=np.float32), (num_priors, 1))
-    prior = np.stack([boxes.reshape(-1), var.reshape(-1)])[None].astype(np.float32)
-    return {"loc": loc, "conf": conf, "prior": prior}
+    return pkg("workloads").detection_head_input(batch, num_priors, num_classes, seed, share_location, peaked)
 
 
 def sort_rows(rows):
@@ -124,7 +102,8 @@ def test_detection_output_bit_exact(capi, gpu_engine, reflib, case):
 
 def test_detection_output_no_detections(capi, gpu_engine, reflib):
     wl = pkg("workloads")
-    b = detection_head_net(wl, 2, 50, 3, conf_thr=2.0, nms_thr=0.45, top_k=10, keep_top_k=5)
+    b = detection_head_net(wl, batch=2, num_priors=50, num_classes=3, conf_thr=2.0, nms_thr=0.45, top_k=10,
+                           keep_top_k=5)
     inputs = detection_inputs(2, 50, 3, seed=3)
     got = run_net(capi, gpu_engine, b, {}, inputs, ["detection_out"])["detection_out"]
     want = run_net(capi, reflib, b, {}, inputs, ["detection_out"])["detection_out"]
