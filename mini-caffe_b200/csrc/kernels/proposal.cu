@@ -189,29 +189,31 @@ __device__ __forceinline__ float box_area(const float4& b) {
 constexpr int kNmsThreads = 1024;
 // Boxes of one image are staged in shared memory when they fit (20 bytes each).
 constexpr int kNmsStagedBoxes = 8192;
-// Bytes of the removed set (two 32-bit words per block of 64 boxes), rounded up
-// so that the float4 array behind it starts on a 16-byte boundary.
-__host__ __device__ constexpr size_t nms_removed_bytes(int col_blocks) {
-  return (static_cast<size_t>(col_blocks) * 8 + 15) & ~static_cast<size_t>(15);
+
+// Bytes in front of the staged boxes: the indices of the kept boxes (at most
+// post_nms_topn), rounded up so that the float4 array starts on a 16-byte boundary.
+__host__ __device__ constexpr size_t nms_kept_bytes(int post_nms_topn) {
+  return (static_cast<size_t>(post_nms_topn) * 4 + 15) & ~static_cast<size_t>(15);
 }
 
 // One block per image walks the score-ordered boxes 64 at a time.  Per step:
-//   1. all threads: the 64 x 64 overlaps inside the step's block (bit c of
-//      diag[r] = "row r suppresses column c", c > r);
+//   1. all threads: which of the step's 64 boxes does an already kept box
+//      suppress (kept boxes x 64 columns), and the 64 x 64 overlaps inside the
+//      block (bit c of diag[r] = "row r suppresses column c", c > r);
 //   2. thread 0: resolves the block in order (a box is kept unless an earlier
-//      kept box suppresses it), writes the kept boxes out, stops at post_nms_topn;
-//   3. all threads: overlaps of the rows kept in this step with every later box
-//      that is still alive; hits go into the removed set (one 32-bit word per
-//      warp-wide group of columns, so no atomics).
-// Overlaps are evaluated only for rows that are kept and columns that are
-// still alive: a few hundred kept rows x pre_nms_topn columns per image instead
-// of the pre_nms_topn^2 / 2 pairs of a full suppression matrix.  The kept set
-// is the one of the sequential algorithm (src/layers/proposal_layer.cpp:161-186).
+//      kept box suppresses it) and stops at post_nms_topn; the kept boxes are
+//      then written out and appended to the kept list in parallel.
+// Overlaps are evaluated lazily, only between kept boxes and the boxes the walk
+// actually reaches: at most post_nms_topn x pre_nms_topn pairs, and far fewer
+// when the walk ends early, instead of the pre_nms_topn^2 / 2 pairs of a full
+// suppression matrix.  The kept set is that of the sequential algorithm
+// (src/layers/proposal_layer.cpp:161-186).
 __global__ void __launch_bounds__(kNmsThreads)
 proposal_nms_kernel(Workspace ws, float threshold, int post_nms_topn, int staged, float* __restrict__ rois,
                     float* __restrict__ roi_scores, int* __restrict__ counts) {
   extern __shared__ __align__(16) unsigned char nms_smem[];
   __shared__ unsigned long long diag[64];
+  __shared__ unsigned long long gone_word;   // columns of the current block that kept boxes suppress
   __shared__ unsigned long long keep_word;
   __shared__ int kept_total;
   __shared__ int stop;
@@ -223,12 +225,10 @@ proposal_nms_kernel(Workspace ws, float threshold, int post_nms_topn, int staged
   float* out = rois + static_cast<size_t>(image) * post_nms_topn * 5;
   float* out_scores = roi_scores ? roi_scores + static_cast<size_t>(image) * post_nms_topn : nullptr;
 
-  // Shared memory: removed set (2 words per block of 64), then, if staged, boxes and areas.
-  unsigned* removed = reinterpret_cast<unsigned*>(nms_smem);
-  float4* s_boxes = reinterpret_cast<float4*>(nms_smem + nms_removed_bytes(cb));   // 16-byte aligned
+  int* kept = reinterpret_cast<int*>(nms_smem);
+  float4* s_boxes = reinterpret_cast<float4*>(nms_smem + nms_kept_bytes(post_nms_topn));   // 16-byte aligned
   float* s_area = reinterpret_cast<float*>(s_boxes + kpad);
   const int t = threadIdx.x;
-  for (int w = t; w < cb * 2; w += kNmsThreads) removed[w] = 0u;
   if (staged) {
     for (int i = t; i < kpad; i += kNmsThreads) {
       const float4 b = i < k ? g_boxes[i] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -244,14 +244,30 @@ proposal_nms_kernel(Workspace ws, float threshold, int post_nms_topn, int staged
   auto box_at = [&](int i) { return staged ? s_boxes[i] : g_boxes[i]; };
   auto area_at = [&](int i, const float4& b) { return staged ? s_area[i] : box_area(b); };
 
-  const int warp = t >> 5, lane = t & 31;
   bool done = false;
   for (int block = 0; block < cb && !done; ++block) {
     const int base = block * 64;
     const int rows = min(64, k - base);
-    // ---- 1. overlaps inside the block: thread = (row, group of four columns)
     if (t < 64) diag[t] = 0ull;
+    if (t == 0) gone_word = 0ull;
+    const int total_before = kept_total;   // read before the barrier: thread 0 updates it in step 2
     __syncthreads();
+    // ---- 1a. kept boxes against this block: thread = (column, every 16th kept box)
+    {
+      const int c = t & 63;
+      if (c < rows) {
+        const float4 b = box_at(base + c);
+        const float area_b = area_at(base + c, b);
+        bool hit = false;
+        for (int q = t >> 6; q < total_before && !hit; q += kNmsThreads / 64) {
+          const int i = kept[q];
+          const float4 a = box_at(i);
+          hit = suppresses(a, area_at(i, a), b, area_b, threshold);
+        }
+        if (hit) atomicOr(&gone_word, 1ull << c);
+      }
+    }
+    // ---- 1b. overlaps inside the block: thread = (row, group of four columns)
     {
       const int r = t >> 4;
       const int c0 = (t & 15) * 4;
@@ -272,21 +288,12 @@ proposal_nms_kernel(Workspace ws, float threshold, int post_nms_topn, int staged
     __syncthreads();
     // ---- 2. resolve the block in score order
     if (t == 0) {
-      unsigned long long gone = static_cast<unsigned long long>(removed[2 * block]) |
-                                (static_cast<unsigned long long>(removed[2 * block + 1]) << 32);
+      unsigned long long gone = gone_word;
       unsigned long long keep = 0ull;
-      int total = kept_total;
+      int total = total_before;
       for (int r = 0; r < rows; ++r) {
         if (!((gone >> r) & 1ull)) {
           keep |= 1ull << r;
-          const int i = base + r;
-          const float4 b = g_boxes[i];
-          out[total * 5 + 0] = static_cast<float>(image);
-          out[total * 5 + 1] = b.x;
-          out[total * 5 + 2] = b.y;
-          out[total * 5 + 3] = b.z;
-          out[total * 5 + 4] = b.w;
-          if (out_scores) out_scores[total] = scores[i];
           ++total;
           if (total == post_nms_topn) {
             stop = 1;
@@ -299,31 +306,21 @@ proposal_nms_kernel(Workspace ws, float threshold, int post_nms_topn, int staged
       kept_total = total;
     }
     __syncthreads();
-    // Everyone takes the same copy of the flag here; thread 0 writes it again
-    // only after the barrier that ends this iteration.
-    done = stop != 0;
-    // ---- 3. the kept rows against every later box that is still alive
-    if (!done && keep_word != 0ull) {
-      const unsigned long long keep = keep_word;
-      for (int group = 2 * (block + 1) + warp; group < 2 * cb; group += kNmsThreads / 32) {
-        const int j = group * 32 + lane;
-        const unsigned word = removed[group];
-        bool hit = false;
-        if (j < k && !((word >> lane) & 1u)) {
-          const float4 b = box_at(j);
-          const float area_b = area_at(j, b);
-          unsigned long long bits = keep;
-          while (bits && !hit) {
-            const int r = __ffsll(static_cast<long long>(bits)) - 1;
-            bits &= bits - 1;
-            const float4 a = box_at(base + r);
-            hit = suppresses(a, area_at(base + r, a), b, area_b, threshold);
-          }
-        }
-        const unsigned hits = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0 && hits) removed[group] = word | hits;
-      }
+    if (t < rows && ((keep_word >> t) & 1ull)) {
+      const int pos = total_before + __popcll(keep_word & ((1ull << t) - 1ull));
+      const int i = base + t;
+      kept[pos] = i;
+      const float4 b = g_boxes[i];
+      out[pos * 5 + 0] = static_cast<float>(image);
+      out[pos * 5 + 1] = b.x;
+      out[pos * 5 + 2] = b.y;
+      out[pos * 5 + 3] = b.z;
+      out[pos * 5 + 4] = b.w;
+      if (out_scores) out_scores[pos] = scores[i];
     }
+    // Everyone takes the same copy of the flag here; thread 0 writes it again
+    // only after the next iteration's first barrier.
+    done = stop != 0;
     __syncthreads();
   }
   if (t == 0) counts[image] = kept_total;
@@ -388,13 +385,14 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
   {
     // Boxes and areas of an image go to shared memory when they fit.
     const int staged = ws.col_blocks * 64 <= kNmsStagedBoxes ? 1 : 0;
-    const size_t smem = nms_removed_bytes(ws.col_blocks) + (staged ? static_cast<size_t>(ws.col_blocks) * 64 * 20 : 0);
+    const size_t smem = nms_kept_bytes(p->post_nms_topn) + (staged ? static_cast<size_t>(ws.col_blocks) * 64 * 20 : 0);
+    if (smem > 220 * 1024) return -7;   // post_nms_topn beyond 10000 with staged boxes: not a detector's setting
     int dev = 0;
     cudaGetDevice(&dev);
     static bool configured[64] = {false};
     if (dev >= 0 && dev < 64 && !configured[dev]) {
       const cudaError_t e = cudaFuncSetAttribute(proposal_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kNmsStagedBoxes * 20 + static_cast<int>(nms_removed_bytes(16384 / 64)));
+                                                 220 * 1024);
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[dev] = true;
     }
