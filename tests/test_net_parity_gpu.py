@@ -122,3 +122,25 @@ def test_cli_on_public_headers_runs_a_net(tmp_path):
     assert run.stderr.count("Forward costs") == 3
     events = json.load(open(tmp_path / "profile.json"))["traceEvents"]
     assert any(e["name"] == "res2a_branch2b" for e in events)
+
+
+def test_folded_model_files_run_the_same(capi, gpu_engine, tmp_path):
+    """fuse_bn's output files through the engine: same function as the unfolded files (the engine
+    folds the unfolded ones in memory, the tool folded the others on disk)."""
+    import os
+    import subprocess
+    from test_fuse_bn_cpu import EXE, build_case
+    if not os.path.isfile(EXE):
+        pytest.skip("fuse_bn not built")
+    wl = pkg("workloads")
+    b, weights, proto, model = build_case(wl, tmp_path)
+    subprocess.run([EXE, "--net", str(proto), "--weight", str(model)], check=True, capture_output=True, timeout=120)
+    x = np.random.default_rng(8).standard_normal((2, 6, 12, 10)).astype(np.float32)
+    outs = {}
+    for tag, p, m in (("orig", proto, model), ("fold", tmp_path / "net_nobn.prototxt", tmp_path / "net_nobn.caffemodel")):
+        net = capi.Net(gpu_engine, str(p), str(m))
+        net.forward(data=x)
+        outs[tag] = {name: net.blob(name).data.copy() for name in ("gap", "c3")}
+        net.close()
+    for name in ("gap", "c3"):
+        assert_close(outs["fold"][name], outs["orig"][name], name)
