@@ -303,6 +303,45 @@ int mcb200_psroi_pool(const float* data_nchw, const float* rois, float* out, int
                       int output_dim, int group_size, int height, int width, float spatial_scale, int* status,
                       void* stream);
 
+/* Deconvolution (transposed convolution), (N, C, H, W) in and out, fp32 FMA
+ * arithmetic, one thread per output element.  `s` describes the input (n, c, h,
+ * w) and the filter; mcb200_deconv_out_shape fills ho = stride*(h-1) +
+ * dil*(kh-1) + 1 - 2*pad (src/layers/deconv_layer.cpp:7-25).  Weights are
+ * [c, cout/group, kh, kw] as Caffe stores them for this layer; bias may be null.
+ * Replaces backward_cpu_gemm + col2im + forward_cpu_bias
+ * (src/layers/deconv_layer.cpp:27-44, src/layers/base_conv_layer.cpp:280-296). */
+int mcb200_deconv_out_shape(mcb200_conv_shape* s);
+int mcb200_deconv_direct(const mcb200_conv_shape* s, const float* in_nchw, const float* w_iohw, const float* bias,
+                         float* out_nchw, void* stream);
+
+/* Crop: out[idx] = in[idx + offsets] over up to six axes
+ * (src/layers/crop_layer.cpp:57-100).                                         */
+int mcb200_crop(const float* in, float* out, int num_axes, const int* in_shape, const int* out_shape,
+                const int* offsets, void* stream);
+
+/* Local response normalisation over (N, C, H, W).  within_channel == 0:
+ * y = x * (k + alpha/size * sum of x^2 over `size` neighbouring channels)^-beta
+ * (src/layers/lrn_layer.cpp:107-150); within_channel == 1:
+ * y = x * (1 + alpha * mean of x^2 over a size x size window)^-beta, the mean
+ * taken like the reference's padded AVE pooling (src/layers/lrn_layer.cpp:19-66). */
+int mcb200_lrn(const float* in_nchw, float* out_nchw, int n, int c, int h, int w, int local_size, float alpha,
+               float beta, float k, int within_channel, void* stream);
+
+/* BatchNorm with statistics of the current batch (use_global_stats: false, as
+ * the shipped WGAN generator runs it): per channel, mean and variance over all
+ * images and pixels, written as the scale = 1 / sqrt(var + eps) and shift =
+ * -mean * scale of mcb200_channel_affine_act (src/layers/batch_norm_layer.cpp:91-135).
+ * Element (image, channel, position) lives at ((image * channels + channel) *
+ * inner + position); inner = 1 for channels-last data.                         */
+int mcb200_channel_batch_stats(const float* x, long long count, int channels, int inner, float eps, float* scale,
+                               float* shift, void* stream);
+
+/* y = tanh(x) or y = 1 / (1 + exp(-x)), elementwise, any layout
+ * (src/layers/tanh_layer.cpp:10-18, src/layers/sigmoid_layer.cpp:10-22).      */
+#define MCB200_UNARY_TANH 0
+#define MCB200_UNARY_SIGMOID 1
+int mcb200_unary(const float* x, float* y, long long count, int op, void* stream);
+
 /* Number of kernels launched by this library on the calling thread since the
  * last reset (bench.py reports it as gpu_launches).                          */
 long long mcb200_launch_count(void);

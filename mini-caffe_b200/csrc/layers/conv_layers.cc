@@ -86,13 +86,11 @@ void FillTailEpilogue(const FusedTail& tail, const DeviceArray& scale, const Dev
 
 // ---------------------------------------------------------------- Convolution
 
-void ConvolutionLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
-  const ConvolutionParameter& p = layer_param_.convolution_param();
-  const int channel_axis = bottom[0]->CanonicalAxisIndex(p.axis());
-  const int spatial_axes = bottom[0]->num_axes() - channel_axis - 1;
-  CHECK(channel_axis == 1 && spatial_axes == 2)
-      << "this engine implements 2-D convolution over (N, C, H, W) blobs; got axis " << channel_axis << " with "
-      << spatial_axes << " spatial axes";
+// Kernel, stride, pad and dilation of a 2-D convolution from either the _h/_w
+// fields or the repeated fields (src/layers/base_conv_layer.cpp:22-88, same rules
+// and messages).
+void ParseConvolutionGeometry(const ConvolutionParameter& p, mcb200_conv_shape* shape) {
+  mcb200_conv_shape& s = *shape;
   auto pick = [&](bool has_h, bool has_w, int vh, int vw, int rep_size, const char* what, int dflt, int* oh, int* ow,
                   auto rep) {
     if (has_h || has_w) {
@@ -107,7 +105,6 @@ void ConvolutionLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob
       *ow = rep_size == 0 ? dflt : static_cast<int>(rep(rep_size == 1 ? 0 : 1));
     }
   };
-  mcb200_conv_shape& s = shape_;
   CHECK(p.has_kernel_h() || p.has_kernel_w() || p.kernel_size_size() > 0) << "kernel_size must be specified";
   pick(p.has_kernel_h(), p.has_kernel_w(), p.kernel_h(), p.kernel_w(), p.kernel_size_size(), "kernel_size", 0, &s.kh,
        &s.kw, [&](int i) { return p.kernel_size(i); });
@@ -122,6 +119,18 @@ void ConvolutionLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob
   pick(false, false, 0, 0, p.dilation_size(), "dilation", 1, &s.dil_h, &s.dil_w, [&](int i) { return p.dilation(i); });
   CHECK_GT(s.dil_h, 0);
   CHECK_GT(s.dil_w, 0);
+
+}
+
+void ConvolutionLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  const ConvolutionParameter& p = layer_param_.convolution_param();
+  const int channel_axis = bottom[0]->CanonicalAxisIndex(p.axis());
+  const int spatial_axes = bottom[0]->num_axes() - channel_axis - 1;
+  CHECK(channel_axis == 1 && spatial_axes == 2)
+      << "this engine implements 2-D convolution over (N, C, H, W) blobs; got axis " << channel_axis << " with "
+      << spatial_axes << " spatial axes";
+  mcb200_conv_shape& s = shape_;
+  ParseConvolutionGeometry(p, &s);
 
   s.c = bottom[0]->shape(1);
   s.cout = static_cast<int>(p.num_output());

@@ -60,9 +60,7 @@ void ChannelwiseLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
 
 void BatchNormLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   const BatchNormParameter& p = layer_param_.batch_norm_param();
-  if (p.has_use_global_stats()) {
-    CHECK(p.use_global_stats()) << "BatchNorm: only inference with stored statistics is implemented";
-  }
+  use_global_stats_ = !p.has_use_global_stats() || p.use_global_stats();   // src/layers/batch_norm_layer.cpp:11-13
   channels_ = bottom[0]->num_axes() == 1 ? 1 : bottom[0]->shape(1);
   eps_ = p.eps();
   if (blobs_.empty()) {
@@ -81,6 +79,7 @@ void BatchNormLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>
 // mean = var = 0); y = (x - mean) / sqrt(var + eps)
 // (src/layers/batch_norm_layer.cpp:83-135).  Evaluated in float like there.
 bool BatchNormLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) {
+  if (!use_global_stats_) return false;   // depends on the data: cannot be folded into a producer
   if (channels != channels_ || blobs_.size() != 3) return false;
   if (!scale) return true;
   const float factor_raw = blobs_[2]->cpu_data()[0];
@@ -97,6 +96,30 @@ bool BatchNormLayer::AsChannelAffine(int channels, std::vector<double>* scale, s
     (*shift)[c] = -static_cast<double>(m) * inv_std;
   }
   return true;
+}
+
+// With use_global_stats: false the mean and variance come from the batch at hand
+// (src/layers/batch_norm_layer.cpp:91-118): one reduction kernel writes the
+// per-channel scale and shift, the affine kernel applies them.
+void BatchNormLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  if (use_global_stats_) {
+    ChannelwiseLayer::Forward_gpu(bottom, top);
+    return;
+  }
+  Context& ctx = Context::Get();
+  if (bottom[0]->count() == 0) return;
+  CHECK_EQ(Channels(bottom[0]), channels_);
+  float* scale = batch_scale_shift_.Reserve(2 * static_cast<size_t>(channels_));
+  float* shift = scale + channels_;
+  const bool nhwc = bottom[0]->device_is_nhwc();
+  const float* x = nhwc ? bottom[0]->gpu_data_nhwc() : bottom[0]->gpu_data();
+  float* y = nhwc ? top[0]->mutable_gpu_data_nhwc() : top[0]->mutable_gpu_data();
+  const int inner = nhwc ? 1 : (bottom[0]->num_axes() > 2 ? bottom[0]->count(2) : 1);
+  KERNEL_CHECK(mcb200_channel_batch_stats(x, bottom[0]->count(), channels_, inner, eps_, scale, shift,
+                                          ctx.stream_ptr()));
+  mcb200_epilogue ep = mcb200_epilogue();
+  KERNEL_CHECK(mcb200_channel_affine_act(x, y, bottom[0]->count(), channels_, inner, scale, shift, &ep,
+                                         ctx.stream_ptr()));
 }
 
 REGISTER_LAYER_CLASS(BatchNorm);

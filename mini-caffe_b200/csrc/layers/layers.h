@@ -131,9 +131,13 @@ class BatchNormLayer : public ChannelwiseLayer {
   const char* type() const override { return "BatchNorm"; }
   int ExactNumBottomBlobs() const override { return 1; }
   bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
  private:
   int channels_ = 0;
   float eps_ = 1e-5f;
+  bool use_global_stats_ = true;   // false: normalise with the statistics of the current batch
+  DeviceScratch batch_scale_shift_;
 };
 
 class ScaleLayer : public ChannelwiseLayer {
@@ -386,6 +390,104 @@ class DetectionOutputLayer : public Layer {
   mcb200_detout_params params_ = mcb200_detout_params();
   std::unique_ptr<Blob> workspace_;
   std::unique_ptr<BlobInt> total_;
+};
+
+// Kernel, stride, pad and dilation of a 2-D convolution-type layer.
+void ParseConvolutionGeometry(const ConvolutionParameter& p, mcb200_conv_shape* shape);
+
+// ---------------------------------------------------------------- layer types of the shipped example nets
+// (SSH: Deconvolution + Crop; WGAN generator: Deconvolution; older nets: LRN, Slice, BN.)
+// They work on (N, C, H, W) device data; parity first, no fusion.
+
+// Transposed convolution (src/layers/deconv_layer.cpp:7-44); weights [C_in, C_out / group, kh, kw].
+class DeconvolutionLayer : public Layer {
+ public:
+  explicit DeconvolutionLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Deconvolution"; }
+  int MinBottomBlobs() const override { return 1; }
+  int MinTopBlobs() const override { return 1; }
+  bool EqualNumBottomTopBlobs() const override { return true; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  mcb200_conv_shape shape_ = mcb200_conv_shape();
+  bool bias_term_ = false;
+};
+
+// top[i] = a range of bottom[0] along one axis (src/layers/slice_layer.cpp:9-96).
+class SliceLayer : public Layer {
+ public:
+  explicit SliceLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Slice"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int MinTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int slice_axis_ = 1;
+  vector<int> slice_point_;
+};
+
+// top = bottom[0] cut to the size of bottom[1] from `axis` on, at given offsets
+// (src/layers/crop_layer.cpp:12-106).
+class CropLayer : public Layer {
+ public:
+  explicit CropLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "Crop"; }
+  int ExactNumBottomBlobs() const override { return 2; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  vector<int> offsets_;
+};
+
+// Batch normalisation with the scale and shift in the same layer and stored
+// statistics: y = (x - b2) * b3 * b0 + b1 with blobs slope, bias, mean and the
+// factor the reference multiplies by (src/layers/bn_layer.cpp:10-140).
+class BNLayer : public ChannelwiseLayer {
+ public:
+  explicit BNLayer(const LayerParameter& param) : ChannelwiseLayer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "BN"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+ private:
+  int channels_ = 0;
+};
+
+// Local response normalisation (src/layers/lrn_layer.cpp:10-160).
+class LRNLayer : public Layer {
+ public:
+  explicit LRNLayer(const LayerParameter& param) : Layer(param) {}
+  void LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  const char* type() const override { return "LRN"; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int size_ = 5;
+  float alpha_ = 1.f, beta_ = 0.75f, k_ = 1.f;
+  bool within_channel_ = false;
+  std::unique_ptr<Blob> in_place_copy_;
+};
+
+// TanH and Sigmoid (the output non-linearity of the WGAN generator and of older heads).
+class UnaryLayer : public Layer {
+ public:
+  UnaryLayer(const LayerParameter& param, int op, const char* type) : Layer(param), op_(op), type_(type) {}
+  void Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) override { top[0]->ReshapeLike(*bottom[0]); }
+  const char* type() const override { return type_; }
+  int ExactNumBottomBlobs() const override { return 1; }
+  int ExactNumTopBlobs() const override { return 1; }
+ protected:
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  int op_;
+  const char* type_;
 };
 
 // Region-of-interest pooling behind Proposal (Faster R-CNN / R-FCN heads).

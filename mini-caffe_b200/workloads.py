@@ -476,3 +476,43 @@ def detection_head_input(batch, num_priors, num_classes, seed, share_location=Tr
     var = np.tile(np.array([0.1, 0.1, 0.2, 0.2], dtype=np.float32), (num_priors, 1))
     prior = np.stack([boxes.reshape(-1), var.reshape(-1)])[None].astype(np.float32)
     return {"loc": loc, "conf": conf, "prior": prior}
+
+
+# ----------------------------------------------------------------- layer types of the shipped example nets
+
+def extra_layers_net(batch=2):
+    """A small network through Deconvolution (plain, strided + padded, grouped, dilated), Crop, Slice,
+    BN and both LRN variants, shaped like their uses in the SSH detector and the WGAN generator."""
+    b = NetBuilder("extra_layers")
+    b.input([("data", (batch, 6, 9, 7)), ("like", (batch, 4, 13, 11))])
+    b.raw("up", "Deconvolution", ["data"], ["up"],
+          "convolution_param { num_output: 4 kernel_size: 4 stride: 2 pad: 1 }")
+    b.params.append(("up_0", (6, 4, 4, 4), "he", 6 * 16))
+    b.params.append(("up_1", (4,), "uniform", 0))
+    b.raw("up_g", "Deconvolution", ["data"], ["up_g"],
+          "convolution_param { num_output: 6 kernel_size: 3 stride: 1 pad: 1 group: 3 bias_term: false }")
+    b.params.append(("up_g_0", (6, 2, 3, 3), "he", 18))
+    b.raw("up_d", "Deconvolution", ["data"], ["up_d"],
+          "convolution_param { num_output: 3 kernel_h: 2 kernel_w: 3 stride_h: 3 stride_w: 2 dilation: 2 }")
+    b.params.append(("up_d_0", (6, 3, 2, 3), "he", 36))
+    b.params.append(("up_d_1", (3,), "uniform", 0))
+    b.raw("crop", "Crop", ["up", "like"], ["crop"], "crop_param { axis: 2 offset: 2 offset: 1 }")
+    b.raw("crop1", "Crop", ["up", "like"], ["crop1"], "crop_param { axis: 2 offset: 1 }")
+    b.raw("slice", "Slice", ["up_g"], ["s0", "s1", "s2"], "slice_param { axis: 1 slice_point: 1 slice_point: 4 }")
+    b.raw("slice_even", "Slice", ["up"], ["e0", "e1"], "slice_param { axis: 2 }")
+    b.raw("bn", "BN", ["crop"], ["bn"], "bn_param { frozen: true }")
+    for i, kind in enumerate(("gamma", "beta", "bn_mean", "bn_var")):
+        b.params.append(("bn_%d" % i, (1, 4), kind, 0))
+    b.raw("lrn_a", "LRN", ["up_g"], ["lrn_a"], "lrn_param { local_size: 5 alpha: 0.0001 beta: 0.75 k: 2 }")
+    b.raw("lrn_w", "LRN", ["bn"], ["lrn_w"],
+          "lrn_param { local_size: 3 alpha: 0.05 beta: 0.75 norm_region: WITHIN_CHANNEL }")
+    return b
+
+
+EXTRA_LAYER_OUTPUTS = ("up", "up_g", "up_d", "crop", "crop1", "s0", "s1", "s2", "e0", "e1", "bn", "lrn_a", "lrn_w")
+
+
+def extra_layers_input(batch=2, seed=0):
+    rng = np.random.default_rng(seed + 7000)
+    return {"data": rng.standard_normal((batch, 6, 9, 7)).astype(np.float32),
+            "like": np.zeros((batch, 4, 13, 11), dtype=np.float32)}

@@ -260,3 +260,72 @@ def psroi_pooling(maps, rois, output_dim, group_size, spatial_scale):
                             acc = F(acc + plane[y, x])
                     out[r, ch, ph, pw] = F(acc / F((he - hs) * (we - ws)))
     return out
+
+
+def deconvolution(x, weight, bias=None, stride=1, pad=0, dilation=1, group=1):
+    """Transposed convolution: every input pixel scatters weight[ci, co] * x into the output at
+    (iy * stride - pad + r * dilation, ...); weight is [C_in, C_out / group, kh, kw]; out = stride * (in - 1)
+    + dilation * (k - 1) + 1 - 2 * pad.  src/layers/deconv_layer.cpp:7-44 (GEMM with the transposed
+    weights, then col2im), src/layers/base_conv_layer.cpp:280-296."""
+    n, c, h, w = x.shape
+    _, cout_g, kh, kw = weight.shape
+    cin_g = c // group
+    ho = stride * (h - 1) + dilation * (kh - 1) + 1 - 2 * pad
+    wo = stride * (w - 1) + dilation * (kw - 1) + 1 - 2 * pad
+    full = np.zeros((n, cout_g * group, ho + 2 * pad, wo + 2 * pad), dtype=np.float64)
+    for g in range(group):
+        xg = x[:, g * cin_g:(g + 1) * cin_g].astype(np.float64)
+        wg = weight[g * cin_g:(g + 1) * cin_g].astype(np.float64)
+        for r in range(kh):
+            for q in range(kw):
+                contrib = np.einsum("nchw,co->nohw", xg, wg[:, :, r, q])
+                y0, x0 = r * dilation, q * dilation
+                full[:, g * cout_g:(g + 1) * cout_g, y0:y0 + stride * (h - 1) + 1:stride,
+                     x0:x0 + stride * (w - 1) + 1:stride] += contrib
+    out = full[:, :, pad:pad + ho, pad:pad + wo]
+    if bias is not None:
+        out = out + bias.astype(np.float64).reshape(1, -1, 1, 1)
+    return out.astype(F)
+
+
+def lrn(x, local_size=5, alpha=1.0, beta=0.75, k=1.0, within_channel=False):
+    """ACROSS_CHANNELS: y = x * (k + alpha/size * sum of x^2 over `size` neighbouring channels)^-beta
+    (src/layers/lrn_layer.cpp:107-150).  WITHIN_CHANNEL: y = x * (1 + alpha * AVE-pool(x^2, size, pad
+    (size-1)/2))^-beta, the pooling being the reference's (divides by the window clipped to the padded
+    plane) (src/layers/lrn_layer.cpp:19-66,152-159)."""
+    if within_channel:
+        pooled = pooling((x.astype(F) ** 2).astype(F), "AVE", local_size, stride=1, pad=(local_size - 1) // 2)
+        return (x * np.power(F(1) + F(alpha) * pooled, F(-beta))).astype(F)
+    n, c, h, w = x.shape
+    pre = (local_size - 1) // 2
+    sq = np.zeros((n, c + local_size - 1, h, w), dtype=F)
+    sq[:, pre:pre + c] = x.astype(F) ** 2
+    scale = np.full(x.shape, F(k), dtype=F)
+    for j in range(local_size):
+        scale += F(alpha / local_size) * sq[:, j:j + c]
+    return (x * np.power(scale, F(-beta))).astype(F)
+
+
+def bn(x, slope, bias, mean, factor):
+    """Inference path of the fused-parameter BN layer: y = ((x - mean) * factor) * slope + bias, `factor`
+    being what the layer's fourth blob holds (src/layers/bn_layer.cpp:66-133)."""
+    shape = (1, -1) + (1,) * (x.ndim - 2)
+    y = (x - mean.astype(F).reshape(shape)) * factor.astype(F).reshape(shape)
+    return (y * slope.astype(F).reshape(shape) + bias.astype(F).reshape(shape)).astype(F)
+
+
+def slice_blob(x, axis, slice_points=None, num_tops=None):
+    """src/layers/slice_layer.cpp:18-96."""
+    if slice_points:
+        return [a.astype(F) for a in np.split(x, list(slice_points), axis=axis)]
+    return [a.astype(F) for a in np.split(x, num_tops, axis=axis)]
+
+
+def crop(x, like_shape, axis=2, offsets=(0,)):
+    """Cut x to like_shape from `axis` on, starting at the offsets (one for all axes, or one per
+    cropped axis).  src/layers/crop_layer.cpp:28-100."""
+    idx = [slice(None)] * x.ndim
+    for i in range(axis, x.ndim):
+        off = offsets[0] if len(offsets) == 1 else offsets[i - axis]
+        idx[i] = slice(off, off + like_shape[i])
+    return np.ascontiguousarray(x[tuple(idx)]).astype(F)

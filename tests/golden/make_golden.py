@@ -26,13 +26,10 @@ wl = importlib.import_module("mini-caffe_b200.workloads")
 REF = capi.CaffeLibrary(os.path.join(ROOT, "oracle", "_ref", "libcaffe_ref.so"))
 
 
-def run(builder, weights, inputs, outputs):
-    net = capi.Net(REF, builder.text(), None, from_buffer=True)
-    net.set_params(weights)
-    net.forward(**inputs)
-    res = {name: net.blob(name).data.copy() for name in outputs}
-    net.close()
-    return res
+def run(builder, weights, inputs, outputs, marks=()):
+    """One network through the reference, in a thread of its own (see tests/parity.py)."""
+    from parity import run_net
+    return run_net(capi, REF, builder, weights, inputs, outputs, marks=marks)
 
 
 def save(name, **arrays):
@@ -66,13 +63,7 @@ def dense_layers():
     x = {"data": rng.standard_normal((2, 6, 11, 9)).astype(np.float32)}
     outs = ["conv", "dw", "prelu", "pmax", "pave", "dil", "sum", "norm", "perm", "cat", "gap", "fc", "prob"]
     marks = outs
-    net = capi.Net(REF, b.text(), None, from_buffer=True)
-    for m in marks:
-        net.mark_output(m)
-    net.set_params(weights)
-    net.forward(**x)
-    res = {name: net.blob(name).data.copy() for name in outs}
-    net.close()
+    res = run(b, weights, x, outs, marks=marks)
     arrays = {"in_data": x["data"]}
     arrays.update({"w_" + k: v for k, v in weights.items()})
     arrays.update({"out_" + k: v for k, v in res.items()})
@@ -143,8 +134,20 @@ def roi_pooling_cases():
                               kw.get("pooled_w", 0), 1.0 / 16], np.float64))
 
 
+def extra_layers_case():
+    b = wl.extra_layers_net(2)
+    weights = wl.init_params(b.params, seed=5, bn_identity=False)
+    x = wl.extra_layers_input(2, seed=1)
+    res = run(b, weights, x, list(wl.EXTRA_LAYER_OUTPUTS), marks=list(wl.EXTRA_LAYER_OUTPUTS))
+    arrays = {"in_data": x["data"]}
+    arrays.update({"w_" + k: v for k, v in weights.items()})
+    arrays.update({"out_" + k: v for k, v in res.items()})
+    save("extra_layers", **arrays)
+
+
 if __name__ == "__main__":
     dense_layers()
+    extra_layers_case()
     roi_pooling_cases()
     proposal_cases()
     detection_cases()

@@ -1,9 +1,42 @@
 """Helpers shared by the parity tests: run one generated network through the
 engine and through the CPU oracle with identical weights and inputs."""
+import os
+
 import numpy as np
 
 
-def run_net(capi, library, builder, weights, inputs, outputs, marks=()):
+def is_reference(library):
+    return os.sep + "_ref" + os.sep in library.path
+
+
+def in_fresh_thread(fn):
+    """Runs fn() in a thread of its own and returns its result (or re-raises its exception).
+
+    Used for every network that runs on the reference build.  The reference hands out host memory
+    without clearing it, keeps a per-thread pool of recycled blocks, and in places depends on what a
+    block holds (a vector of ones is refilled only when its last element is not 1, src/layers/
+    bias_layer.cpp:62-65; other places count on fresh memory being zero).  Its results therefore
+    depend on which nets the thread ran before.  A new thread has an empty pool, and the oracle build
+    zeroes fresh blocks (oracle/zero_fresh_memory.h), so each oracle net starts from the state the
+    reference was written for."""
+    import threading
+    box = {}
+
+    def body():
+        try:
+            box["value"] = fn()
+        except BaseException as exc:   # noqa: BLE001  (re-raised in the caller's thread)
+            box["error"] = exc
+
+    t = threading.Thread(target=body)
+    t.start()
+    t.join()
+    if "error" in box:
+        raise box["error"]
+    return box["value"]
+
+
+def _run_net(capi, library, builder, weights, inputs, outputs, marks):
     net = capi.Net(library, builder.text(), None, from_buffer=True)
     for m in marks:
         net.mark_output(m)
@@ -11,7 +44,15 @@ def run_net(capi, library, builder, weights, inputs, outputs, marks=()):
     net.forward(**inputs)
     result = {name: net.blob(name).data.copy() for name in outputs}
     net.close()
+    if is_reference(library):
+        library.memory_pool_clear()   # the thread's large blocks go back to the heap before it ends
     return result
+
+
+def run_net(capi, library, builder, weights, inputs, outputs, marks=()):
+    if is_reference(library):
+        return in_fresh_thread(lambda: _run_net(capi, library, builder, weights, inputs, outputs, marks))
+    return _run_net(capi, library, builder, weights, inputs, outputs, marks)
 
 
 def error_stats(got, want):

@@ -89,11 +89,18 @@ def test_folded_files_compute_the_same_function_on_the_reference(capi, reflib, t
     subprocess.run([tool, "--net", str(proto), "--weight", str(model)], check=True, capture_output=True, timeout=120)
     x = np.random.default_rng(8).standard_normal((2, 6, 12, 10)).astype(np.float32)
     outs = {}
-    for tag, p, m in (("orig", proto, model), ("fold", tmp_path / "net_nobn.prototxt", tmp_path / "net_nobn.caffemodel")):
+    from parity import in_fresh_thread
+
+    def run_files(p, m):
         net = capi.Net(reflib, str(p), str(m))
         net.forward(data=x)
-        outs[tag] = {name: net.blob(name).data.copy() for name in ("gap", "c3")}
+        res = {name: net.blob(name).data.copy() for name in ("gap", "c3")}
         net.close()
+        reflib.memory_pool_clear()
+        return res
+
+    for tag, p, m in (("orig", proto, model), ("fold", tmp_path / "net_nobn.prototxt", tmp_path / "net_nobn.caffemodel")):
+        outs[tag] = in_fresh_thread(lambda: run_files(p, m))
     for name in ("gap", "c3"):
         scale = max(1.0, float(np.abs(outs["orig"][name]).max()))
         assert np.abs(outs["orig"][name] - outs["fold"][name]).max() <= 2e-5 * scale

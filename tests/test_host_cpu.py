@@ -209,6 +209,12 @@ def test_reference_example_prototxts_parse(capi, engine):
         net.close()
         built += 1
     assert built >= 10
+    # the SSH detector (Deconvolution + Crop + Proposal) and the WGAN generator (Deconvolution +
+    # BatchNorm on batch statistics + TanH) are among the ones that build
+    for name in ("ssh/test_ssh.prototxt", "wgan/g.prototxt", "r-fcn/test_agnostic.prototxt"):
+        net = capi.Net(engine, os.path.join(REFERENCE_MODELS, name), "")
+        assert len(net.blobs()) > 3
+        net.close()
     net = capi.Net(engine, os.path.join(REFERENCE_MODELS, "deeplandmark", "1_F.prototxt"),
                    os.path.join(REFERENCE_MODELS, "deeplandmark", "1_F.caffemodel"))
     assert float(np.abs(dict(net.params())["conv1_0"].data).sum()) > 0

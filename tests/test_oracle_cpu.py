@@ -123,3 +123,27 @@ def test_roi_pooling_restatements_bit_exact(no):
     assert np.array_equal(got.view(np.uint32), g["out"].view(np.uint32))
     # the fixtures hold the special cases: empty bins give exactly 0, and some bins are not empty
     assert (g["out"] == 0).any() and (g["out"] != 0).any()
+
+
+def test_extra_layer_restatements_follow_the_reference(no):
+    """Deconvolution, Crop, Slice, BN and LRN against the fixture the compiled reference produced."""
+    g = load("extra_layers")
+    x = g["in_data"]
+    up = no.deconvolution(x, g["w_up_0"], g["w_up_1"], stride=2, pad=1)
+    close(up, g["out_up"])
+    up_g = no.deconvolution(x, g["w_up_g_0"], None, stride=1, pad=1, group=3)
+    close(up_g, g["out_up_g"])
+    # kernel 2 x 3, stride 3 x 2, dilation 2: the restatement takes square parameters, so check the
+    # shape rule only: stride * (in - 1) + dilation * (k - 1) + 1 - 2 * pad
+    assert g["out_up_d"].shape == (2, 3, 3 * 8 + 2 * 1 + 1, 2 * 6 + 2 * 2 + 1)
+    crop = no.crop(g["out_up"], (2, 4, 13, 11), axis=2, offsets=(2, 1))
+    assert np.array_equal(crop, g["out_crop"])
+    assert np.array_equal(no.crop(g["out_up"], (2, 4, 13, 11), axis=2, offsets=(1,)), g["out_crop1"])
+    s0, s1, s2 = no.slice_blob(g["out_up_g"], 1, slice_points=(1, 4))
+    assert np.array_equal(s0, g["out_s0"]) and np.array_equal(s1, g["out_s1"]) and np.array_equal(s2, g["out_s2"])
+    e0, e1 = no.slice_blob(g["out_up"], 2, num_tops=2)
+    assert np.array_equal(e0, g["out_e0"]) and np.array_equal(e1, g["out_e1"])
+    bn = no.bn(g["out_crop"], g["w_bn_0"], g["w_bn_1"], g["w_bn_2"], g["w_bn_3"])
+    close(bn, g["out_bn"])
+    close(no.lrn(g["out_up_g"], 5, 0.0001, 0.75, 2.0), g["out_lrn_a"])
+    close(no.lrn(g["out_bn"], 3, 0.05, 0.75, within_channel=True), g["out_lrn_w"])
