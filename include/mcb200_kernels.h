@@ -111,8 +111,8 @@ int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld,
  * with 4 floats per pixel (mcb200_conv_rows_pad_input), and one k-iteration then
  * covers a whole filter row: 8 neighbouring pixels x 4 channels = one 128-byte
  * row per output pixel, fetched by a tiled tensor map whose pixel pitch is the
- * convolution stride.  An M tile is one output row of one image.  Requires
- * kw <= 8, dil_w == 1 and an output width of at most 128.
+ * convolution stride.  An M tile is one output row of one image, or a segment of
+ * 128 pixels of it when the row is wider.  Requires kw <= 8 and dil_w == 1.
  *   padded copy: [n, hp, wp, 4] floats with (hp, wp) from mcb200_conv_rows_padded_dims
  *   weights:     [cout][kh][8 * 4] via mcb200_conv_rows_pack_weights
  * Launch with mcb200_conv_tc_launch.                                            */

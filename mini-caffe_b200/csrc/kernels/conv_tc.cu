@@ -78,7 +78,8 @@ struct ConvTcArgs {
   mcb200_epilogue ep;
   int* status;
   int tma_epilogue;  // output (and residual) meet the 16-byte rules of TMA tiles
-  int tile_rows;     // valid rows of an M tile: 128, or the output width in row mode
+  int tile_rows;     // rows of an M tile: 128, or in row mode min(output width, 128)
+  int row_segments;  // row mode: M tiles per output row of an image (ceil(output width / tile_rows))
   int a_bytes;       // bytes one activation tile load delivers
   int stages;        // depth of the operand ring (2 .. kMaxStages)
   int slots;         // staging slots per epilogue warp: 1 or 2; 2 or 3 when a residual is added
@@ -172,8 +173,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles = (args.cout + BN - 1) / BN;
-  // Row mode: an M tile is one output row of one image (tile_rows <= 128 pixels).
-  const int m_tiles = kMode == kModeRows ? args.m / args.tile_rows : (args.m + kBlockM - 1) / kBlockM;
+  // Row mode: an M tile is (a segment of at most 128 pixels of) one output row of one image.
+  const int m_tiles = kMode == kModeRows ? (args.m / args.wo) * args.row_segments : (args.m + kBlockM - 1) / kBlockM;
+  // Row mode helpers: image row (n * ho + p) and first pixel of the segment of M tile mt.
+  auto row_of = [&](int mt) { return mt / args.row_segments; };
+  auto seg_start = [&](int mt) { return (mt % args.row_segments) * args.tile_rows; };
   // A work unit is an M tile (or a pair of neighbouring M tiles) x an N tile;
   // `worker` is the CTA (or pair) index among `workers`.
   const uint32_t rank = kPair ? cluster_cta_rank() : 0u;
@@ -262,8 +266,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             !kPair ? a_bytes : (rank != 0u ? 0u : (mt + 1 < m_tiles ? 2u * a_bytes : a_bytes));
         int base_w = 0, base_h = 0, base_n = 0;
         if (kMode == kModeRows) {
-          base_n = mt / args.ho;
-          base_h = (mt - base_n * args.ho) * args.stride_h;   // row in the spatially padded copy
+          const int row = row_of(mt);
+          base_n = row / args.ho;
+          base_h = (row - base_n * args.ho) * args.stride_h;   // row in the spatially padded copy
+          base_w = seg_start(mt);                              // first output pixel of the segment
         }
         if (kMode == kModeIm2col) {
           const int q = m0 % args.wo;
@@ -292,7 +298,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (j >= nsub) break;
             if (kMode == kModeRows) {
               // A sub-tile is one filter row: tile_rows pixels x (8 pixels x 4 channels) of a padded input row.
-              tma_load_4d(&map_a, bar, a_dst, 0, 0, row_h, base_n);
+              tma_load_4d(&map_a, bar, a_dst, 0, base_w, row_h, base_n);   // pixels past the row read as zero
               row_h += args.dil_h;
             } else if (kMode == kModeIm2col) {
               if (kPair) {
@@ -485,7 +491,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (++ld_slot == slots) ld_slot = 0;
       mbar_expect_tx(&res_bar[ew][slot], 4096);
       if (kMode == kModeRows) {
-        tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, quad * 32, mt);
+        tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, seg_start(mt) + quad * 32, row_of(mt));
       } else {
         tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, mt * kBlockM + quad * 32, 0);
       }
@@ -503,8 +509,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int mt = unit_to_mt(unit);
       const int n0 = (tile - unit * n_tiles) * BN;
       // First output row (pixel) of this warp's 32-row slice, and how many of the 32 exist.
-      const int row0 = (kMode == kModeRows ? mt * args.tile_rows : mt * kBlockM) + quad * 32;
-      const int rows_here = kMode == kModeRows ? args.tile_rows - quad * 32 : args.m - row0;
+      const int row0 = (kMode == kModeRows ? row_of(mt) * args.wo + seg_start(mt) : mt * kBlockM) + quad * 32;
+      const int rows_here = kMode == kModeRows ? min(args.tile_rows, args.wo - seg_start(mt)) - quad * 32 : args.m - row0;
       // Per-column constants of this tile go to shared memory once, so that the
       // inner loops are a broadcast 16-byte load and fused multiply-adds.  Two
       // copies (tile parity): a warp may still be reading the previous tile's.
@@ -632,7 +638,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) {
             if (kMode == kModeRows) {
-              tma_store_3d(&map_out, slot_ptr(slot), col0, quad * 32, mt);
+              tma_store_3d(&map_out, slot_ptr(slot), col0, seg_start(mt) + quad * 32, row_of(mt));   // clipped at the row's end
             } else {
               tma_store_3d(&map_out, slot_ptr(slot), col0, row0, 0);
             }
@@ -838,8 +844,9 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
       configured[dev] = true;
     }
   }
-  const long long m_tiles = kMode == kModeRows ? static_cast<long long>(plan->shape.n) * plan->shape.ho
-                                               : (plan->m + kBlockM - 1) / kBlockM;
+  const long long m_tiles = kMode == kModeRows
+                                ? static_cast<long long>(plan->shape.n) * plan->shape.ho * args.row_segments
+                                : (plan->m + kBlockM - 1) / kBlockM;
   const long long m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
   const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * m_units;
   if (tiles > 0x3fffffffLL) return cudaErrorInvalidConfiguration;
@@ -1051,7 +1058,8 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
     }
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  a.tile_rows = plan->im2col == kModeRows ? plan->shape.wo : kBlockM;
+  a.tile_rows = plan->im2col == kModeRows ? (plan->shape.wo < kBlockM ? plan->shape.wo : kBlockM) : kBlockM;
+  a.row_segments = plan->im2col == kModeRows ? (plan->shape.wo + a.tile_rows - 1) / a.tile_rows : 1;
   a.a_bytes = a.tile_rows * kBlockK * 4;
   cudaError_t e = cudaErrorInvalidValue;
   const int mode = plan->im2col;
@@ -1131,7 +1139,7 @@ extern "C" int mcb200_conv_rows_supported(const mcb200_conv_shape* s) {
   if (!s || s->group != 1 || s->c < 1 || s->c > 4 || s->kw > 8 || s->dil_w != 1) return 0;
   mcb200_conv_shape t = *s;
   if (mcb200_conv_out_shape(&t) != 0) return 0;
-  return t.wo >= 1 && t.wo <= kBlockM;
+  return t.wo >= 1;
 }
 
 extern "C" int mcb200_conv_rows_padded_dims(const mcb200_conv_shape* s, int* hp, int* wp) {
@@ -1201,7 +1209,8 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
                               static_cast<cuuint64_t>(s->n)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s->stride_w) * 16, static_cast<cuuint64_t>(wp) * 16,
                                  static_cast<cuuint64_t>(wp) * 16 * hp};
-  const cuuint32_t box[4] = {kBlockK, static_cast<cuuint32_t>(plan->shape.wo), 1, 1};
+  // One M tile = up to 128 output pixels of a row; wider rows are cut into segments.
+  const cuuint32_t box[4] = {kBlockK, static_cast<cuuint32_t>(plan->shape.wo < kBlockM ? plan->shape.wo : kBlockM), 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(padded_in), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

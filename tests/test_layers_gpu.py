@@ -39,6 +39,39 @@ def test_depthwise_and_grouped_convolution(capi, gpu_engine, reflib):
         assert_close(got[name], want[name], name)
 
 
+@pytest.mark.parametrize("channels,size,k,stride,pad,cout", [
+    (3, (23, 300), 3, 1, 1, 64),     # output rows of 300 pixels: three segments, the last one partial
+    (3, (9, 257), 7, 2, 3, 24),      # 129 pixels per row: a second segment of one pixel
+    (1, (6, 128), 5, 1, 2, 16),      # exactly one full segment, single channel
+    (4, (5, 140), 3, 1, 0, 72),      # no padding, two N tiles
+])
+def test_first_layer_convolution_with_wide_rows(capi, gpu_engine, reflib, channels, size, k, stride, pad, cout):
+    """Layers with at most four input channels run the tensor-core kernel's row mode; output rows wider
+    than an M tile (128 pixels) are cut into segments."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("wide")
+    b.input([("data", (2, channels) + size)])
+    b.conv("c", "data", "c", channels, cout, k, stride=stride, pad=pad)
+    b.relu("c_relu", "c")
+    weights = wl.init_params(b.params, seed=21)
+    x = {"data": np.random.default_rng(22).standard_normal((2, channels) + size).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["c"])
+    assert got["c"].shape == want["c"].shape
+    assert_close(got["c"], want["c"], "wide first layer")
+
+
+@pytest.mark.parametrize("stride,size", [(1, (14, 14)), (2, (15, 9)), (1, (5, 3)), (2, (2, 2))])
+def test_depthwise_3x3_sizes(capi, gpu_engine, reflib, stride, size):
+    wl = pkg("workloads")
+    b = wl.NetBuilder("dw3")
+    b.input([("data", (2, 24) + size)])
+    b.conv("dw", "data", "dw", 24, 24, 3, stride=stride, pad=1, group=24)
+    weights = wl.init_params(b.params, seed=5)
+    x = {"data": np.random.default_rng(6).standard_normal((2, 24) + size).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["dw"])
+    assert np.abs(got["dw"] - want["dw"]).max() <= 2e-5
+
+
 @pytest.mark.parametrize("method,k,stride,pad,size", [
     ("MAX", 3, 2, 0, (112, 112)), ("MAX", 2, 2, 0, (75, 75)), ("MAX", 3, 1, 1, (19, 19)),
     ("AVE", 3, 2, 1, (14, 15)), ("AVE", 2, 2, 1, (9, 9)), ("MAX", 3, 2, 1, (13, 11)),
