@@ -34,19 +34,39 @@ __device__ __forceinline__ unsigned long long make_key(float score, uint32_t ind
 constexpr unsigned long long kPadKey = 0xFFFFFFFFFFFFFFFFull;
 
 // Finds the k-th smallest (1-based) of n distinct keys with an MSB-first radix
-// walk, 8 bits per pass.  Whole block; `hist` is 256 ints of shared memory,
-// `bcast` two unsigned long longs.  `fetch(i)` returns key i.
+// walk, 8 bits per pass, and returns a threshold T such that exactly k keys
+// are <= T.  Whole block; `hist` is 256 ints of shared memory, `bcast` two
+// unsigned long longs.  `fetch(i)` returns key i.
+//
+// Scores of one layer share their sign and most exponent bits, so in the first
+// passes nearly every key falls into the same bin: lanes of a warp that hit
+// the same bin are combined (__match_any_sync) into one shared-memory add.
+// The walk stops as soon as the chosen bin holds exactly the keys still
+// wanted (with distinct scores: after the four score bytes), because all of
+// them are then selected whatever their lower bits are.
 template <typename Fetch>
 __device__ unsigned long long block_kth_smallest(Fetch fetch, int n, int k, int* hist, unsigned long long* bcast) {
   unsigned long long prefix = 0, mask = 0;
   int remaining = k;
+  const int lane = threadIdx.x & 31;
   for (int pass = 7; pass >= 0; --pass) {
     for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0;
     __syncthreads();
     const int shift = pass * 8;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const unsigned long long key = fetch(i);
-      if ((key & mask) == prefix) atomicAdd(&hist[static_cast<int>((key >> shift) & 0xFFull)], 1);
+    for (int base = 0; base < n; base += blockDim.x) {   // the same trip count for every thread
+      const int i = base + threadIdx.x;
+      unsigned long long key = 0;
+      bool live = i < n;
+      if (live) {
+        key = fetch(i);
+        live = (key & mask) == prefix;
+      }
+      const unsigned live_lanes = __ballot_sync(0xffffffffu, live);
+      if (live) {
+        const int bin = static_cast<int>((key >> shift) & 0xFFull);
+        const unsigned peers = __match_any_sync(live_lanes, bin);
+        if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -55,14 +75,21 @@ __device__ unsigned long long block_kth_smallest(Fetch fetch, int n, int k, int*
         if (cum + hist[bin] >= remaining) break;
         cum += hist[bin];
       }
-      bcast[0] = prefix | (static_cast<unsigned long long>(bin) << shift);
-      bcast[1] = static_cast<unsigned long long>(remaining - cum);
+      const unsigned long long next = prefix | (static_cast<unsigned long long>(bin) << shift);
+      if (cum + hist[bin] == remaining) {   // the whole bin is wanted: done
+        bcast[0] = next | ((1ull << shift) - 1ull);
+        bcast[1] = 0ull;
+      } else {
+        bcast[0] = next;
+        bcast[1] = static_cast<unsigned long long>(remaining - cum);
+      }
     }
     __syncthreads();
     prefix = bcast[0];
     remaining = static_cast<int>(bcast[1]);
     mask |= 0xFFull << shift;
     __syncthreads();
+    if (remaining == 0) break;
   }
   return prefix;
 }

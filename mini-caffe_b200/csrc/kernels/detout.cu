@@ -2,10 +2,10 @@
 //   A. per (image, class) block: collect priors whose class score passes the
 //      confidence threshold, take the top_k best (radix select + bitonic sort in
 //      shared memory, ties by prior index like std::stable_sort), decode their
-//      boxes, greedy NMS by one warp with ballots
+//      boxes, greedy NMS (overlap bit matrix by the whole block, walk by one warp)
 //   B. per image block: if more than keep_top_k detections survive, keep the
 //      keep_top_k best over all classes; lay the rows out label-ascending
-//   C. one block: prefix sum of the per-image counts, compact the rows
+//   C. per image block: prefix sum of the per-image counts, compact the rows
 // The host reads back one int (the row count).
 //
 // Arithmetic follows mini-caffe's CPU code operation by operation so that the
@@ -223,9 +223,53 @@ detout_class_kernel(const float* __restrict__ loc, const float* __restrict__ con
   }
   __syncthreads();
 
-  // Greedy NMS by warp 0: candidate i is kept iff its overlap with every box
-  // kept so far is <= the (possibly adaptive) threshold.
-  if (threadIdx.x < 32) {
+  // Greedy NMS: candidate i is kept iff its overlap with every box kept so far
+  // is <= the threshold.  With a fixed threshold (eta == 1, the usual case) the
+  // overlaps do not depend on the walk: the whole block evaluates the lower
+  // triangle into a bit matrix (row i, bit j < i: box j would suppress box i),
+  // which takes the place of the candidate keys in shared memory, and one warp
+  // then walks the rows holding the kept set as one 32-bit word per lane.
+  const int words = (count + 31) >> 5;
+  const bool fixed_threshold = !(eta < 1.f);
+  const bool use_matrix = fixed_threshold && words <= 32 &&
+                          static_cast<size_t>(count) * words * sizeof(uint32_t) <= static_cast<size_t>(p.num_priors) * 8;
+  if (use_matrix) {
+    uint32_t* suppress = reinterpret_cast<uint32_t*>(cand);
+    const float threshold_fixed = p.nms_threshold;
+    // Consecutive threads take consecutive rows of one word column: the boxes
+    // compared against are a broadcast, the row's own box a stride-5 access.
+    for (int t = threadIdx.x; t < count * words; t += blockDim.x) {
+      const int w = t / count;
+      const int i = t - w * count;
+      const int j0 = w << 5;
+      uint32_t bits = 0;
+      if (j0 < i) {
+        const Box cur = boxes[i];
+        const int jn = min(32, i - j0);
+        for (int b = 0; b < jn; ++b) {
+          if (jaccard(cur, boxes[j0 + b]) > threshold_fixed) bits |= 1u << b;
+        }
+      }
+      suppress[i * words + w] = bits;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      uint32_t kept_word = 0;   // lane w: boxes 32 w .. 32 w + 31 kept so far
+      int nk = 0;
+      for (int i = 0; i < count; ++i) {
+        const uint32_t hit = lane < words ? (suppress[i * words + lane] & kept_word) : 0u;
+        if (!__any_sync(0xffffffffu, hit != 0u)) {
+          if (lane == (i >> 5)) kept_word |= 1u << (i & 31);
+          if (lane == 0) kept[nk] = i;
+          ++nk;
+        }
+      }
+      if (lane == 0) num_kept = nk;
+    }
+  } else if (threadIdx.x < 32) {
+    // Adaptive threshold (eta < 1) or a very long candidate list: one warp
+    // compares each candidate with the kept list, 32 kept boxes at a time.
     const int lane = threadIdx.x;
     float adaptive = p.nms_threshold;
     int nk = 0;
@@ -299,15 +343,15 @@ detout_image_kernel(mcb200_detout_params p, Workspace ws) {
     threshold = block_kth_smallest(fetch, total, p.keep_top_k, hist, bcast);
   }
   // Within a class the entries are in descending score order, so the kept ones
-  // are a prefix of it.
-  for (int c = threadIdx.x; c < classes; c += blockDim.x) {
-    int keep = 0;
-    const int n = counts[c];
-    for (int j = 0; j < n; ++j) {
-      if (make_key(entries[static_cast<size_t>(c) * limit + j].score, static_cast<uint32_t>(c * limit + j)) <= threshold)
-        ++keep;
-    }
-    selected[c] = keep;
+  // are a prefix of it; its length is the number of the class's keys <= threshold.
+  for (int c = threadIdx.x; c < classes; c += blockDim.x) selected[c] = 0;
+  __syncthreads();
+  for (int e = threadIdx.x; e < total; e += blockDim.x) {
+    int c = 0;
+    while (offsets[c + 1] <= e) ++c;
+    const int j = e - offsets[c];
+    if (make_key(entries[static_cast<size_t>(c) * limit + j].score, static_cast<uint32_t>(c * limit + j)) <= threshold)
+      atomicAdd(&selected[c], 1);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -338,23 +382,34 @@ detout_image_kernel(mcb200_detout_params p, Workspace ws) {
 
 // ---------------------------------------------------------------- C. compaction
 
+// One block per image: the block sums the counts of the images before its own
+// (and of all images, for the total) and copies its rows behind them.
 __global__ void __launch_bounds__(256)
 detout_compact_kernel(Workspace ws, int batch, float* __restrict__ out, int* __restrict__ total_out) {
-  __shared__ int base;
-  int run = 0;
-  for (int image = 0; image < batch; ++image) {
-    const int n = ws.image_count[image];
-    const float* rows = ws.rows + static_cast<size_t>(image) * ws.max_rows * 7;
-    for (int i = threadIdx.x; i < n * 7; i += blockDim.x) out[static_cast<size_t>(run) * 7 + i] = rows[i];
-    run += n;
-  }
-  if (threadIdx.x == 0) base = run;
+  __shared__ int sums[2];
+  const int image = blockIdx.x;
+  if (threadIdx.x == 0) sums[0] = sums[1] = 0;
   __syncthreads();
-  if (base == 0) {
-    // No detection at all: one row per image, image id followed by -1.
-    for (int i = threadIdx.x; i < batch * 7; i += blockDim.x) out[i] = (i % 7 == 0) ? static_cast<float>(i / 7) : -1.f;
+  int before = 0, all = 0;
+  for (int i = threadIdx.x; i < batch; i += blockDim.x) {
+    const int n = ws.image_count[i];
+    all += n;
+    if (i < image) before += n;
   }
-  if (threadIdx.x == 0) *total_out = base;
+  if (before) atomicAdd(&sums[0], before);
+  if (all) atomicAdd(&sums[1], all);
+  __syncthreads();
+  const int first = sums[0], total = sums[1];
+  const int n = ws.image_count[image];
+  const float* rows = ws.rows + static_cast<size_t>(image) * ws.max_rows * 7;
+  for (int i = threadIdx.x; i < n * 7; i += blockDim.x) out[static_cast<size_t>(first) * 7 + i] = rows[i];
+  if (image == 0) {
+    if (total == 0) {
+      // No detection at all: one row per image, image id followed by -1.
+      for (int i = threadIdx.x; i < batch * 7; i += blockDim.x) out[i] = (i % 7 == 0) ? static_cast<float>(i / 7) : -1.f;
+    }
+    if (threadIdx.x == 0) *total_out = total;
+  }
 }
 
 int validate(const mcb200_detout_params* p, int batch) {
@@ -415,7 +470,7 @@ extern "C" int mcb200_detout_forward(const mcb200_detout_params* p, int batch, c
   count_launch();
   detout_image_kernel<<<batch, 256, 0, st>>>(*p, ws);
   count_launch();
-  detout_compact_kernel<<<1, 256, 0, st>>>(ws, batch, out, total);
+  detout_compact_kernel<<<batch, 256, 0, st>>>(ws, batch, out, total);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
