@@ -242,7 +242,28 @@ def secondary_figures(capi, wl, engine, L, stream, torch):
     out["conv_relu_b32"] = {"kernel_ms": conv_ms.value / max(1, n), "tf32_tflops": flops / (conv_ms.value / max(1, n) * 1e-3) / 1e12,
                             "algorithmic_bytes": 4 * (2 * 32 * 64 * 56 * 56 + 64 * 64 * 9 + 64)}
     net.close()
+    out["resnet50_bf16_storage"] = bf16_storage_figure(capi, wl, engine, L, stream, torch)
     return out
+
+
+def bf16_storage_figure(capi, wl, engine, L, stream, torch, batch=BATCH_PER_GPU, reps=30):
+    """The engine's precision opt-in (MINICAFFE_PRECISION=bf16 while the net is constructed): the same
+    ResNet-50 pass with bfloat16 operands in the tensor-core convolutions and bfloat16 storage of the
+    blobs between them.  Input resident on the device; not the headline (which is fp32 storage / TF32)."""
+    previous = os.environ.get("MINICAFFE_PRECISION")
+    os.environ["MINICAFFE_PRECISION"] = "bf16"
+    try:
+        net = build_resnet(capi, wl, engine, batch)
+    finally:
+        if previous is None:
+            del os.environ["MINICAFFE_PRECISION"]
+        else:
+            os.environ["MINICAFFE_PRECISION"] = previous
+    net.forward(**wl.image_input(batch, seed=0))
+    ms = time_forwards(engine, L, net, stream, torch, reps)
+    net.close()
+    return {"images_per_s": batch / (ms * 1e-3), "ms_per_step": ms, "batch": batch, "dtype": "bf16 operands and storage, fp32 accumulation",
+            "how": "MINICAFFE_PRECISION=bf16 at net construction"}
 
 
 def run_tail_workload(args, capi, wl):

@@ -149,6 +149,14 @@ class CAFFE_API Blob {
   const real_t* gpu_data_nhwc() const;
   /*! \brief channels-last device buffer to be overwritten; other copies become stale */
   real_t* mutable_gpu_data_nhwc();
+  /*!
+   * \brief channels-last device copy rounded to bfloat16 (16-bit cells), made from
+   *        the current fp32 values on first use; written and read by the tensor-core
+   *        convolutions of a net built with bfloat16 storage.  Every other accessor
+   *        widens it back to fp32 first, so callers never see it.
+   */
+  const void* gpu_data_nhwc_bf16() const;
+  void* mutable_gpu_data_nhwc_bf16();
   /*! \brief true when the freshest device copy is the channels-last one */
   bool device_is_nhwc() const;
   /*! \brief counter that advances whenever host code may have written the data */

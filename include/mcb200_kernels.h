@@ -87,6 +87,8 @@ typedef struct mcb200_conv_plan {
   int im2col;               /* 0 matrix rows, 1 im2col tensor map, 2 row mode      */
   int out_ld, res_ld;
   int cta_pair;             /* 1: launched as two-CTA clusters (tcgen05 cta_group::2) */
+  int operand_bf16;         /* 1: built by mcb200_conv_tc_plan_bf16                 */
+  int out_bf16;             /* element type the cached output tile map was built for */
   const float* out_ptr;
   const float* res_ptr;
 } __attribute__((aligned(64))) mcb200_conv_plan;
@@ -104,6 +106,23 @@ int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float
  * the previous launch (their tile maps are cached in it).                     */
 int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld,
                           const mcb200_epilogue* ep, int* status, void* stream);
+
+/* bfloat16 storage (opt-in; the reference computes in fp32 throughout, so these
+ * have no counterpart there).  Activations, the packed weights and the residual
+ * are bfloat16, the tensor cores run tcgen05.mma kind::f16 with fp32
+ * accumulation, the fused tail is evaluated in fp32 and the result is stored
+ * as bfloat16 (out_is_bf16 != 0) or fp32.  c_stride % 8 == 0; `ep->residual`
+ * is read as a bfloat16 pointer with `residual_ld` in elements.  Weights:
+ * [cout][kh*kw][roundup(c,64)] bfloat16, round to nearest even.               */
+size_t mcb200_conv_packed_weight_count_bf16(const mcb200_conv_shape* s);
+int mcb200_conv_pack_weights_bf16(const mcb200_conv_shape* s, const float* w_oihw, uint16_t* packed, void* stream);
+int mcb200_conv_tc_plan_bf16(const mcb200_conv_shape* s, const uint16_t* in, const uint16_t* packed_w,
+                             mcb200_conv_plan* plan);
+int mcb200_conv_tc_launch_bf16(mcb200_conv_plan* plan, void* out, int out_is_bf16, int out_ld,
+                               const mcb200_epilogue* ep, int* status, void* stream);
+/* Element-wise copies between an fp32 and a bfloat16 tensor of `count` elements. */
+int mcb200_f32_to_bf16(const float* src, uint16_t* dst, size_t count, void* stream);
+int mcb200_bf16_to_f32(const uint16_t* src, float* dst, size_t count, void* stream);
 
 /* "Row mode" of the same kernel for layers with at most four input channels (the
  * first layer of an image network), where 32-channel blocks would be almost all

@@ -92,6 +92,18 @@ real_t* Blob::mutable_gpu_data_nhwc() {
   return static_cast<real_t*>(data_->mutable_gpu_data_nhwc(num(), channels(), height(), width()));
 }
 
+const void* Blob::gpu_data_nhwc_bf16() const {
+  CHECK(data_);
+  CHECK_LE(num_axes(), 4);
+  return data_->gpu_data_nhwc_bf16(num(), channels(), height(), width());
+}
+
+void* Blob::mutable_gpu_data_nhwc_bf16() {
+  CHECK(data_);
+  CHECK_LE(num_axes(), 4);
+  return data_->mutable_gpu_data_nhwc_bf16(num(), channels(), height(), width());
+}
+
 bool Blob::device_is_nhwc() const { return data_ && data_->nhwc_is_freshest(); }
 
 unsigned long long Blob::host_version() const { return data_ ? data_->host_version() : 0; }

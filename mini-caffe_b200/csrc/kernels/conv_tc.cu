@@ -49,6 +49,8 @@ using namespace sm100;
 
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 32;                            // fp32 elements = one 128-byte swizzle row
+constexpr int kBlockKHalf = 64;                        // bfloat16 elements of the same 128 bytes
+constexpr int kMmaPerBlock = 4;                        // 32-byte K steps of a swizzle row (K = 8 tf32 / 16 bf16)
 constexpr int kTileABytes = kBlockM * kBlockK * 4;     // 16 KiB
 // Warp roles.  A warp may only read the tensor-memory lanes [32 * (warp % 4), +32),
 // so the eight epilogue warps form four pairs that share a lane quadrant and split
@@ -83,6 +85,7 @@ struct ConvTcArgs {
   int a_bytes;       // bytes one activation tile load delivers
   int stages;        // depth of the operand ring (2 .. kMaxStages)
   int slots;         // staging slots per epilogue warp: 1 or 2; 2 or 3 when a residual is added
+  int out_half;      // bfloat16 operands only: the output is stored as bfloat16 too (else fp32)
 };
 
 constexpr int kMaxStages = 8;
@@ -142,13 +145,19 @@ struct RingPos {
 // turn over.  Barriers that both CTAs signal (stage full, accumulator drained)
 // live in rank 0; tcgen05.commit delivers the arrivals that both CTAs wait on to
 // each CTA's own copy of the barrier.
-template <int BN, int kMode, bool kPair>
+//
+// kHalf: activations, weights and the residual are bfloat16 (tcgen05.mma
+// kind::f16, fp32 accumulation); a k-iteration then covers 64 channels in the
+// same 128-byte rows.  The output is bfloat16 or fp32 (args.out_half).
+template <int BN, int kMode, bool kPair, bool kHalf>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
                const ConvTcArgs args) {
   static_assert(!(kPair && kMode == kModeRows), "row mode runs unpaired");
+  static_assert(!(kHalf && kMode == kModeRows), "row mode takes fp32 images");
   using Plan = SmemPlan<BN, kMode, kPair>;
+  constexpr int kElemsK = kHalf ? kBlockKHalf : kBlockK;   // channels per k-iteration
   const int stages = args.stages;
   const int slots = args.slots;
 
@@ -306,8 +315,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               } else {
                 tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
               }
-              c0 += kBlockK;
-              if (c0 >= args.c_blocks * kBlockK) {
+              c0 += kElemsK;
+              if (c0 >= args.c_blocks * kElemsK) {
                 c0 = 0;
                 off_w = static_cast<uint16_t>(off_w + args.dil_w);
                 if (++sx == args.kw) {
@@ -322,7 +331,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               } else {
                 tma_load_2d(&map_a, bar, a_dst, c0, m0);
               }
-              c0 += kBlockK;
+              c0 += kElemsK;
             }
             a_dst += kTileABytes;
           }
@@ -361,7 +370,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             } else {
               tma_load_2d(&map_b, bar, b_dst, k0, n0);
             }
-            k0 += kBlockK;
+            k0 += kElemsK;
             b_dst += Plan::kTileBBytes;
           }
           ++issued;
@@ -373,7 +382,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issuer
     if ((!kPair || rank == 0u) && elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_tf32(kPair ? 2 * kBlockM : kBlockM, BN);
+      constexpr uint32_t idesc = kHalf ? umma_idesc_bf16(kPair ? 2 * kBlockM : kBlockM, BN)
+                                       : umma_idesc_tf32(kPair ? 2 * kBlockM : kBlockM, BN);
       RingPos pos;
       int local = 0;   // tiles done by this CTA
       bool alive = true;
@@ -400,10 +410,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < Plan::kSub; ++j) {
             if (j >= nsub) break;
 #pragma unroll
-            for (int kk = 0; kk < kBlockK / 8; ++kk) {
-              // Each K=8 step is 32 bytes further along the swizzled row: +2 in the
-              // descriptor's 16-byte address units.
-              if (kPair) {
+            for (int kk = 0; kk < kMmaPerBlock; ++kk) {
+              // Each K step (8 tf32 or 16 bf16) is 32 bytes further along the swizzled
+              // row: +2 in the descriptor's 16-byte address units.
+              if (kHalf) {
+                if (kPair) {
+                  umma_bf16_pair(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+                } else {
+                  umma_bf16(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+                }
+              } else if (kPair) {
                 umma_tf32_pair(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
               } else {
                 umma_tf32(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
@@ -489,7 +505,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!cursor_next(ld, mt, col)) return;
       const int slot = ld_slot;
       if (++ld_slot == slots) ld_slot = 0;
-      mbar_expect_tx(&res_bar[ew][slot], 4096);
+      mbar_expect_tx(&res_bar[ew][slot], kHalf ? 2048 : 4096);   // 32 x 32 bfloat16 or fp32
       if (kMode == kModeRows) {
         tma_load_3d(&map_res, &res_bar[ew][slot], slot_ptr(slot), col, seg_start(mt) + quad * 32, row_of(mt));
       } else {
@@ -623,17 +639,56 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // shared-memory round trip after the other (long ones while the
           // tensor core and the TMA keep shared memory busy).
           float4 v[8];
-          if (has_res) {
+          if (kHalf) {
+            // bfloat16 rows are 64 bytes: four 16-byte pieces, piece p stored at
+            // position p ^ ((row >> 1) & 3) (the 64-byte swizzle).
+            uint8_t* hrow = reinterpret_cast<uint8_t*>(slot_ptr(slot)) + lane * 64;
+            const int hswz = (lane >> 1) & 3;
+            if (has_res) {
+              uint4 w[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              v[j] = finish4(j, *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2)), true);
+              for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const uint4*>(hrow + ((q ^ hswz) << 4));
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                v[2 * q] = finish4(2 * q, make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)),
+                                   true);
+                v[2 * q + 1] = finish4(2 * q + 1,
+                                       make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
+                                       true);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+            }
+            if (args.out_half) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 w;
+                w.x = pack_bf16x2(v[2 * q].x, v[2 * q].y);
+                w.y = pack_bf16x2(v[2 * q].z, v[2 * q].w);
+                w.z = pack_bf16x2(v[2 * q + 1].x, v[2 * q + 1].y);
+                w.w = pack_bf16x2(v[2 * q + 1].z, v[2 * q + 1].w);
+                *reinterpret_cast<uint4*>(hrow + ((q ^ hswz) << 4)) = w;
+              }
+            } else {
+              // fp32 rows (128 bytes) overlap other lanes' bfloat16 residual rows.
+              if (has_res) __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
             }
           } else {
+            if (has_res) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+              for (int j = 0; j < 8; ++j) {
+                v[j] = finish4(j, *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2)), true);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
           }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -648,24 +703,38 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // ---- plain stores (rows not 16-byte aligned) ----
           const int row = row0 + lane;
           if (lane < rows_here) {
-            float* out_row = args.out + static_cast<size_t>(row) * args.out_ld;
-            const float* res_row = has_res ? ep.residual + static_cast<size_t>(row) * ep.residual_ld : nullptr;
+            const size_t out_off = static_cast<size_t>(row) * args.out_ld;
+            const size_t res_off = static_cast<size_t>(row) * ep.residual_ld;
+            auto residual_at = [&](int c) {
+              if (kHalf) {
+                return __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(ep.residual)[res_off + c])
+                                       << 16);
+              }
+              return ep.residual[res_off + c];
+            };
+            auto store_at = [&](int c, float value) {
+              if (kHalf && args.out_half) {
+                reinterpret_cast<uint16_t*>(args.out)[out_off + c] = static_cast<uint16_t>(pack_bf16x2(value, 0.f));
+              } else {
+                args.out[out_off + c] = value;
+              }
+            };
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int c = col0 + j * 4;
               if (c >= args.cout) break;
               float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (res_row) {
-                r.x = res_row[c];
-                if (c + 1 < args.cout) r.y = res_row[c + 1];
-                if (c + 2 < args.cout) r.z = res_row[c + 2];
-                if (c + 3 < args.cout) r.w = res_row[c + 3];
+              if (has_res) {
+                r.x = residual_at(c);
+                if (c + 1 < args.cout) r.y = residual_at(c + 1);
+                if (c + 2 < args.cout) r.z = residual_at(c + 2);
+                if (c + 3 < args.cout) r.w = residual_at(c + 3);
               }
-              const float4 v = finish4(j, r, res_row != nullptr);
-              out_row[c] = v.x;
-              if (c + 1 < args.cout) out_row[c + 1] = v.y;
-              if (c + 2 < args.cout) out_row[c + 2] = v.z;
-              if (c + 3 < args.cout) out_row[c + 3] = v.w;
+              const float4 v = finish4(j, r, has_res);
+              store_at(c, v.x);
+              if (c + 1 < args.cout) store_at(c + 1, v.y);
+              if (c + 2 < args.cout) store_at(c + 2, v.z);
+              if (c + 3 < args.cout) store_at(c + 3, v.w);
             }
           }
         }
@@ -716,6 +785,45 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, float* __restri
     if (cc < c) v = round_to_tf32(w[(static_cast<size_t>(co) * c + cc) * taps + tap]);
     packed[i] = v;
   }
+}
+
+// Same image in bfloat16 (round to nearest even), taps padded to a multiple of 64 channels.
+__global__ void pack_weights_bf16_kernel(const float* __restrict__ w, uint16_t* __restrict__ packed, int cout, int c,
+                                         int taps, int c_pad) {
+  const size_t total = static_cast<size_t>(cout) * taps * c_pad;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % c_pad);
+    const int tap = static_cast<int>((i / c_pad) % taps);
+    const int co = static_cast<int>(i / (static_cast<size_t>(c_pad) * taps));
+    float v = 0.f;
+    if (cc < c) v = w[(static_cast<size_t>(co) * c + cc) * taps + tap];
+    packed[i] = static_cast<uint16_t>(pack_bf16x2(v, 0.f));
+  }
+}
+
+// fp32 <-> bfloat16 copies of an activation tensor (the layout does not change).
+__global__ void f32_to_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, size_t quads,
+                                   const float* __restrict__ src1, uint16_t* __restrict__ dst1, size_t count) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t first = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  for (size_t i = first; i < quads; i += stride) {
+    const float4 v = src[i];
+    dst[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+  for (size_t i = quads * 4 + first; i < count; i += stride) dst1[i] = static_cast<uint16_t>(pack_bf16x2(src1[i], 0.f));
+}
+
+__global__ void bf16_to_f32_kernel(const uint2* __restrict__ src, float4* __restrict__ dst, size_t quads,
+                                   const uint16_t* __restrict__ src1, float* __restrict__ dst1, size_t count) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t first = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  for (size_t i = first; i < quads; i += stride) {
+    const uint2 w = src[i];
+    dst[i] = make_float4(bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y));
+  }
+  for (size_t i = quads * 4 + first; i < count; i += stride)
+    dst1[i] = __uint_as_float(static_cast<uint32_t>(src1[i]) << 16);
 }
 
 // ------------------------------------------------------------------ tensor maps
@@ -796,28 +904,31 @@ int pick_cta_pair(int block_n, long long m, int k_iters) {
   return (block_n >= 128 && m > kBlockM && k_iters > 16) ? 1 : 0;
 }
 
-// Tile map for the staged epilogue over a row-major fp32 matrix with row pitch
-// `ld`, 32 x 32 boxes, 128-byte swizzle.  The rows are split as (group, row in
+// Tile map for the staged epilogue over a row-major matrix with row pitch `ld`
+// (elements), 32 x 32 boxes: fp32 with the 128-byte swizzle, or bfloat16 (64-byte
+// box rows) with the 64-byte swizzle.  The rows are split as (group, row in
 // group): ordinary tiles use one group of all rows; row mode uses one group per
 // output row of an image so that a tile never spills into the next row.
-CUresult encode_tile_map(CUtensorMap* map, const float* base, int cols, int ld, long long rows_per_group,
+CUresult encode_tile_map(CUtensorMap* map, const void* base, bool half, int cols, int ld, long long rows_per_group,
                          long long groups) {
   const DriverApi& api = driver_api();
+  const cuuint64_t es = half ? 2 : 4;
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows_per_group),
                               static_cast<cuuint64_t>(groups)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4,
-                                 static_cast<cuuint64_t>(ld) * 4 * static_cast<cuuint64_t>(rows_per_group)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es,
+                                 static_cast<cuuint64_t>(ld) * es * static_cast<cuuint64_t>(rows_per_group)};
   const cuuint32_t box[3] = {32, 32, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  return api.tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  return api.tiled(map, half ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   half ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <int BN, int kMode, bool kPair>
+template <int BN, int kMode, bool kPair, bool kHalf>
 cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaStream_t stream) {
   using Plan = SmemPlan<BN, kMode, kPair>;
-  auto kernel = conv_tc_kernel<BN, kMode, kPair>;
+  auto kernel = conv_tc_kernel<BN, kMode, kPair, kHalf>;
   // The large-shared-memory opt-in is per device: do it once for each device
   // this process launches on.  What the ring may use is the CTA limit minus the
   // kernel's static shared memory (barriers, per-column tables).
@@ -932,10 +1043,61 @@ extern "C" int mcb200_conv_pack_weights(const mcb200_conv_shape* s, const float*
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float* packed_w,
-                                   mcb200_conv_plan* plan) {
+extern "C" size_t mcb200_conv_packed_weight_count_bf16(const mcb200_conv_shape* s) {
+  const size_t c_pad = static_cast<size_t>((s->c + kBlockKHalf - 1) / kBlockKHalf) * kBlockKHalf;
+  return static_cast<size_t>(s->cout) * s->kh * s->kw * c_pad;
+}
+
+extern "C" int mcb200_conv_pack_weights_bf16(const mcb200_conv_shape* s, const float* w_oihw, uint16_t* packed,
+                                             void* stream) {
+  if (!s || !w_oihw || !packed || s->group != 1) return -1;
+  const int c_pad = (s->c + kBlockKHalf - 1) / kBlockKHalf * kBlockKHalf;
+  const size_t total = mcb200_conv_packed_weight_count_bf16(s);
+  const int threads = 256;
+  const int blocks = static_cast<int>((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
+                                                                                  : 148 * 8);
+  pack_weights_bf16_kernel<<<blocks > 0 ? blocks : 1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      w_oihw, packed, s->cout, s->c, s->kh * s->kw, c_pad);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_f32_to_bf16(const float* src, uint16_t* dst, size_t count, void* stream) {
+  if (!src || !dst) return -1;
+  if (count == 0) return 0;
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0);
+  const size_t quads = vec ? count / 4 : 0;
+  const size_t items = quads + (count - quads * 4);
+  const int blocks = static_cast<int>((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
+  f32_to_bf16_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(src), reinterpret_cast<uint2*>(dst), quads, src, dst, count);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_bf16_to_f32(const uint16_t* src, float* dst, size_t count, void* stream) {
+  if (!src || !dst) return -1;
+  if (count == 0) return 0;
+  const bool vec = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((reinterpret_cast<uintptr_t>(src) & 7) == 0);
+  const size_t quads = vec ? count / 4 : 0;
+  const size_t items = quads + (count - quads * 4);
+  const int blocks = static_cast<int>((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
+  bf16_to_f32_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint2*>(src), reinterpret_cast<float4*>(dst), quads, src, dst, count);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+namespace {
+
+// Shared by the fp32 (TF32) and the bfloat16 plan: `in` and `packed_w` hold
+// elements of `es` bytes, a k-iteration covers `kelems` channels (128 bytes).
+int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, mcb200_conv_plan* plan, bool half) {
+  const cuuint64_t es = half ? 2 : 4;
+  const int kelems = half ? kBlockKHalf : kBlockK;
+  const CUtensorMapDataType dtype = half ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   if (!s || !in || !packed_w || !plan) return -1;
-  if (s->group != 1 || (s->c_stride & 3) != 0 || s->c_stride < s->c) return -2;
+  if (s->group != 1 || (s->c_stride & (half ? 7 : 3)) != 0 || s->c_stride < s->c) return -2;
   if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(packed_w) & 15)) return -3;
   if (s->pad_h > 127 || s->pad_w > 127 || (s->kh - 1) * s->dil_h > 255 || (s->kw - 1) * s->dil_w > 255) return -4;
   const DriverApi& api = driver_api();
@@ -945,11 +1107,13 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   plan->out_ptr = nullptr;
   plan->res_ptr = nullptr;
   plan->out_ld = plan->res_ld = plan->cta_pair = 0;
+  plan->operand_bf16 = half ? 1 : 0;
+  plan->out_bf16 = 0;
   if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
   plan->m = static_cast<int>(m_ll);
-  plan->c_blocks = (s->c + kBlockK - 1) / kBlockK;
+  plan->c_blocks = (s->c + kelems - 1) / kelems;
   plan->k_iters = s->kh * s->kw * plan->c_blocks;
   plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
   plan->cta_pair = pick_cta_pair(plan->block_n, plan->m, plan->k_iters);
@@ -963,24 +1127,24 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   if (pointwise) {
     // Plain row-major matrix [m, c] with row pitch c_stride.
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(s->c), static_cast<cuuint64_t>(plan->m)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(s->c_stride) * 4};
-    const cuuint32_t box[2] = {kBlockK, kBlockM};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(s->c_stride) * es};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kelems), kBlockM};
     const cuuint32_t estr[2] = {1, 1};
-    r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(in), dims, strides, box, estr,
+    r = api.tiled(ma, dtype, 2, const_cast<void*>(in), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   } else {
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(s->c), static_cast<cuuint64_t>(s->w),
                                 static_cast<cuuint64_t>(s->h), static_cast<cuuint64_t>(s->n)};
-    const cuuint64_t pix = static_cast<cuuint64_t>(s->c_stride) * 4;
+    const cuuint64_t pix = static_cast<cuuint64_t>(s->c_stride) * es;
     const cuuint64_t strides[3] = {pix, pix * s->w, pix * s->w * s->h};
     // Window of base pixels (top-left filter corners): starts at -pad and ends
     // where the last tap still lies inside the padded image.
     const int lower[2] = {-s->pad_w, -s->pad_h};
     const int upper[2] = {s->pad_w - (s->kw - 1) * s->dil_w, s->pad_h - (s->kh - 1) * s->dil_h};
     const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(s->stride_w), static_cast<cuuint32_t>(s->stride_h), 1};
-    r = api.im2col(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(in), dims, strides, lower, upper,
-                   kBlockK, kBlockM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    r = api.im2col(ma, dtype, 4, const_cast<void*>(in), dims, strides, lower, upper,
+                   static_cast<cuuint32_t>(kelems), kBlockM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     // Drivers up to CUDA 13.1 encode a flag in im2col descriptors of tensors
     // smaller than 128 KiB that makes the load misbehave; NVIDIA's CUTLASS
@@ -992,13 +1156,14 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   }
   if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
   {
-    const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kBlockK;
+    const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kelems;
     const cuuint64_t dims[2] = {kp, static_cast<cuuint64_t>(s->cout)};
-    const cuuint64_t strides[1] = {kp * 4};
+    const cuuint64_t strides[1] = {kp * es};
     // A CTA of a pair fetches half of the weight tile.
-    const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(plan->cta_pair ? plan->block_n / 2 : plan->block_n)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kelems),
+                               static_cast<cuuint32_t>(plan->cta_pair ? plan->block_n / 2 : plan->block_n)};
     const cuuint32_t estr[2] = {1, 1};
-    r = api.tiled(mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(packed_w), dims, strides, box, estr,
+    r = api.tiled(mb, dtype, 2, const_cast<void*>(packed_w), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -200 - static_cast<int>(r);
@@ -1006,11 +1171,43 @@ extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, 
   return 0;
 }
 
+int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, const mcb200_epilogue* ep, int* status,
+                void* stream);
+
+}  // namespace
+
+extern "C" int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float* packed_w,
+                                   mcb200_conv_plan* plan) {
+  return plan_core(s, in, packed_w, plan, false);
+}
+
+extern "C" int mcb200_conv_tc_plan_bf16(const mcb200_conv_shape* s, const uint16_t* in, const uint16_t* packed_w,
+                                        mcb200_conv_plan* plan) {
+  return plan_core(s, in, packed_w, plan, true);
+}
+
 extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld, const mcb200_epilogue* ep,
                                      int* status, void* stream) {
+  if (plan && plan->operand_bf16) return -8;   // bfloat16 plans go through mcb200_conv_tc_launch_bf16
+  return launch_core(plan, out, false, out_ld, ep, status, stream);
+}
+
+extern "C" int mcb200_conv_tc_launch_bf16(mcb200_conv_plan* plan, void* out, int out_is_bf16, int out_ld,
+                                          const mcb200_epilogue* ep, int* status, void* stream) {
+  if (plan && !plan->operand_bf16) return -8;
+  return launch_core(plan, out, out_is_bf16 != 0, out_ld, ep, status, stream);
+}
+
+namespace {
+
+int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, const mcb200_epilogue* ep, int* status,
+                void* stream) {
   if (!plan || !out || out_ld < plan->shape.cout) return -1;
+  const bool half = plan->operand_bf16 != 0;
+  if (out_half && !half) return -1;
   ConvTcArgs a;
-  a.out = out;
+  a.out = static_cast<float*>(out);
+  a.out_half = out_half ? 1 : 0;
   a.out_ld = out_ld;
   a.m = plan->m;
   a.cout = plan->shape.cout;
@@ -1034,23 +1231,24 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
   if (a.ep.act == 2 && !a.ep.prelu) return -2;
   a.status = status;
   // The staged epilogue needs 16-byte aligned rows; otherwise plain stores are used.
-  const bool out_ok = (out_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
-  const bool res_ok = !a.ep.residual || ((a.ep.residual_ld % 4 == 0) && a.ep.residual_ld >= plan->shape.cout &&
+  const bool out_ok = (out_ld % (out_half ? 8 : 4) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  const bool res_ok = !a.ep.residual || ((a.ep.residual_ld % (half ? 8 : 4) == 0) && a.ep.residual_ld >= plan->shape.cout &&
                                          ((reinterpret_cast<uintptr_t>(a.ep.residual) & 15) == 0));
   a.tma_epilogue = (out_ok && res_ok) ? 1 : 0;
   if (a.tma_epilogue) {
     const bool rows = plan->im2col == kModeRows;
     const long long per_group = rows ? plan->shape.wo : plan->m;
     const long long groups = rows ? static_cast<long long>(plan->shape.n) * plan->shape.ho : 1;
-    if (plan->out_ptr != out || plan->out_ld != out_ld) {
-      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_out), out, plan->shape.cout, out_ld, per_group,
-                          groups) != CUDA_SUCCESS)
+    if (plan->out_ptr != out || plan->out_ld != out_ld || plan->out_bf16 != a.out_half) {
+      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_out), out, out_half, plan->shape.cout, out_ld,
+                          per_group, groups) != CUDA_SUCCESS)
         return -4;
-      plan->out_ptr = out;
+      plan->out_ptr = static_cast<const float*>(out);
       plan->out_ld = out_ld;
+      plan->out_bf16 = a.out_half;
     }
     if (a.ep.residual && (plan->res_ptr != a.ep.residual || plan->res_ld != a.ep.residual_ld)) {
-      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_res), a.ep.residual, plan->shape.cout,
+      if (encode_tile_map(reinterpret_cast<CUtensorMap*>(plan->tma_res), a.ep.residual, half, plan->shape.cout,
                           a.ep.residual_ld, per_group, groups) != CUDA_SUCCESS)
         return -5;
       plan->res_ptr = a.ep.residual;
@@ -1063,13 +1261,34 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
   a.a_bytes = a.tile_rows * kBlockK * 4;
   cudaError_t e = cudaErrorInvalidValue;
   const int mode = plan->im2col;
-#define MCB200_DISPATCH(BN)                                                            \
-  e = mode == kModeRows     ? launch_variant<BN, kModeRows, false>(plan, a, st)        \
-      : mode == kModeIm2col ? launch_variant<BN, kModeIm2col, false>(plan, a, st)      \
-                            : launch_variant<BN, kModeMatrix, false>(plan, a, st)
-#define MCB200_DISPATCH_PAIR(BN)                                                       \
-  e = mode == kModeIm2col ? launch_variant<BN, kModeIm2col, true>(plan, a, st)         \
-                          : launch_variant<BN, kModeMatrix, true>(plan, a, st)
+#define MCB200_DISPATCH(BN)                                                               \
+  e = mode == kModeRows     ? launch_variant<BN, kModeRows, false, false>(plan, a, st)    \
+      : mode == kModeIm2col ? launch_variant<BN, kModeIm2col, false, false>(plan, a, st)  \
+                            : launch_variant<BN, kModeMatrix, false, false>(plan, a, st)
+#define MCB200_DISPATCH_PAIR(BN)                                                          \
+  e = mode == kModeIm2col ? launch_variant<BN, kModeIm2col, true, false>(plan, a, st)     \
+                          : launch_variant<BN, kModeMatrix, true, false>(plan, a, st)
+#define MCB200_DISPATCH_HALF(BN, PAIR)                                                    \
+  e = mode == kModeIm2col ? launch_variant<BN, kModeIm2col, PAIR, true>(plan, a, st)      \
+                          : launch_variant<BN, kModeMatrix, PAIR, true>(plan, a, st)
+  if (half) {
+    if (mode == kModeRows) return -3;
+    if (plan->cta_pair) {
+      switch (plan->block_n) {
+        case 128: MCB200_DISPATCH_HALF(128, true); break;
+        case 256: MCB200_DISPATCH_HALF(256, true); break;
+        default: return -3;
+      }
+    } else {
+      switch (plan->block_n) {
+        case 64: MCB200_DISPATCH_HALF(64, false); break;
+        case 128: MCB200_DISPATCH_HALF(128, false); break;
+        case 256: MCB200_DISPATCH_HALF(256, false); break;
+        default: return -3;
+      }
+    }
+    return static_cast<int>(e);
+  }
   if (plan->cta_pair) {
     if (mode == kModeRows) return -3;
     switch (plan->block_n) {
@@ -1085,10 +1304,13 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
     case 256: MCB200_DISPATCH(256); break;
     default: return -3;
   }
+#undef MCB200_DISPATCH_HALF
 #undef MCB200_DISPATCH_PAIR
 #undef MCB200_DISPATCH
   return static_cast<int>(e);
 }
+
+}  // namespace
 
 // ------------------------------------------------------------------ row mode (few input channels)
 
@@ -1194,6 +1416,7 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   plan->out_ptr = nullptr;
   plan->res_ptr = nullptr;
   plan->out_ld = plan->res_ld = plan->cta_pair = 0;
+  plan->operand_bf16 = plan->out_bf16 = 0;
   if (mcb200_conv_out_shape(&plan->shape) != 0) return -6;
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;

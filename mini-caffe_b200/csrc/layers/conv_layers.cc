@@ -61,14 +61,16 @@ void FoldTail(const FusedTail& tail, int channels, const float* bias, std::vecto
   shift->assign(b.begin(), b.end());
 }
 
-void FillTailEpilogue(const FusedTail& tail, const DeviceArray& scale, const DeviceArray& shift, bool nhwc_residual,
-                      int channels, mcb200_epilogue* ep) {
+void FillTailEpilogue(const FusedTail& tail, const DeviceArray& scale, const DeviceArray& shift,
+                      ResidualCopy residual_copy, int channels, mcb200_epilogue* ep) {
   *ep = mcb200_epilogue();
   ep->scale = scale.get();
   ep->shift = shift.get();
   ep->residual_coeff = 1.f;
   if (tail.residual) {
-    ep->residual = nhwc_residual ? tail.residual->gpu_data_nhwc() : tail.residual->gpu_data();
+    ep->residual = residual_copy == kResidualNhwcHalf
+                       ? static_cast<const float*>(tail.residual->gpu_data_nhwc_bf16())   // 16-bit cells
+                       : (residual_copy == kResidualNhwc ? tail.residual->gpu_data_nhwc() : tail.residual->gpu_data());
     ep->residual_ld = channels;
     ep->residual_coeff = tail.residual_coeff;
   }
@@ -204,6 +206,10 @@ void ConvolutionLayer::RefreshParameters() {
     if (path_ == kTensorCore && use_rows_) {
       float* packed = packed_weights_.Reserve(mcb200_conv_rows_packed_weight_count(&shape_));
       KERNEL_CHECK(mcb200_conv_rows_pack_weights(&shape_, blobs_[0]->gpu_data(), packed, ctx.stream_ptr()));
+    } else if (path_ == kTensorCore && half_operands_) {
+      float* packed = packed_weights_.Reserve((mcb200_conv_packed_weight_count_bf16(&shape_) + 1) / 2);
+      KERNEL_CHECK(mcb200_conv_pack_weights_bf16(&shape_, blobs_[0]->gpu_data(), reinterpret_cast<uint16_t*>(packed),
+                                                 ctx.stream_ptr()));
     } else if (path_ == kTensorCore) {
       float* packed = packed_weights_.Reserve(mcb200_conv_packed_weight_count(&shape_));
       KERNEL_CHECK(mcb200_conv_pack_weights(&shape_, blobs_[0]->gpu_data(), packed, ctx.stream_ptr()));
@@ -235,7 +241,11 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
   for (size_t i = 0; i < bottom.size(); ++i) {
     mcb200_conv_shape s = shape_;
     const float* in = nullptr;
-    if (path_ == kTensorCore && use_rows_) {
+    const bool half = half_operands_ && HalfStorageCapable();
+    if (half) {
+      s.c_stride = s.c;
+      in = static_cast<const float*>(bottom[i]->gpu_data_nhwc_bf16());   // 16-bit cells
+    } else if (path_ == kTensorCore && use_rows_) {
       int hp = 0, wp = 0;
       CHECK_EQ(mcb200_conv_rows_padded_dims(&s, &hp, &wp), 0);
       s.c_stride = 4;
@@ -263,14 +273,19 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
       in = padded;
     }
     mcb200_epilogue ep;
-    FillTailEpilogue(i == 0 ? tail_ : FusedTail(), scale_, shift_, true, s.cout, &ep);
-    float* out = top[i]->mutable_gpu_data_nhwc();
+    FillTailEpilogue(i == 0 ? tail_ : FusedTail(), scale_, shift_, half ? kResidualNhwcHalf : kResidualNhwc, s.cout,
+                     &ep);
+    const bool half_out = half && half_top_;
+    float* out = half_out ? static_cast<float*>(top[i]->mutable_gpu_data_nhwc_bf16()) : top[i]->mutable_gpu_data_nhwc();
     if (path_ == kTensorCore) {
       if (!plans_[i]) plans_[i].reset(new PlanSlot);
       PlanSlot& slot = *plans_[i];
       const float* w = packed_weights_.Reserve(0);
       if (!slot.valid || slot.in != in || slot.weights != w || std::memcmp(&slot.shape, &s, sizeof(s)) != 0) {
-        int rc = use_rows_ ? mcb200_conv_rows_plan(&s, in, w, &slot.plan) : mcb200_conv_tc_plan(&s, in, w, &slot.plan);
+        int rc = half ? mcb200_conv_tc_plan_bf16(&s, reinterpret_cast<const uint16_t*>(in),
+                                                 reinterpret_cast<const uint16_t*>(w), &slot.plan)
+                 : use_rows_ ? mcb200_conv_rows_plan(&s, in, w, &slot.plan)
+                             : mcb200_conv_tc_plan(&s, in, w, &slot.plan);
         if (rc != 0 && use_rows_) {
           // The driver refused the row-mode tensor map: use the general path from now on.
           LOG(WARNING) << "layer " << layer_param_.name() << ": row-mode plan rejected (" << rc
@@ -287,7 +302,12 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
         slot.shape = s;
         slot.valid = true;
       }
-      KERNEL_CHECK(mcb200_conv_tc_launch(&slot.plan, out, s.cout, &ep, ctx.status_word(), ctx.stream_ptr()));
+      if (half) {
+        KERNEL_CHECK(mcb200_conv_tc_launch_bf16(&slot.plan, out, half_out ? 1 : 0, s.cout, &ep, ctx.status_word(),
+                                                ctx.stream_ptr()));
+      } else {
+        KERNEL_CHECK(mcb200_conv_tc_launch(&slot.plan, out, s.cout, &ep, ctx.status_word(), ctx.stream_ptr()));
+      }
     } else if (path_ == kDepthwise) {
       KERNEL_CHECK(mcb200_conv_depthwise(&s, in, packed_weights_.Reserve(0), out, &ep, ctx.stream_ptr()));
     } else {
@@ -383,7 +403,7 @@ void InnerProductLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Bl
   // Rows of the (N, C, H, W)-ordered input are the K-vectors.
   const float* in = bottom[0]->gpu_data();
   mcb200_epilogue ep;
-  FillTailEpilogue(tail_, scale_, shift_, false, N_, &ep);
+  FillTailEpilogue(tail_, scale_, shift_, kResidualNchw, N_, &ep);
   float* out = top[0]->mutable_gpu_data();
   if (tensor_core) {
     if (!plan_) {

@@ -45,11 +45,22 @@ class ConvolutionLayer : public Layer {
   bool EqualNumBottomTopBlobs() const override { return true; }
   bool AcceptsFusedTail() const override { return true; }
   void SetFusedTail(const FusedTail& tail) override { tail_ = tail; tail_version_ = 0; }
+  bool HalfStorageCapable() const override {
+    return path_ == kTensorCore && !use_rows_ && shape_.c % 8 == 0 && shape_.cout % 8 == 0;
+  }
+  void SetHalfStorage(bool operands, bool top) override {
+    if (operands != half_operands_) weight_version_ = 0;   // the packed weight image differs
+    half_operands_ = operands;
+    half_top_ = operands && top;
+  }
 
  protected:
   void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
   void RefreshParameters();
   void FillEpilogue(mcb200_epilogue* ep);
+
+  bool half_operands_ = false;   // bfloat16 activations, weights and residual (tcgen05 kind::f16)
+  bool half_top_ = false;        // ... and a bfloat16 result
 
   mcb200_conv_shape shape_ = mcb200_conv_shape();
   bool bias_term_ = false;
@@ -103,8 +114,10 @@ class InnerProductLayer : public Layer {
 unsigned long long TailVersion(const FusedTail& tail);
 void FoldTail(const FusedTail& tail, int channels, const float* bias, std::vector<float>* scale,
               std::vector<float>* shift, bool* has_scale, bool* has_shift);
-void FillTailEpilogue(const FusedTail& tail, const DeviceArray& scale, const DeviceArray& shift, bool nhwc_residual,
-                      int channels, mcb200_epilogue* ep);
+// Which device copy of the residual blob the kernel reads.
+enum ResidualCopy { kResidualNchw, kResidualNhwc, kResidualNhwcHalf };
+void FillTailEpilogue(const FusedTail& tail, const DeviceArray& scale, const DeviceArray& shift,
+                      ResidualCopy residual_copy, int channels, mcb200_epilogue* ep);
 
 // ---------------------------------------------------------------- per-channel / elementwise
 

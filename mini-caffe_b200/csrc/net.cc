@@ -23,6 +23,7 @@
 #include "caffe/net.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <map>
 #include <set>
 #include <sstream>
@@ -46,7 +47,17 @@ struct NetPlan {
   std::vector<NetStep> steps;
   std::vector<std::vector<int> > input_shapes;  // shapes of the Input tops the plan was built for
   std::vector<bool> visible;                    // per blob: guaranteed readable after Forward
+  // Opt-in read when the net is constructed (environment MINICAFFE_PRECISION=bf16):
+  // blobs that only tensor-core convolutions read are stored as bfloat16.
+  bool half_storage = false;
 };
+
+namespace {
+bool HalfStorageRequested() {
+  const char* v = getenv("MINICAFFE_PRECISION");
+  return v && (std::string(v) == "bf16" || std::string(v) == "BF16" || std::string(v) == "bfloat16");
+}
+}  // namespace
 
 Net::Net(const string& param_file) : plan_(new NetPlan) {
   NetParameter param;
@@ -60,6 +71,7 @@ Net::~Net() { delete plan_; }
 
 void Net::Init(const NetParameter& param) {
   if (!plan_) plan_ = new NetPlan;
+  plan_->half_storage = HalfStorageRequested();
   name_ = param.name();
   CHECK_GT(param.layer_size(), 0) << "the net has no layers";
   std::map<string, int> blob_name_to_idx;
@@ -261,6 +273,38 @@ void Net::PlaceMemory() {
       producer->SetFusedTail(tail);
     }
     plan.steps.push_back(step);
+  }
+
+  // ---- bfloat16 storage ----
+  // A capable layer (tensor-core convolution, channel counts that are multiples
+  // of eight) computes on bfloat16 operands; its result is stored as bfloat16
+  // too if nobody but such layers reads it (as input or as fused residual) and
+  // callers cannot see it.  Everything else stays fp32, and a blob crossing the
+  // border is converted on first use by its storage object.
+  {
+    const int steps = static_cast<int>(plan.steps.size());
+    std::vector<bool> operands(steps, false);
+    for (int s = 0; s < steps; ++s) {
+      operands[s] = plan.half_storage && layers_[plan.steps[s].layer_id]->HalfStorageCapable();
+    }
+    for (int s = 0; s < steps; ++s) {
+      bool top_half = false;
+      const NetStep& step = plan.steps[s];
+      if (operands[s] && step.top_ids.size() == 1 && !plan.visible[step.top_ids[0]]) {
+        const int blob = step.top_ids[0];
+        int readers = 0;
+        top_half = true;
+        for (int k = s + 1; k < steps && top_half; ++k) {
+          const NetStep& later = plan.steps[k];
+          const bool reads = std::find(later.bottom_ids.begin(), later.bottom_ids.end(), blob) != later.bottom_ids.end();
+          const bool writes = std::find(later.top_ids.begin(), later.top_ids.end(), blob) != later.top_ids.end();
+          if (reads) ++readers;
+          if ((reads && !operands[k]) || writes) top_half = false;
+        }
+        if (readers == 0) top_half = false;
+      }
+      layers_[step.layer_id]->SetHalfStorage(operands[s], top_half);
+    }
   }
 
   // ---- lifetimes over the fused schedule ----

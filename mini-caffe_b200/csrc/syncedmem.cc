@@ -130,19 +130,20 @@ SyncedMemory::~SyncedMemory() {
   MemoryPool* pool = MemoryPool::Get();
   if (host_.ptr) {
     // A pinned block may be the target of a copy that is still in flight.
-    if (valid_ & (kDevice | kDeviceNhwc)) {
+    if (valid_ & (kDevice | kDeviceNhwc | kDeviceNhwcHalf)) {
       try { Context::Get().Sync(); } catch (...) {}
     }
     pool->ReturnCPU(host_);
   }
   if (dev_.ptr) pool->ReturnGPU(dev_);
   if (nhwc_.ptr) pool->ReturnGPU(nhwc_);
+  if (half_.ptr) pool->ReturnGPU(half_);
 }
 
 void SyncedMemory::EnsureHost() {
   if (!host_.ptr) {
     host_ = MemoryPool::Get()->RequestCPU(size_ ? size_ : 4);
-    if (!(valid_ & (kDevice | kDeviceNhwc))) {
+    if (!(valid_ & (kDevice | kDeviceNhwc | kDeviceNhwcHalf))) {
       std::memset(host_.ptr, 0, size_);  // same as the reference: fresh memory reads as zero
       valid_ |= kHost;
     }
@@ -169,7 +170,35 @@ void SyncedMemory::EnsureNhwcBuffer() {
   }
 }
 
+void SyncedMemory::EnsureHalfBuffer() {
+  if (!half_.ptr) {
+    Context& ctx = Context::Get();
+    ctx.Activate();
+    half_ = MemoryPool::Get()->RequestGPU(size_ / 2 ? size_ / 2 : 4, ctx.device());
+  }
+}
+
+void SyncedMemory::WidenHalf() {
+  if (!(valid_ & kDeviceNhwcHalf) || (valid_ & (kHost | kDevice | kDeviceNhwc))) return;
+  Context& ctx = Context::Get();
+  const size_t count = static_cast<size_t>(dims_[0]) * dims_[1] * dims_[2] * dims_[3];
+  if (OrdersCoincide(dims_[1], dims_[2], dims_[3])) {
+    EnsureDevice();
+    KERNEL_CHECK(mcb200_bf16_to_f32(static_cast<const uint16_t*>(half_.ptr), static_cast<float*>(dev_.ptr), count,
+                                    ctx.stream_ptr()));
+    valid_ |= kDevice;
+  } else {
+    EnsureNhwcBuffer();
+    KERNEL_CHECK(mcb200_bf16_to_f32(static_cast<const uint16_t*>(half_.ptr), static_cast<float*>(nhwc_.ptr), count,
+                                    ctx.stream_ptr()));
+    nhwc_aliases_dev_ = false;
+    valid_ |= kDeviceNhwc;
+  }
+}
+
 void SyncedMemory::DeviceFromFreshest() {
+  if (valid_ & kDevice) return;
+  WidenHalf();
   if (valid_ & kDevice) return;
   EnsureDevice();
   if (valid_ & kDevice) return;  // freshly zero-filled
@@ -219,6 +248,7 @@ void* SyncedMemory::mutable_gpu_data() {
 const void* SyncedMemory::gpu_data_nhwc(int n, int c, int h, int w) {
   CHECK_LE(static_cast<size_t>(n) * c * h * w * sizeof(float), size_);
   if (OrdersCoincide(c, h, w)) return gpu_data();
+  WidenHalf();
   if (valid_ & kDeviceNhwc) {
     CHECK(dims_[0] == n && dims_[1] == c && dims_[2] == h && dims_[3] == w)
         << "channels-last copy was written with another shape";
@@ -243,6 +273,33 @@ void* SyncedMemory::mutable_gpu_data_nhwc(int n, int c, int h, int w) {
   nhwc_aliases_dev_ = false;
   valid_ = kDeviceNhwc;
   return nhwc_.ptr;
+}
+
+const void* SyncedMemory::gpu_data_nhwc_bf16(int n, int c, int h, int w) {
+  const size_t count = static_cast<size_t>(n) * c * h * w;
+  CHECK_LE(count * sizeof(float), size_);
+  if (valid_ & kDeviceNhwcHalf) {
+    CHECK(dims_[0] == n && dims_[1] == c && dims_[2] == h && dims_[3] == w)
+        << "bfloat16 copy was written with another shape";
+    return half_.ptr;
+  }
+  const void* wide = gpu_data_nhwc(n, c, h, w);
+  EnsureHalfBuffer();
+  Context& ctx = Context::Get();
+  KERNEL_CHECK(mcb200_f32_to_bf16(static_cast<const float*>(wide), static_cast<uint16_t*>(half_.ptr), count,
+                                  ctx.stream_ptr()));
+  dims_[0] = n; dims_[1] = c; dims_[2] = h; dims_[3] = w;
+  valid_ |= kDeviceNhwcHalf;
+  return half_.ptr;
+}
+
+void* SyncedMemory::mutable_gpu_data_nhwc_bf16(int n, int c, int h, int w) {
+  CHECK_LE(static_cast<size_t>(n) * c * h * w * sizeof(float), size_);
+  EnsureHalfBuffer();
+  dims_[0] = n; dims_[1] = c; dims_[2] = h; dims_[3] = w;
+  nhwc_aliases_dev_ = false;
+  valid_ = kDeviceNhwcHalf;
+  return half_.ptr;
 }
 
 }  // namespace caffe

@@ -1,8 +1,11 @@
-// Storage behind a Blob: up to three copies of the same values,
+// Storage behind a Blob: up to four copies of the same values,
 //   * host (pinned when a device exists), in Caffe's (N, C, H, W) order,
 //   * device, same order,
 //   * device, channels-last (N, H, W, C) -- the order the tensor-core and most
 //     other kernels of the engine work in,
+//   * device, channels-last, rounded to bfloat16 -- written and read only by
+//     the tensor-core convolutions of a net built with bfloat16 storage; every
+//     other accessor first widens it back to fp32,
 // with a bit per copy saying whether it is current.  A read accessor brings
 // its copy up to date from whichever copy is (host<->device copies on the
 // thread's stream, layout conversion by a transpose kernel); a mutable
@@ -48,7 +51,7 @@ class MemoryPool {
 
 class SyncedMemory {
  public:
-  enum Copy { kHost = 1, kDevice = 2, kDeviceNhwc = 4 };
+  enum Copy { kHost = 1, kDevice = 2, kDeviceNhwc = 4, kDeviceNhwcHalf = 8 };
 
   explicit SyncedMemory(size_t size);
   ~SyncedMemory();
@@ -61,21 +64,26 @@ class SyncedMemory {
   // orders coincide (c == 1 or h*w == 1) it is the plain device copy.
   const void* gpu_data_nhwc(int n, int c, int h, int w);
   void* mutable_gpu_data_nhwc(int n, int c, int h, int w);
+  // bfloat16 channels-last copy (16-bit cells), rounded from the fp32 values on first use.
+  const void* gpu_data_nhwc_bf16(int n, int c, int h, int w);
+  void* mutable_gpu_data_nhwc_bf16(int n, int c, int h, int w);
 
   size_t size() const { return size_; }
   int valid() const { return valid_; }
-  bool nhwc_is_freshest() const { return (valid_ & kDeviceNhwc) && !(valid_ & kDevice); }
+  bool nhwc_is_freshest() const { return (valid_ & (kDeviceNhwc | kDeviceNhwcHalf)) && !(valid_ & kDevice); }
   unsigned long long host_version() const { return host_version_; }
 
  private:
   void EnsureHost();
   void EnsureDevice();
   void EnsureNhwcBuffer();
+  void EnsureHalfBuffer();
+  void WidenHalf();           // only the bfloat16 copy is current: make an fp32 device copy current too
   void DeviceFromFreshest();  // make kDevice valid
   static bool OrdersCoincide(int c, int h, int w) { return c == 1 || h * w == 1; }
 
   size_t size_;
-  MemBlock host_, dev_, nhwc_;
+  MemBlock host_, dev_, nhwc_, half_;
   int valid_;               // bit set of Copy
   bool nhwc_aliases_dev_;   // the channels-last copy is dev_ itself
   int dims_[4];             // (n, c, h, w) the channels-last copy was written with

@@ -1,0 +1,123 @@
+"""bfloat16 storage, the engine's precision opt-in (environment MINICAFFE_PRECISION=bf16, read when a
+net is constructed): tensor-core convolutions whose channel counts are multiples of eight take their
+operands as bfloat16, and blobs that only such layers read are stored as bfloat16.
+
+Stated bound for this mode, looser than the TF32 one: elementwise
+
+    |a - b| <= 1e-1 * max(1, rms(b)) + 4e-2 * |b|
+
+against the reference's fp32 CPU results (bfloat16 carries 8 significant bits, i.e. 2^-9 relative per
+rounding, and a 50-layer net rounds every activation once per layer: measured on ResNet-50, the
+largest error of a late blob is about 1 % of the blob's peak and 7 % of its RMS, four times the TF32
+figure), and the default fp32 / TF32
+behaviour must be untouched when the variable is absent.
+"""
+import numpy as np
+import pytest
+
+from conftest import pkg
+from parity import assert_close, error_stats, run_net
+
+pytestmark = pytest.mark.gpu
+
+BF16_ATOL = 1e-1
+BF16_RTOL = 4e-2
+
+
+@pytest.fixture(scope="module")
+def gpu_engine(engine):
+    engine.set_mode(True, 0)
+    return engine
+
+
+def run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=()):
+    monkeypatch.delenv("MINICAFFE_PRECISION", raising=False)
+    wide = run_net(capi, gpu_engine, b, weights, x, outs, marks=marks)
+    monkeypatch.setenv("MINICAFFE_PRECISION", "bf16")
+    narrow = run_net(capi, gpu_engine, b, weights, x, outs, marks=marks)
+    monkeypatch.delenv("MINICAFFE_PRECISION", raising=False)
+    return wide, narrow
+
+
+def test_single_convolution(monkeypatch, capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.conv_relu(2)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.conv_relu_input(2)
+    out = "conv"
+    wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, [out])
+    want = run_net(capi, reflib, b, weights, x, [out])
+    assert_close(wide[out], want[out], "tf32")
+    assert_close(narrow[out], want[out], "bf16", atol=BF16_ATOL, rtol=BF16_RTOL)
+    # the two modes really are different arithmetic
+    assert not np.array_equal(wide[out], narrow[out])
+
+
+def test_resnet50_batch4(monkeypatch, capi, gpu_engine, reflib):
+    wl = pkg("workloads")
+    b = wl.resnet50(4)
+    weights = wl.init_params(b.params, seed=3)
+    x = wl.image_input(4, seed=5)
+    outs = ["res2c", "res4f", "pool5", "fc1000", "prob"]
+    marks = ["res2c", "res4f"]
+    wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=marks)
+    want = run_net(capi, reflib, b, weights, x, outs, marks=marks)
+    for name in outs:
+        st = assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
+        tf = error_stats(wide[name], want[name])
+        print("%-8s bf16 max|err|/peak %.2e   tf32 %.2e" % (name, st["max_abs_over_peak"], tf["max_abs_over_peak"]))
+    assert np.array_equal(np.argmax(narrow["prob"], axis=1), np.argmax(want["prob"], axis=1))
+
+
+def test_mixed_consumers(monkeypatch, capi, gpu_engine, reflib):
+    """Blobs that cross the border between bfloat16 and fp32 layers: a convolution output read by a
+    pooling layer and by another convolution, a residual that comes from a pooling layer, a grouped
+    convolution (direct kernel, fp32) between two tensor-core ones, 20 output channels (not a
+    multiple of eight: that layer stays TF32), and a standalone Eltwise."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("mixed")
+    b.input([("data", (3, 16, 20, 24))])
+    b.conv("a", "data", "a", 16, 32, 3, pad=1)
+    b.relu("a_relu", "a")
+    b.raw("pool", "Pooling", ["a"], ["pool"], "pooling_param { pool: MAX kernel_size: 3 stride: 1 pad: 1 }")
+    b.conv("b", "a", "b", 32, 32, 1)
+    b.conv("c", "b", "c", 32, 32, 3, pad=1)
+    b.raw("sum", "Eltwise", ["c", "pool"], ["sum"], "eltwise_param { operation: SUM }")
+    b.relu("sum_relu", "sum")
+    b.conv("g", "sum", "g", 32, 32, 3, pad=1, group=4)
+    b.conv("d", "g", "d", 32, 20, 1)
+    b.conv("e", "d", "e", 20, 16, 3, pad=1)
+    b.raw("twice", "Eltwise", ["e", "e"], ["twice"], "eltwise_param { operation: SUM }")
+    weights = wl.init_params(b.params, seed=11)
+    x = {"data": np.random.default_rng(12).standard_normal((3, 16, 20, 24)).astype(np.float32)}
+    outs = ["a", "sum", "g", "d", "twice"]
+    marks = ["a", "sum", "g", "d"]
+    wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=marks)
+    want = run_net(capi, reflib, b, weights, x, outs, marks=marks)
+    for name in outs:
+        assert_close(wide[name], want[name], "tf32 " + name)
+        assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
+    # nothing marked: more blobs become bfloat16-only; the final result must still agree
+    wide2, narrow2 = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, ["twice"])
+    assert np.array_equal(wide2["twice"], wide["twice"])
+    assert_close(narrow2["twice"], want["twice"], "bf16 unmarked", atol=BF16_ATOL, rtol=BF16_RTOL)
+
+
+def test_repeated_passes_and_new_input(monkeypatch, capi, gpu_engine):
+    """The bfloat16 copies are rebuilt on every pass: a second pass with another input gives that
+    input's result, and a repeat of the first input repeats the first result bit for bit."""
+    wl = pkg("workloads")
+    monkeypatch.setenv("MINICAFFE_PRECISION", "bf16")
+    b = wl.resnet50(2)
+    net = capi.Net(gpu_engine, b.text(), None, from_buffer=True)
+    net.set_params(wl.init_params(b.params, seed=1))
+    x1, x2 = wl.image_input(2, seed=1), wl.image_input(2, seed=2)
+    net.forward(**x1)
+    first = net.blob("fc1000").data.copy()
+    net.forward(**x2)
+    second = net.blob("fc1000").data.copy()
+    net.forward(**x1)
+    again = net.blob("fc1000").data.copy()
+    net.close()
+    assert not np.array_equal(first, second)
+    assert np.array_equal(first, again)

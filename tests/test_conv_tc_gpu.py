@@ -34,7 +34,8 @@ class ConvPlan(ctypes.Structure):
                 ("tma_out", ctypes.c_uint64 * 16), ("tma_res", ctypes.c_uint64 * 16), ("shape", ConvShape),
                 ("m", ctypes.c_int), ("k_iters", ctypes.c_int), ("c_blocks", ctypes.c_int),
                 ("block_n", ctypes.c_int), ("im2col", ctypes.c_int), ("out_ld", ctypes.c_int),
-                ("res_ld", ctypes.c_int), ("cta_pair", ctypes.c_int), ("out_ptr", ctypes.c_void_p),
+                ("res_ld", ctypes.c_int), ("cta_pair", ctypes.c_int), ("operand_bf16", ctypes.c_int),
+                ("out_bf16", ctypes.c_int), ("out_ptr", ctypes.c_void_p),
                 ("res_ptr", ctypes.c_void_p)]
 
 
@@ -211,3 +212,105 @@ def test_every_tile_width_gives_the_same_result(kernels, block_n):
     got, plan = _with_planner(block_n, "0", lambda: run_conv(kernels, x.cuda(), wt, **kw))
     assert plan.block_n == block_n
     assert torch.equal(base, got)
+
+
+# ---------------------------------------------------------------- bfloat16 storage (opt-in)
+
+def run_conv_bf16(lib, x_nchw, w, *, out_bf16, stride=1, pad=0, dil=1, scale=None, shift=None, residual=None,
+                  act=0):
+    """The same kernel on bfloat16 activations / weights / residual (mcb200_conv_tc_plan_bf16 and
+    mcb200_conv_tc_launch_bf16); the inputs are converted with the library's own copy kernel."""
+    L = lib
+    L.mcb200_conv_packed_weight_count_bf16.restype = ctypes.c_size_t
+    n, c, h, wd = x_nchw.shape
+    cout, _, kh, kw = w.shape
+    x32 = x_nchw.permute(0, 2, 3, 1).contiguous().cuda()
+    x16 = torch.empty(x32.shape, device="cuda", dtype=torch.bfloat16)
+    assert L.mcb200_f32_to_bf16(ctypes.c_void_p(x32.data_ptr()), ctypes.c_void_p(x16.data_ptr()),
+                                ctypes.c_size_t(x32.numel()), None) == 0
+    assert torch.equal(x16, x32.to(torch.bfloat16))          # round to nearest even, like torch
+    s = ConvShape(n, h, wd, c, c, cout, kh, kw, stride, stride, pad, pad, dil, dil, 1, 0, 0)
+    assert L.mcb200_conv_out_shape(ctypes.byref(s)) == 0
+    packed = torch.empty(L.mcb200_conv_packed_weight_count_bf16(ctypes.byref(s)), device="cuda", dtype=torch.bfloat16)
+    wdev = w.contiguous().cuda()
+    assert L.mcb200_conv_pack_weights_bf16(ctypes.byref(s), ctypes.c_void_p(wdev.data_ptr()),
+                                           ctypes.c_void_p(packed.data_ptr()), None) == 0
+    plan = aligned_plan()
+    rc = L.mcb200_conv_tc_plan_bf16(ctypes.byref(s), ctypes.c_void_p(x16.data_ptr()),
+                                    ctypes.c_void_p(packed.data_ptr()), ctypes.byref(plan))
+    assert rc == 0, rc
+    assert plan.operand_bf16 == 1
+    out = torch.full((n, s.ho, s.wo, cout), float("nan"), device="cuda",
+                     dtype=torch.bfloat16 if out_bf16 else torch.float32)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    ep = Epilogue()
+    ep.residual_coeff = 1.0
+    keep = []
+    for name, t in (("scale", scale), ("shift", shift)):
+        if t is not None:
+            d = t.contiguous().cuda()
+            keep.append(d)
+            setattr(ep, name, d.data_ptr())
+    if residual is not None:
+        r = residual.permute(0, 2, 3, 1).contiguous().cuda().to(torch.bfloat16)
+        keep.append(r)
+        ep.residual = r.data_ptr()
+        ep.residual_ld = cout
+    ep.act = act
+    # the fp32 entry point refuses a bfloat16 plan
+    assert L.mcb200_conv_tc_launch(ctypes.byref(plan), ctypes.c_void_p(out.data_ptr()), cout, ctypes.byref(ep),
+                                   ctypes.c_void_p(status.data_ptr()), None) == -8
+    rc = L.mcb200_conv_tc_launch_bf16(ctypes.byref(plan), ctypes.c_void_p(out.data_ptr()), 1 if out_bf16 else 0, cout,
+                                      ctypes.byref(ep), ctypes.c_void_p(status.data_ptr()), None)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "kernel reported a timed-out barrier wait"
+    if out_bf16:
+        widened = torch.empty(out.shape, device="cuda", dtype=torch.float32)
+        assert L.mcb200_bf16_to_f32(ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(widened.data_ptr()),
+                                    ctypes.c_size_t(out.numel()), None) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(widened, out.float())
+        out = widened
+    return out.permute(0, 3, 1, 2).contiguous().cpu(), plan
+
+
+BF16_CASES = [
+    # name, N, C, H, W, Cout, k, stride, pad, dil, residual, out_bf16
+    ("pointwise_res", 2, 64, 28, 28, 256, 1, 1, 0, 1, True, True),
+    ("pointwise_to_fp32", 2, 256, 14, 14, 64, 1, 1, 0, 1, False, False),
+    ("res_to_fp32", 1, 512, 7, 7, 2048, 1, 1, 0, 1, True, False),
+    ("3x3", 2, 64, 56, 56, 64, 3, 1, 1, 1, False, True),
+    ("3x3_stride2_pairs", 3, 128, 28, 28, 128, 3, 2, 1, 1, False, True),
+    ("1x1_stride2", 2, 256, 28, 28, 512, 1, 2, 0, 1, False, True),
+    ("odd_channels", 3, 24, 13, 17, 40, 3, 1, 1, 1, True, True),      # 24 channels: one partial block of 64
+    ("wide_k", 2, 1024, 14, 14, 256, 1, 1, 0, 1, False, True),
+    ("unaligned_out", 2, 32, 9, 11, 20, 3, 1, 1, 1, True, True),      # 20 output channels: plain bfloat16 stores
+]
+
+
+@pytest.mark.parametrize("case", BF16_CASES, ids=[c[0] for c in BF16_CASES])
+def test_conv_tc_bfloat16_storage(kernels, case):
+    """Operands rounded to bfloat16 exactly as the kernel sees them, products accumulated in double:
+    what is left is the fp32 accumulation (relative 1e-5 of the largest value) and, for bfloat16 output,
+    one rounding of the result (2^-9 relative)."""
+    name, n, c, h, w, cout, k, stride, pad, dil, with_res, out_bf16 = case
+    g = torch.Generator().manual_seed(4321)
+    x = torch.randn((n, c, h, w), generator=g)
+    wt = torch.randn((cout, c, k, k), generator=g) * (2.0 / (c * k * k)) ** 0.5
+    scale = torch.rand(cout, generator=g) + 0.5
+    shift = torch.randn(cout, generator=g)
+    ho = (h + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    wo = (w + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    res = torch.randn((n, cout, ho, wo), generator=g) if with_res else None
+    got, plan = run_conv_bf16(kernels, x, wt, out_bf16=out_bf16, stride=stride, pad=pad, dil=dil, scale=scale,
+                              shift=shift, residual=res, act=1)
+    xr, wr = x.to(torch.bfloat16).float(), wt.to(torch.bfloat16).float()
+    rr = res.to(torch.bfloat16).float() if with_res else None
+    want = reference(xr, wr, stride=stride, pad=pad, dil=dil, scale=scale, shift=shift, residual=rr, res_coeff=1.0,
+                     act=1, slope=0.0, prelu=None)
+    assert got.shape == want.shape
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    bound = 2e-5 * float(want.abs().max()) + (want.abs() * 2.0 ** -8 if out_bf16 else 0.0)
+    assert (err <= bound).all(), (name, float(err.max()), plan.block_n, plan.cta_pair)
