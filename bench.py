@@ -317,8 +317,16 @@ def main():
     ap.add_argument("--workload", default="resnet50",
                     choices=["resnet50", "proposal", "detection_output", "psroi_pooling"],
                     help="resnet50 is the benchmark; the others time one detection-tail layer on its own")
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"],
+                    help="tf32 (default, the benchmark: fp32 storage, TF32 tensor cores) or the engine's bfloat16 "
+                         "storage opt-in for the whole run (profiler captures of that mode)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    # The engine reads the opt-in from the environment when a net is constructed.
+    if args.precision == "bf16":
+        os.environ["MINICAFFE_PRECISION"] = "bf16"
+    else:
+        os.environ.pop("MINICAFFE_PRECISION", None)
 
     capi = importlib.import_module("mini-caffe_b200.capi")
     wl = importlib.import_module("mini-caffe_b200.workloads")
@@ -492,7 +500,7 @@ def main():
         if conv_ms is None or session_ms.value < conv_ms.value:
             conv_ms, conv_launches = session_ms, session_launches
     peaks = load_peaks()
-    conv_bytes = wl.resnet50_conv_bytes(batch)          # per forward pass
+    conv_bytes = wl.resnet50_conv_bytes(batch, bf16_storage=args.precision == "bf16")   # per forward pass
     conv_flops = wl.resnet50_flops_per_image() * batch
     conv_s_per_step = conv_ms.value * 1e-3 / timed_steps
     launches_per_step = conv_launches / timed_steps
@@ -501,7 +509,7 @@ def main():
         "kernel": "conv_tc_kernel (tcgen05 implicit GEMM, %d launches per forward)" % round(launches_per_step),
         "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
         "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
-        "traffic": CONV_DRAM_BYTES_PER_LAUNCH if batch == BATCH_PER_GPU else None,
+        "traffic": CONV_DRAM_BYTES_PER_LAUNCH if (batch == BATCH_PER_GPU and args.precision == "tf32") else None,
         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum averaged over the 54 launches of a pass, from "
                         "the ncu capture summarised in profiles/conv_tc_kernel_resnet50_b64.md (same workload)",
         "algorithmic_bytes_per_launch": conv_bytes / launches_per_step,
@@ -531,7 +539,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
             "config": {"workload": "resnet50 forward (Caffe layout conv+BN+Scale+ReLU, Eltwise residuals), batch %d "
                                    "per GPU, 3x224x224 fp32 input" % batch,
                        "global_batch": world * batch, "parallelism": "replica per GPU, batch sharded, no collective",

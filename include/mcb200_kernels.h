@@ -113,7 +113,10 @@ int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld,
  * accumulation, the fused tail is evaluated in fp32 and the result is stored
  * as bfloat16 (out_is_bf16 != 0) or fp32.  c_stride % 8 == 0; `ep->residual`
  * is read as a bfloat16 pointer with `residual_ld` in elements.  Weights:
- * [cout][kh*kw][roundup(c,64)] bfloat16, round to nearest even.               */
+ * [cout][kh*kw][roundup(c,64)] bfloat16, round to nearest even.
+ * mcb200_conv_tc_launch_bf16 also takes plans of the fp32 entry points
+ * (mcb200_conv_tc_plan, mcb200_conv_rows_plan): fp32 operands and residual,
+ * TF32 tensor cores, result stored as bfloat16 or fp32.                       */
 size_t mcb200_conv_packed_weight_count_bf16(const mcb200_conv_shape* s);
 int mcb200_conv_pack_weights_bf16(const mcb200_conv_shape* s, const float* w_oihw, uint16_t* packed, void* stream);
 int mcb200_conv_tc_plan_bf16(const mcb200_conv_shape* s, const uint16_t* in, const uint16_t* packed_w,
@@ -192,6 +195,12 @@ void mcb200_pool_out_shape(int h, int w, int kh, int kw, int sh, int sw, int ph,
  * to the padded image (src/layers/pooling_layer.cpp:124-181).                */
 int mcb200_pool_nhwc(const float* in, float* out, int n, int h, int w, int c, int kh, int kw, int sh, int sw,
                      int ph, int pw, int ho, int wo, int method, void* stream);
+/* MAX pooling with a 2x2 or 3x3 window over a bfloat16 channels-last tensor
+ * (c % 8 == 0), for nets that store their activations as bfloat16: equal to
+ * pooling the fp32 tensor and rounding the result.                           */
+int mcb200_pool_max_nhwc_bf16_supported(int c, int kh, int kw);
+int mcb200_pool_max_nhwc_bf16(const uint16_t* in, uint16_t* out, int n, int h, int w, int c, int kh, int kw,
+                              int sh, int sw, int ph, int pw, int ho, int wo, void* stream);
 
 /* ------------------------------------------------------------------ softmax */
 /* Softmax over `channels` of data viewed as [outer, channels, inner]

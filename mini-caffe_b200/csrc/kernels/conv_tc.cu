@@ -85,7 +85,7 @@ struct ConvTcArgs {
   int a_bytes;       // bytes one activation tile load delivers
   int stages;        // depth of the operand ring (2 .. kMaxStages)
   int slots;         // staging slots per epilogue warp: 1 or 2; 2 or 3 when a residual is added
-  int out_half;      // bfloat16 operands only: the output is stored as bfloat16 too (else fp32)
+  int out_half;      // the output is stored as bfloat16 (else fp32), whatever the operands are
 };
 
 constexpr int kMaxStages = 8;
@@ -148,7 +148,8 @@ struct RingPos {
 //
 // kHalf: activations, weights and the residual are bfloat16 (tcgen05.mma
 // kind::f16, fp32 accumulation); a k-iteration then covers 64 channels in the
-// same 128-byte rows.  The output is bfloat16 or fp32 (args.out_half).
+// same 128-byte rows.  Independently of that, the output is stored as fp32 or
+// as bfloat16 (args.out_half).
 template <int BN, int kMode, bool kPair, bool kHalf>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -639,53 +640,44 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // shared-memory round trip after the other (long ones while the
           // tensor core and the TMA keep shared memory busy).
           float4 v[8];
-          if (kHalf) {
-            // bfloat16 rows are 64 bytes: four 16-byte pieces, piece p stored at
-            // position p ^ ((row >> 1) & 3) (the 64-byte swizzle).
-            uint8_t* hrow = reinterpret_cast<uint8_t*>(slot_ptr(slot)) + lane * 64;
-            const int hswz = (lane >> 1) & 3;
-            if (has_res) {
-              uint4 w[4];
+          // bfloat16 rows are 64 bytes: four 16-byte pieces, piece q stored at
+          // position q ^ ((row >> 1) & 3) (the 64-byte swizzle).
+          uint8_t* hrow = reinterpret_cast<uint8_t*>(slot_ptr(slot)) + lane * 64;
+          const int hswz = (lane >> 1) & 3;
+          if (!has_res) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const uint4*>(hrow + ((q ^ hswz) << 4));
+            for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+          } else if (kHalf) {
+            uint4 w[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                v[2 * q] = finish4(2 * q, make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)),
-                                   true);
-                v[2 * q + 1] = finish4(2 * q + 1,
-                                       make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
-                                       true);
-              }
-            } else {
+            for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const uint4*>(hrow + ((q ^ hswz) << 4));
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
-            }
-            if (args.out_half) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 w;
-                w.x = pack_bf16x2(v[2 * q].x, v[2 * q].y);
-                w.y = pack_bf16x2(v[2 * q].z, v[2 * q].w);
-                w.z = pack_bf16x2(v[2 * q + 1].x, v[2 * q + 1].y);
-                w.w = pack_bf16x2(v[2 * q + 1].z, v[2 * q + 1].w);
-                *reinterpret_cast<uint4*>(hrow + ((q ^ hswz) << 4)) = w;
-              }
-            } else {
-              // fp32 rows (128 bytes) overlap other lanes' bfloat16 residual rows.
-              if (has_res) __syncwarp();
-#pragma unroll
-              for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
+            for (int q = 0; q < 4; ++q) {
+              v[2 * q] = finish4(2 * q, make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)),
+                                 true);
+              v[2 * q + 1] = finish4(2 * q + 1,
+                                     make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
+                                     true);
             }
           } else {
-            if (has_res) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                v[j] = finish4(j, *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2)), true);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+            for (int j = 0; j < 8; ++j) {
+              v[j] = finish4(j, *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2)), true);
             }
+          }
+          // Residual and result rows of different widths overlap other lanes' rows.
+          if (has_res && (args.out_half != 0) != kHalf) __syncwarp();
+          if (args.out_half) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_bf16x2(v[2 * q].x, v[2 * q].y);
+              w.y = pack_bf16x2(v[2 * q].z, v[2 * q].w);
+              w.z = pack_bf16x2(v[2 * q + 1].x, v[2 * q + 1].y);
+              w.w = pack_bf16x2(v[2 * q + 1].z, v[2 * q + 1].w);
+              *reinterpret_cast<uint4*>(hrow + ((q ^ hswz) << 4)) = w;
+            }
+          } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
           }
@@ -713,7 +705,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               return ep.residual[res_off + c];
             };
             auto store_at = [&](int c, float value) {
-              if (kHalf && args.out_half) {
+              if (args.out_half) {
                 reinterpret_cast<uint16_t*>(args.out)[out_off + c] = static_cast<uint16_t>(pack_bf16x2(value, 0.f));
               } else {
                 args.out[out_off + c] = value;
@@ -1194,7 +1186,6 @@ extern "C" int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out
 
 extern "C" int mcb200_conv_tc_launch_bf16(mcb200_conv_plan* plan, void* out, int out_is_bf16, int out_ld,
                                           const mcb200_epilogue* ep, int* status, void* stream) {
-  if (plan && !plan->operand_bf16) return -8;
   return launch_core(plan, out, out_is_bf16 != 0, out_ld, ep, status, stream);
 }
 
@@ -1204,7 +1195,6 @@ int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, co
                 void* stream) {
   if (!plan || !out || out_ld < plan->shape.cout) return -1;
   const bool half = plan->operand_bf16 != 0;
-  if (out_half && !half) return -1;
   ConvTcArgs a;
   a.out = static_cast<float*>(out);
   a.out_half = out_half ? 1 : 0;

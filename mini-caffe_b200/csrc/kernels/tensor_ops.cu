@@ -313,6 +313,53 @@ __global__ void pool_max_small_kernel(const float4* __restrict__ in, float4* __r
   }
 }
 
+// The same window maximum over bfloat16 cells, eight channels (16 bytes) per
+// thread.  Rounding to bfloat16 is monotonic, so the maximum of rounded values
+// is the rounded maximum: a bfloat16 blob pooled here equals the fp32 blob
+// pooled and then rounded.  Taps outside the image count as the most negative
+// finite bfloat16.
+template <int K>
+__global__ void pool_max_small_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, PoolArgs a) {
+  const int cg = a.c >> 3;
+  const unsigned total = static_cast<unsigned>(a.n) * a.ho * a.wo * cg;
+  auto max2 = [](uint32_t p, uint32_t q) {
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(p), "r"(q));
+    return r;
+  };
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned g = i % cg;
+    unsigned t = i / cg;
+    const int ox = static_cast<int>(t % a.wo);
+    t /= a.wo;
+    const int oy = static_cast<int>(t % a.ho);
+    const unsigned n = t / a.ho;
+    const int y0 = oy * a.sh - a.ph;
+    const int x0 = ox * a.sw - a.pw;
+    const uint4* base = in + static_cast<size_t>(n) * a.h * a.w * cg + g;
+    uint4 v[K * K];
+#pragma unroll
+    for (int dy = 0; dy < K; ++dy) {
+#pragma unroll
+      for (int dx = 0; dx < K; ++dx) {
+        const int y = y0 + dy, x = x0 + dx;
+        const bool inside = y >= 0 && y < a.h && x >= 0 && x < a.w;
+        v[dy * K + dx] = inside ? __ldg(base + (static_cast<size_t>(y) * a.w + x) * cg)
+                                : make_uint4(0xFF7FFF7Fu, 0xFF7FFF7Fu, 0xFF7FFF7Fu, 0xFF7FFF7Fu);
+      }
+    }
+    uint4 m = v[0];
+#pragma unroll
+    for (int j = 1; j < K * K; ++j) {
+      m.x = max2(m.x, v[j].x);
+      m.y = max2(m.y, v[j].y);
+      m.z = max2(m.z, v[j].z);
+      m.w = max2(m.w, v[j].w);
+    }
+    out[i] = m;
+  }
+}
+
 // ---------------------------------------------------------------- softmax
 
 // inner == 1: one warp per row, the row is streamed three times from L1/L2
@@ -543,6 +590,31 @@ extern "C" int mcb200_pool_nhwc(const float* in, float* out, int n, int h, int w
     pool_nhwc_kernel<4><<<grid_for(items, threads), threads, 0, as_stream(stream)>>>(in, out, a);
   } else {
     pool_nhwc_kernel<1><<<grid_for(items, threads), threads, 0, as_stream(stream)>>>(in, out, a);
+  }
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_pool_max_nhwc_bf16_supported(int c, int kh, int kw) {
+  return (c % 8 == 0 && kh == kw && (kh == 2 || kh == 3)) ? 1 : 0;
+}
+
+extern "C" int mcb200_pool_max_nhwc_bf16(const uint16_t* in, uint16_t* out, int n, int h, int w, int c, int kh, int kw,
+                                         int sh, int sw, int ph, int pw, int ho, int wo, void* stream) {
+  if (!in || !out || n < 0 || h < 1 || w < 1 || c < 1 || sh < 1 || sw < 1 || ho < 1 || wo < 1) return -1;
+  if (!mcb200_pool_max_nhwc_bf16_supported(c, kh, kw)) return -2;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return -3;
+  if (n == 0) return 0;
+  PoolArgs a = {n, h, w, c, kh, kw, sh, sw, ph, pw, ho, wo, MCB200_POOL_MAX};
+  const long long items = static_cast<long long>(n) * ho * wo * (c / 8);
+  if (items >= 0x7fffffffLL) return -4;
+  const int threads = 256;
+  const uint4* in4 = reinterpret_cast<const uint4*>(in);
+  uint4* out4 = reinterpret_cast<uint4*>(out);
+  if (kh == 3) {
+    pool_max_small_bf16_kernel<3><<<grid_for(items, threads, 32), threads, 0, as_stream(stream)>>>(in4, out4, a);
+  } else {
+    pool_max_small_bf16_kernel<2><<<grid_for(items, threads, 32), threads, 0, as_stream(stream)>>>(in4, out4, a);
   }
   count_launch();
   return static_cast<int>(cudaGetLastError());

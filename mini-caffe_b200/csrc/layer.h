@@ -104,10 +104,14 @@ class Layer {
   // Consumer side: true if the layer is y = sum_i coeff[i] * bottom[i].
   virtual bool AsWeightedSum(std::vector<float>* coeffs) { return false; }
   // ---- bfloat16 storage (nets built with MINICAFFE_PRECISION=bf16) ----
-  // True if the layer, as shaped now, can take its bottoms (and a fused
-  // residual) from their bfloat16 copies and store top 0 as bfloat16.
-  virtual bool HalfStorageCapable() const { return false; }
-  // operands: read bottoms / residual as bfloat16; top: store top 0 as bfloat16.
+  // As shaped now: can the layer take its bottoms (and a fused residual) from
+  // their bfloat16 copies / store top 0 as bfloat16?  HalfNeedsBoth: only both
+  // together (a layer without arithmetic of its own, e.g. max pooling).
+  virtual bool HalfOperandsCapable() const { return false; }
+  virtual bool HalfTopCapable() const { return false; }
+  virtual bool HalfNeedsBoth() const { return false; }
+  // The net's decision.  operands: read bottoms / residual as bfloat16; top:
+  // store top 0 as bfloat16.
   virtual void SetHalfStorage(bool operands, bool top) {}
   // Sum of host_version() over the parameter blobs: changes when weights do.
   unsigned long long ParamVersion() const {

@@ -241,7 +241,7 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
   for (size_t i = 0; i < bottom.size(); ++i) {
     mcb200_conv_shape s = shape_;
     const float* in = nullptr;
-    const bool half = half_operands_ && HalfStorageCapable();
+    const bool half = half_operands_ && HalfOperandsCapable();
     if (half) {
       s.c_stride = s.c;
       in = static_cast<const float*>(bottom[i]->gpu_data_nhwc_bf16());   // 16-bit cells
@@ -275,7 +275,7 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
     mcb200_epilogue ep;
     FillTailEpilogue(i == 0 ? tail_ : FusedTail(), scale_, shift_, half ? kResidualNhwcHalf : kResidualNhwc, s.cout,
                      &ep);
-    const bool half_out = half && half_top_;
+    const bool half_out = half_top_ && HalfTopCapable();
     float* out = half_out ? static_cast<float*>(top[i]->mutable_gpu_data_nhwc_bf16()) : top[i]->mutable_gpu_data_nhwc();
     if (path_ == kTensorCore) {
       if (!plans_[i]) plans_[i].reset(new PlanSlot);
@@ -302,7 +302,7 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
         slot.shape = s;
         slot.valid = true;
       }
-      if (half) {
+      if (half || half_out) {
         KERNEL_CHECK(mcb200_conv_tc_launch_bf16(&slot.plan, out, half_out ? 1 : 0, s.cout, &ep, ctx.status_word(),
                                                 ctx.stream_ptr()));
       } else {

@@ -45,13 +45,12 @@ class ConvolutionLayer : public Layer {
   bool EqualNumBottomTopBlobs() const override { return true; }
   bool AcceptsFusedTail() const override { return true; }
   void SetFusedTail(const FusedTail& tail) override { tail_ = tail; tail_version_ = 0; }
-  bool HalfStorageCapable() const override {
-    return path_ == kTensorCore && !use_rows_ && shape_.c % 8 == 0 && shape_.cout % 8 == 0;
-  }
+  bool HalfOperandsCapable() const override { return path_ == kTensorCore && !use_rows_ && shape_.c % 8 == 0; }
+  bool HalfTopCapable() const override { return path_ == kTensorCore && shape_.cout % 8 == 0; }
   void SetHalfStorage(bool operands, bool top) override {
     if (operands != half_operands_) weight_version_ = 0;   // the packed weight image differs
     half_operands_ = operands;
-    half_top_ = operands && top;
+    half_top_ = top;
   }
 
  protected:
@@ -60,7 +59,7 @@ class ConvolutionLayer : public Layer {
   void FillEpilogue(mcb200_epilogue* ep);
 
   bool half_operands_ = false;   // bfloat16 activations, weights and residual (tcgen05 kind::f16)
-  bool half_top_ = false;        // ... and a bfloat16 result
+  bool half_top_ = false;        // the result is stored as bfloat16
 
   mcb200_conv_shape shape_ = mcb200_conv_shape();
   bool bias_term_ = false;
@@ -232,8 +231,18 @@ class PoolingLayer : public Layer {
   const char* type() const override { return "Pooling"; }
   int ExactNumBottomBlobs() const override { return 1; }
   int ExactNumTopBlobs() const override { return 1; }
+  // Max pooling commutes with rounding to bfloat16: a bfloat16 blob is pooled as it is.
+  bool HalfOperandsCapable() const override {
+    return method_ == MCB200_POOL_MAX && channels_ > 0 &&
+           mcb200_pool_max_nhwc_bf16_supported(channels_, kernel_h_, kernel_w_) != 0;
+  }
+  bool HalfTopCapable() const override { return HalfOperandsCapable(); }
+  bool HalfNeedsBoth() const override { return true; }
+  void SetHalfStorage(bool operands, bool top) override { half_ = operands && top; }
  protected:
   void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
+  bool half_ = false;      // bottom and top are bfloat16-stored
+  int channels_ = 0;       // of the bottom, 0 unless it has four axes
   int kernel_h_ = 0, kernel_w_ = 0, stride_h_ = 1, stride_w_ = 1, pad_h_ = 0, pad_w_ = 0;
   int pooled_h_ = 0, pooled_w_ = 0;
   bool global_ = false;

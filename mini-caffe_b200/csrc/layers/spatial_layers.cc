@@ -75,10 +75,19 @@ void PoolingLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top
     CHECK_LT((pooled_w_ - 1) * stride_w_, bottom[0]->width() + pad_w_);
   }
   top[0]->Reshape(bottom[0]->num(), bottom[0]->channels(), pooled_h_, pooled_w_);
+  channels_ = bottom[0]->channels();
 }
 
 void PoolingLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   Context& ctx = Context::Get();
+  if (half_ && HalfOperandsCapable()) {
+    const uint16_t* in16 = static_cast<const uint16_t*>(bottom[0]->gpu_data_nhwc_bf16());
+    uint16_t* out16 = static_cast<uint16_t*>(top[0]->mutable_gpu_data_nhwc_bf16());
+    KERNEL_CHECK(mcb200_pool_max_nhwc_bf16(in16, out16, bottom[0]->num(), bottom[0]->height(), bottom[0]->width(),
+                                           bottom[0]->channels(), kernel_h_, kernel_w_, stride_h_, stride_w_, pad_h_,
+                                           pad_w_, pooled_h_, pooled_w_, ctx.stream_ptr()));
+    return;
+  }
   const float* in = bottom[0]->gpu_data_nhwc();
   float* out = top[0]->mutable_gpu_data_nhwc();
   KERNEL_CHECK(mcb200_pool_nhwc(in, out, bottom[0]->num(), bottom[0]->height(), bottom[0]->width(),

@@ -276,34 +276,65 @@ void Net::PlaceMemory() {
   }
 
   // ---- bfloat16 storage ----
-  // A capable layer (tensor-core convolution, channel counts that are multiples
-  // of eight) computes on bfloat16 operands; its result is stored as bfloat16
-  // too if nobody but such layers reads it (as input or as fused residual) and
-  // callers cannot see it.  Everything else stays fp32, and a blob crossing the
-  // border is converted on first use by its storage object.
+  // Which blobs exist only as bfloat16.  A blob qualifies if callers cannot see
+  // it, its producer can store bfloat16, and every step that reads it (as input
+  // or as fused residual) actually runs on bfloat16 operands.  A step does so
+  // only if it is able to and ALL its own inputs are bfloat16 blobs: a layer
+  // fed with fp32 data computes in TF32 on it rather than paying a conversion
+  // pass.  Start from the optimistic assignment and withdraw blobs until the
+  // rules hold everywhere (each round withdraws at least one, so it ends).
   {
     const int steps = static_cast<int>(plan.steps.size());
-    std::vector<bool> operands(steps, false);
-    for (int s = 0; s < steps; ++s) {
-      operands[s] = plan.half_storage && layers_[plan.steps[s].layer_id]->HalfStorageCapable();
-    }
-    for (int s = 0; s < steps; ++s) {
-      bool top_half = false;
-      const NetStep& step = plan.steps[s];
-      if (operands[s] && step.top_ids.size() == 1 && !plan.visible[step.top_ids[0]]) {
+    std::vector<char> half_blob(num_blobs, 0);
+    auto own_inputs = [&](const NetStep& st) { return static_cast<int>(st.bottoms.size()); };
+    if (plan.half_storage) {
+      for (int s = 0; s < steps; ++s) {
+        const NetStep& step = plan.steps[s];
+        if (step.top_ids.size() != 1 || plan.visible[step.top_ids[0]]) continue;
+        if (!layers_[step.layer_id]->HalfTopCapable()) continue;
         const int blob = step.top_ids[0];
         int readers = 0;
-        top_half = true;
-        for (int k = s + 1; k < steps && top_half; ++k) {
+        bool ok = true;
+        for (int k = s + 1; k < steps && ok; ++k) {
           const NetStep& later = plan.steps[k];
           const bool reads = std::find(later.bottom_ids.begin(), later.bottom_ids.end(), blob) != later.bottom_ids.end();
           const bool writes = std::find(later.top_ids.begin(), later.top_ids.end(), blob) != later.top_ids.end();
           if (reads) ++readers;
-          if ((reads && !operands[k]) || writes) top_half = false;
+          if (writes || (reads && !layers_[later.layer_id]->HalfOperandsCapable())) ok = false;
         }
-        if (readers == 0) top_half = false;
+        half_blob[blob] = ok && readers > 0;
       }
-      layers_[step.layer_id]->SetHalfStorage(operands[s], top_half);
+    }
+    auto runs_half = [&](int s) {
+      const NetStep& step = plan.steps[s];
+      Layer* layer = layers_[step.layer_id].get();
+      if (!layer->HalfOperandsCapable() || own_inputs(step) == 0) return false;
+      for (int i = 0; i < own_inputs(step); ++i) {
+        if (!half_blob[step.bottom_ids[i]]) return false;
+      }
+      if (layer->HalfNeedsBoth() && !(step.top_ids.size() == 1 && half_blob[step.top_ids[0]])) return false;
+      return true;
+    };
+    for (bool changed = plan.half_storage; changed;) {
+      changed = false;
+      for (int s = 0; s < steps; ++s) {
+        if (runs_half(s)) continue;
+        const NetStep& step = plan.steps[s];
+        for (int b : step.bottom_ids) {   // inputs and fused residual alike
+          if (half_blob[b]) {
+            half_blob[b] = 0;
+            changed = true;
+          }
+        }
+        if (layers_[step.layer_id]->HalfNeedsBoth() && step.top_ids.size() == 1 && half_blob[step.top_ids[0]]) {
+          half_blob[step.top_ids[0]] = 0;
+          changed = true;
+        }
+      }
+    }
+    for (int s = 0; s < steps; ++s) {
+      const NetStep& step = plan.steps[s];
+      layers_[step.layer_id]->SetHalfStorage(runs_half(s), step.top_ids.size() == 1 && half_blob[step.top_ids[0]] != 0);
     }
   }
 

@@ -227,15 +227,22 @@ def resnet50_flops_per_image():
     return sum(2 * cout * ho * ho * cin * k * k for _, cin, cout, k, _, _, ho, _ in resnet50_conv_table())
 
 
-def resnet50_conv_bytes(batch):
+def resnet50_conv_bytes(batch, bf16_storage=False):
     """Algorithmic bytes of the convolution / inner-product kernels of one forward pass:
-    4 * (input + output + weights + per-channel terms [+ residual input when fused]), each
-    tensor counted once per layer."""
+    element size * (input + output + weights [+ residual input when fused]) + 4 * per-channel
+    terms, each tensor counted once per layer.  Elements are 4 bytes; with the engine's bfloat16
+    storage the 48 convolutions between pool1 and pool5 read 2-byte activations, weights and
+    residuals and write 2-byte results, except the last one, which writes fp32 for the average
+    pool (conv1 and fc1000 stay fp32)."""
     total = 0
-    for _, cin, cout, k, _, hi, ho, res in resnet50_conv_table():
-        total += 4 * (batch * cin * hi * hi + batch * cout * ho * ho + cout * cin * k * k + cout)
+    table = resnet50_conv_table()
+    for i, (name, cin, cout, k, _, hi, ho, res) in enumerate(table):
+        narrow = bf16_storage and name not in ("conv1", "fc1000")
+        es_in = 2 if narrow else 4
+        es_out = 2 if (narrow and table[i + 1][0] != "fc1000") else 4
+        total += es_in * (batch * cin * hi * hi + cout * cin * k * k) + es_out * batch * cout * ho * ho + 4 * cout
         if res:
-            total += 4 * batch * cout * ho * ho
+            total += es_in * batch * cout * ho * ho
     return total
 
 

@@ -1,6 +1,7 @@
 """bfloat16 storage, the engine's precision opt-in (environment MINICAFFE_PRECISION=bf16, read when a
-net is constructed): tensor-core convolutions whose channel counts are multiples of eight take their
-operands as bfloat16, and blobs that only such layers read are stored as bfloat16.
+net is constructed): blobs that callers cannot see and that only tensor-core convolutions (channel
+counts multiples of eight) or 2x2 / 3x3 max pooling read are stored as bfloat16, and a convolution whose
+input is such a blob computes on bfloat16 operands.
 
 Stated bound for this mode, looser than the TF32 one: elementwise
 
@@ -48,9 +49,9 @@ def test_single_convolution(monkeypatch, capi, gpu_engine, reflib):
     wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, [out])
     want = run_net(capi, reflib, b, weights, x, [out])
     assert_close(wide[out], want[out], "tf32")
-    assert_close(narrow[out], want[out], "bf16", atol=BF16_ATOL, rtol=BF16_RTOL)
-    # the two modes really are different arithmetic
-    assert not np.array_equal(wide[out], narrow[out])
+    # A layer computes on bfloat16 only if its input is a bfloat16-stored blob; here both the input and
+    # the output are visible to the caller (fp32), so the mode changes nothing.
+    assert np.array_equal(wide[out], narrow[out])
 
 
 def test_resnet50_batch4(monkeypatch, capi, gpu_engine, reflib):
@@ -62,6 +63,7 @@ def test_resnet50_batch4(monkeypatch, capi, gpu_engine, reflib):
     marks = ["res2c", "res4f"]
     wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=marks)
     want = run_net(capi, reflib, b, weights, x, outs, marks=marks)
+    assert not np.array_equal(wide["res2c"], narrow["res2c"])      # the two modes really are different arithmetic
     for name in outs:
         st = assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
         tf = error_stats(wide[name], want[name])
@@ -121,3 +123,49 @@ def test_repeated_passes_and_new_input(monkeypatch, capi, gpu_engine):
     net.close()
     assert not np.array_equal(first, second)
     assert np.array_equal(first, again)
+
+
+def test_vgg_style_trunk_with_pooling(monkeypatch, capi, gpu_engine, reflib):
+    """Convolution groups separated by max pooling (2x2 stride 2, ceil-rounded odd sizes; 3x3 stride 1
+    pad 1): the pooled blobs stay bfloat16, a first layer with three input channels (row mode, fp32
+    image) writes bfloat16 directly, and an average pooling layer in between takes fp32."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("vgg_like")
+    b.input([("data", (2, 3, 37, 45))])
+    b.conv("c1_1", "data", "c1_1", 3, 32, 3, pad=1)
+    b.relu("r1_1", "c1_1")
+    b.conv("c1_2", "c1_1", "c1_2", 32, 32, 3, pad=1)
+    b.relu("r1_2", "c1_2")
+    b.raw("p1", "Pooling", ["c1_2"], ["p1"], "pooling_param { pool: MAX kernel_size: 2 stride: 2 }")
+    b.conv("c2_1", "p1", "c2_1", 32, 64, 3, pad=1)
+    b.relu("r2_1", "c2_1")
+    b.raw("p2", "Pooling", ["c2_1"], ["p2"], "pooling_param { pool: MAX kernel_size: 3 stride: 1 pad: 1 }")
+    b.conv("c3_1", "p2", "c3_1", 64, 64, 3, pad=2, dilation=2)
+    b.relu("r3_1", "c3_1")
+    b.raw("p3", "Pooling", ["c3_1"], ["p3"], "pooling_param { pool: AVE kernel_size: 2 stride: 2 }")
+    b.conv("c4_1", "p3", "c4_1", 64, 48, 1)
+    weights = wl.init_params(b.params, seed=31)
+    x = {"data": np.random.default_rng(32).standard_normal((2, 3, 37, 45)).astype(np.float32)}
+    for marks in ([], ["p1", "p2", "c3_1"]):
+        outs = ["c4_1"] + marks
+        wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=marks)
+        want = run_net(capi, reflib, b, weights, x, outs, marks=marks)
+        for name in outs:
+            assert_close(wide[name], want[name], "tf32 " + name)
+            assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
+        assert not np.array_equal(wide["c4_1"], narrow["c4_1"])
+
+
+def test_ssd300_heads(monkeypatch, capi, gpu_engine, reflib):
+    """SSD300 (VGG-16 trunk, dilated fc6, L2Norm, six multibox heads) at batch 1: box regressions and
+    class scores in front of DetectionOutput against the reference."""
+    wl = pkg("workloads")
+    b = wl.ssd300_vgg16(1, with_detection_output=False)
+    weights = wl.init_params(b.params, seed=2)
+    x = wl.ssd_input(1, seed=4)
+    outs = ["mbox_loc", "mbox_conf_flatten"]
+    wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=outs)
+    want = run_net(capi, reflib, b, weights, x, outs, marks=outs)
+    for name in outs:
+        assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
+        print(name, error_stats(narrow[name], want[name]), error_stats(wide[name], want[name]))
