@@ -84,12 +84,13 @@ struct ConvTcArgs {
   int row_segments;  // row mode: M tiles per output row of an image (ceil(output width / tile_rows))
   int a_bytes;       // bytes one activation tile load delivers
   int stages;        // depth of the operand ring (2 .. kMaxStages)
-  int slots;         // staging slots per epilogue warp: 1 or 2; 2 or 3 when a residual is added
+  int slots;         // staging slots per epilogue warp: 1 or 2; 2 .. kMaxSlots when a residual is added
+  int res_depth;     // residual sub-tiles a warp requests ahead of the one it works on (1 .. slots - 1)
   int out_half;      // the output is stored as bfloat16 (else fp32), whatever the operands are
 };
 
 constexpr int kMaxStages = 8;
-constexpr int kMaxSlots = 3;
+constexpr int kMaxSlots = 8;
 constexpr int kSharedLimit = 232448;   // 227 KiB: the most one CTA can have on sm_100
 
 // Shared memory of one persistent CTA = operand ring (`stages` x (A tile + B
@@ -114,6 +115,12 @@ struct SmemPlan {
   static constexpr int dynamic_bytes(int stages, int slots) {
     return stages * kStageBytes + staging_bytes(slots) + 1024;   // + alignment slack
   }
+};
+
+// Compile-time tag for the activation of the fused tail (0 none, 1 ReLU, 2 per-column negative slope).
+template <int kAct>
+struct ActTag {
+  static constexpr int value = kAct;
 };
 
 // Ring position of a k-iteration: stage index and the parity of its use.
@@ -463,13 +470,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Chunk sequence of this warp: for each of its CTA's tiles, the 32-column
     // chunks it owns that exist (the last n-tile may have fewer), left to right.
     // `seq` numbers them.  With a residual the warp cycles through its staging
-    // slots, and a cursor of lane 0 walks the same sequence one chunk ahead of
-    // the computation: it copies the next chunk's residual sub-tile into the
-    // slot that comes free next (with three slots the store that last read it,
-    // two chunks back, has had a whole chunk's time to finish; with two slots it
-    // is the previous chunk's store).  Asking L2 for the residual further ahead
-    // (cp.async.bulk.prefetch) was tried and removed: the lines were evicted by
-    // the output stream before use and DRAM reads grew by half.
+    // slots, and a cursor of lane 0 walks the same sequence a few chunks ahead of
+    // the computation (args.res_depth): it copies a coming chunk's residual
+    // sub-tile into the slot that comes free next.  Asking L2 for the residual
+    // further ahead instead (cp.async.bulk.prefetch) was tried and removed: the
+    // lines were evicted by the output stream before use and DRAM reads grew by
+    // half.
     struct ChunkCursor {
       int local;   // how many of this CTA's tiles lie behind the cursor
       int chunk;   // next chunk of the current tile
@@ -514,7 +520,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     };
     const bool staged = args.tma_epilogue != 0;
-    if (staged && has_res && lane == 0) issue_residual();
+    // Residual sub-tiles are requested `res_depth` chunks ahead: a request takes
+    // a DRAM round trip (one to two microseconds), several times the time a warp
+    // needs per chunk.  Requesting chunk g + depth reuses the slot of chunk
+    // g + depth - slots, so at most slots - depth - 1 of the latest stores may
+    // still be reading shared memory at that point.
+    const int res_depth = args.res_depth;
+    const int stores_in_flight = slots - res_depth - 1;
+    if (staged && has_res && lane == 0) {
+      for (int d = 0; d < res_depth; ++d) issue_residual();
+    }
 
     int seq = 0;
     int local = 0;
@@ -564,8 +579,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const float4* sc4 = reinterpret_cast<const float4*>(t_scale + chunk * 32);
         const float4* sh4 = reinterpret_cast<const float4*>(t_shift + chunk * 32);
         const float4* sl4 = reinterpret_cast<const float4*>(t_slope + chunk * 32);
-        // v = acc * scale + shift (+ coeff * residual), then the activation.
-        auto finish4 = [&](int j, float4 r, bool add_res) {
+        // v = acc * scale + shift (+ coeff * residual), then the activation.  The
+        // activation is a compile-time tag: with a run-time test inside, every
+        // group of four values became its own chain of small basic blocks (load,
+        // multiply-add, branch, ...), each exposing its latencies, and a sub-tile
+        // took over a thousand cycles; as straight-line code the 32 chains of a
+        // row overlap.
+        auto finish4 = [&](auto act_tag, int j, float4 r, bool add_res) {
+          constexpr int kAct = decltype(act_tag)::value;
           const float4 sc = sc4[j], sh = sh4[j];
           float4 v;
           v.x = fmaf(__uint_as_float(acc[j * 4 + 0]), sc.x, sh.x);
@@ -578,37 +599,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             v.z = fmaf(ep.residual_coeff, r.z, v.z);
             v.w = fmaf(ep.residual_coeff, r.w, v.w);
           }
-          if (act_mode == 1) {
+          if (kAct == 1) {
             v.x = fmaxf(v.x, 0.f);
             v.y = fmaxf(v.y, 0.f);
             v.z = fmaxf(v.z, 0.f);
             v.w = fmaxf(v.w, 0.f);
-          } else if (act_mode == 2) {
+          } else if (kAct == 2) {
             const float4 sl = sl4[j];
             v.x = v.x > 0.f ? v.x : v.x * sl.x;
             v.y = v.y > 0.f ? v.y : v.y * sl.y;
             v.z = v.z > 0.f ? v.z : v.z * sl.z;
             v.w = v.w > 0.f ? v.w : v.w * sl.w;
           }
-          if (ep.round_tf32) {
-            v.x = round_to_tf32(v.x);
-            v.y = round_to_tf32(v.y);
-            v.z = round_to_tf32(v.z);
-            v.w = round_to_tf32(v.w);
-          }
           return v;
+        };
+        auto round4 = [&](float4& v) {
+          v.x = round_to_tf32(v.x);
+          v.y = round_to_tf32(v.y);
+          v.z = round_to_tf32(v.z);
+          v.w = round_to_tf32(v.w);
         };
         if (staged) {
           const int slot = has_res ? cur_slot : (slots == 2 ? (g & 1) : 0);
           float* buf = slot_ptr(slot) + lane * 32;
           if (has_res) {
             if (lane == 0) {
-              // The next chunk's residual goes into the slot that comes free
-              // next; with three slots the latest store may still be reading.
-              if (slots == 3) {
-                tma_store_wait_read<1>();
-              } else {
-                tma_store_wait_read<0>();
+              switch (stores_in_flight) {
+                case 0: tma_store_wait_read<0>(); break;
+                case 1: tma_store_wait_read<1>(); break;
+                case 2: tma_store_wait_read<2>(); break;
+                default: tma_store_wait_read<3>(); break;
               }
               issue_residual();
             }
@@ -644,26 +664,40 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // position q ^ ((row >> 1) & 3) (the 64-byte swizzle).
           uint8_t* hrow = reinterpret_cast<uint8_t*>(slot_ptr(slot)) + lane * 64;
           const int hswz = (lane >> 1) & 3;
-          if (!has_res) {
+          auto fill = [&](auto act_tag) {
+            if (!has_res) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = finish4(j, make_float4(0.f, 0.f, 0.f, 0.f), false);
-          } else if (kHalf) {
-            uint4 w[4];
+              for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+            } else if (kHalf) {
+              uint4 w[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const uint4*>(hrow + ((q ^ hswz) << 4));
+              for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const uint4*>(hrow + ((q ^ hswz) << 4));
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              v[2 * q] = finish4(2 * q, make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)),
-                                 true);
-              v[2 * q + 1] = finish4(2 * q + 1,
-                                     make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
-                                     true);
+              for (int q = 0; q < 4; ++q) {
+                v[2 * q] = finish4(act_tag, 2 * q,
+                                   make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)), true);
+                v[2 * q + 1] = finish4(act_tag, 2 * q + 1,
+                                       make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
+                                       true);
+              }
+            } else {
+              float4 r[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) r[j] = *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2));
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, r[j], true);
             }
+          };
+          if (act_mode == 1) {
+            fill(ActTag<1>());
+          } else if (act_mode == 0) {
+            fill(ActTag<0>());
           } else {
+            fill(ActTag<2>());
+          }
+          if (ep.round_tf32) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              v[j] = finish4(j, *reinterpret_cast<const float4*>(buf + ((j ^ swz) << 2)), true);
-            }
+            for (int j = 0; j < 8; ++j) round4(v[j]);
           }
           // Residual and result rows of different widths overlap other lanes' rows.
           if (has_res && (args.out_half != 0) != kHalf) __syncwarp();
@@ -722,7 +756,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (c + 2 < args.cout) r.z = residual_at(c + 2);
                 if (c + 3 < args.cout) r.w = residual_at(c + 3);
               }
-              const float4 v = finish4(j, r, has_res);
+              float4 v = act_mode == 1   ? finish4(ActTag<1>(), j, r, has_res)
+                         : act_mode == 0 ? finish4(ActTag<0>(), j, r, has_res)
+                                         : finish4(ActTag<2>(), j, r, has_res);
+              if (ep.round_tf32) round4(v);
               store_at(c, v.x);
               if (c + 1 < args.cout) store_at(c + 1, v.y);
               if (c + 2 < args.cout) store_at(c + 2, v.z);
@@ -965,6 +1002,14 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   // that no next main loop covers it); otherwise one, and a deeper ring.
   args.slots = args.ep.residual != nullptr ? (args.k_iters <= 4 ? 3 : 2)
                                            : ((args.k_iters < 16 || tiles <= workers_max) ? 2 : 1);
+  args.res_depth = 1;
+  if (args.ep.residual != nullptr) {
+    const char* force_slots = getenv("MCB200_RES_SLOTS");   // experiments: "2" .. "8"
+    const char* force_depth = getenv("MCB200_RES_DEPTH");   // experiments: "1" .. slots - 1
+    if (force_slots && atoi(force_slots) >= 2 && atoi(force_slots) <= kMaxSlots) args.slots = atoi(force_slots);
+    if (force_depth && atoi(force_depth) >= 1) args.res_depth = atoi(force_depth);
+    if (args.res_depth > args.slots - 1) args.res_depth = args.slots - 1;
+  }
   int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots)) / Plan::kStageBytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
