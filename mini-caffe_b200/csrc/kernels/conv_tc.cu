@@ -534,6 +534,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int seq = 0;
     int local = 0;
     bool alive = true;
+    int table_n0[2] = {-1, -1};          // first column the per-column tables were filled for
+    uint32_t table_fills[2] = {0u, 0u};
     for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
       const int ab = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
@@ -543,30 +545,37 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // First output row (pixel) of this warp's 32-row slice, and how many of the 32 exist.
       const int row0 = (kMode == kModeRows ? row_of(mt) * args.wo + seg_start(mt) : mt * kBlockM) + quad * 32;
       const int rows_here = kMode == kModeRows ? min(args.tile_rows, args.wo - seg_start(mt)) - quad * 32 : args.m - row0;
-      // Per-column constants of this tile go to shared memory once, so that the
-      // inner loops are a broadcast 16-byte load and fused multiply-adds.  Two
-      // copies (tile parity): a warp may still be reading the previous tile's.
-      float* t_scale = col_scale[ab];
-      float* t_shift = col_shift[ab];
-      float* t_slope = col_slope[ab];
-      for (int c = epi_tid; c < BN; c += kEpilogueWarps * 32) {
-        const int cc = n0 + c;
-        const bool in = cc < args.cout;
-        t_scale[c] = (in && ep.scale) ? __ldg(ep.scale + cc) : 1.f;
-        t_shift[c] = (in && ep.shift) ? __ldg(ep.shift + cc) : 0.f;
-        t_slope[c] = ep.act == 2 ? ((in && ep.prelu) ? __ldg(ep.prelu + (ep.prelu_shared ? 0 : cc)) : 0.f) : ep.slope;
-      }
-      // Rendezvous of the epilogue warps on the table (an mbarrier rather than a
-      // named barrier, so that the wait is bounded like every other one).
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&col_bar[ab]);
-      alive = __all_sync(0xffffffffu, mbar_wait_bounded(&col_bar[ab], use, abort, kWaitLimitCycles));
-      if (!alive) break;
-
       // tcgen05.ld is warp-collective: the whole warp takes the same branch.
       alive = __all_sync(0xffffffffu, mbar_wait_bounded(&tmem_full_bar[ab], use, abort, kWaitLimitCycles));
       if (!alive) break;
       tc_fence_after_sync();
+      // Per-column constants of the tile's columns go to shared memory, so that the
+      // inner loops are a broadcast 16-byte load and fused multiply-adds.  Two
+      // copies (tile parity), each kept while the CTA's tiles of that parity stay
+      // in the same column range (always, when the layer has one N tile or the
+      // grid is a multiple of the N tiles).  A copy may be overwritten here: the
+      // accumulator of this parity is full again, so every warp has finished
+      // the tile that last used the copy.
+      float* t_scale = col_scale[ab];
+      float* t_shift = col_shift[ab];
+      float* t_slope = col_slope[ab];
+      if (table_n0[ab] != n0) {
+        for (int c = epi_tid; c < BN; c += kEpilogueWarps * 32) {
+          const int cc = n0 + c;
+          const bool in = cc < args.cout;
+          t_scale[c] = (in && ep.scale) ? __ldg(ep.scale + cc) : 1.f;
+          t_shift[c] = (in && ep.shift) ? __ldg(ep.shift + cc) : 0.f;
+          t_slope[c] = ep.act == 2 ? ((in && ep.prelu) ? __ldg(ep.prelu + (ep.prelu_shared ? 0 : cc)) : 0.f) : ep.slope;
+        }
+        // Rendezvous of the epilogue warps on the table (an mbarrier rather than a
+        // named barrier, so that the wait is bounded like every other one).
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&col_bar[ab]);
+        alive = __all_sync(0xffffffffu, mbar_wait_bounded(&col_bar[ab], table_fills[ab] & 1u, abort, kWaitLimitCycles));
+        if (!alive) break;
+        ++table_fills[ab];
+        table_n0[ab] = n0;
+      }
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN) + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
       for (int chunk = half; chunk < chunks_full; chunk += 2) {
