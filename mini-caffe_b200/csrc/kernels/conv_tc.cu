@@ -94,7 +94,8 @@ constexpr int kMaxSlots = 8;
 constexpr int kSharedLimit = 232448;   // 227 KiB: the most one CTA can have on sm_100
 
 // Shared memory of one persistent CTA = operand ring (`stages` x (A tile + B
-// tile)) + epilogue staging (`slots` x 4 KiB for each of the eight warps).  The
+// tile)) + epilogue staging (`slots` x 4 KiB for each of the eight warps; 2 KiB
+// when residual and result are both bfloat16).  The
 // copies in flight are what hides the round trip of a stage (L2 -> shared
 // memory, barrier hop, MMA completion, barrier hop: about a microsecond), so
 // the ring takes every byte the epilogue can spare: launches that add a
@@ -111,9 +112,9 @@ struct SmemPlan {
   static constexpr int kSub = (kMode != kModeRows && kTileABytes + kTileBBytes <= 24 * 1024) ? 2 : 1;
   static constexpr int kStageBytes = kSub * (kTileABytes + kTileBBytes);
   static constexpr int kStageBOffset = kSub * kTileABytes;   // [A sub-tiles][B sub-tiles]
-  static constexpr int staging_bytes(int slots) { return kEpilogueWarps * slots * 4096; }
-  static constexpr int dynamic_bytes(int stages, int slots) {
-    return stages * kStageBytes + staging_bytes(slots) + 1024;   // + alignment slack
+  static constexpr int staging_bytes(int slots, int slot_bytes) { return kEpilogueWarps * slots * slot_bytes; }
+  static constexpr int dynamic_bytes(int stages, int slots, int slot_bytes) {
+    return stages * kStageBytes + staging_bytes(slots, slot_bytes) + 1024;   // + alignment slack
   }
 };
 
@@ -460,8 +461,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int half = ew >> 2;                   // chunks half, half + 2, ... of every tile
     const mcb200_epilogue& ep = args.ep;
     const bool has_res = ep.residual != nullptr;
-    uint8_t* staging = staging_base + ew * (slots * 4096);
-    auto slot_ptr = [&](int slot) { return reinterpret_cast<float*>(staging + slot * 4096); };
+    // A slot holds a 32 x 32 sub-tile: 4 KiB, or 2 KiB when residual and result are both bfloat16.
+    const int slot_bytes = (kHalf && args.out_half) ? 2048 : 4096;
+    uint8_t* staging = staging_base + ew * (slots * slot_bytes);
+    auto slot_ptr = [&](int slot) { return reinterpret_cast<float*>(staging + slot * slot_bytes); };
     const int chunks_full = BN / 32;
     const int epi_tid = threadIdx.x - kFirstEpilogueWarp * 32;   // 0..255 over the epilogue warps
     // 0: no activation, 1: plain ReLU, 2: per-column negative slope (leaky ReLU / PReLU)
@@ -1009,8 +1012,9 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   // chunks overlap), else two.  Without: two when the epilogue is the busy
   // or the exposed part (few k-iterations per tile, or a single tile per CTA so
   // that no next main loop covers it); otherwise one, and a deeper ring.
-  args.slots = args.ep.residual != nullptr ? (args.k_iters <= 4 ? 3 : 2)
-                                           : ((args.k_iters < 16 || tiles <= workers_max) ? 2 : 1);
+  const int k_units = args.k_iters * (kHalf ? 2 : 1);   // in 32-channel steps, the unit the rules were measured in
+  args.slots = args.ep.residual != nullptr ? (k_units <= 4 ? 3 : 2)
+                                           : ((k_units < 16 || tiles <= workers_max) ? 2 : 1);
   args.res_depth = 1;
   if (args.ep.residual != nullptr) {
     const char* force_slots = getenv("MCB200_RES_SLOTS");   // experiments: "2" .. "8"
@@ -1019,11 +1023,12 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     if (force_depth && atoi(force_depth) >= 1) args.res_depth = atoi(force_depth);
     if (args.res_depth > args.slots - 1) args.res_depth = args.slots - 1;
   }
-  int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots)) / Plan::kStageBytes;
+  const int slot_bytes = (kHalf && args.out_half) ? 2048 : 4096;
+  int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots, slot_bytes)) / Plan::kStageBytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   args.stages = stages;
-  const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots);
+  const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots, slot_bytes);
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
   const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);
@@ -1162,7 +1167,8 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   plan->c_blocks = (s->c + kelems - 1) / kelems;
   plan->k_iters = s->kh * s->kw * plan->c_blocks;
   plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
-  plan->cta_pair = pick_cta_pair(plan->block_n, plan->m, plan->k_iters);
+  // The pairing rule was measured in 32-channel k-iterations; a bfloat16 k-iteration covers 64.
+  plan->cta_pair = pick_cta_pair(plan->block_n, plan->m, plan->k_iters * (half ? 2 : 1));
   const bool pointwise = s->kh == 1 && s->kw == 1 && s->stride_h == 1 && s->stride_w == 1 && s->pad_h == 0 &&
                          s->pad_w == 0;
   plan->im2col = pointwise ? 0 : 1;
