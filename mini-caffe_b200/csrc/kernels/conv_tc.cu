@@ -90,7 +90,7 @@ struct ConvTcArgs {
 };
 
 constexpr int kMaxStages = 8;
-constexpr int kMaxSlots = 8;
+constexpr int kMaxSlots = 4;     // every barrier here is static shared memory that the operand ring cannot use
 constexpr int kSharedLimit = 232448;   // 227 KiB: the most one CTA can have on sm_100
 
 // Shared memory of one persistent CTA = operand ring (`stages` x (A tile + B
