@@ -45,7 +45,7 @@ E2E_THREADS = 2        # host threads per GPU in the end-to-end leg, each with i
 # DRAM bytes per convolution launch (read + write, averaged over the 54 launches of one pass at
 # batch 64) from one ncu capture of this workload: 3589 MB read + 1139 MB written per pass.  Below
 # the algorithmic 126 MB per launch because small activations stay in L2 between layers.
-CONV_DRAM_BYTES_PER_LAUNCH = 87.56e6
+CONV_DRAM_BYTES_PER_LAUNCH = 87.61e6
 METRIC = "resnet50_images_per_sec"
 UNIT = "images/s"
 
