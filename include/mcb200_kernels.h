@@ -159,6 +159,13 @@ int mcb200_conv_direct(const mcb200_conv_shape* s, const float* in, const float*
 int mcb200_dw_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed, void* stream);
 int mcb200_conv_depthwise(const mcb200_conv_shape* s, const float* in, const float* packed_w, float* out,
                           const mcb200_epilogue* ep, void* stream);
+/* The 3x3 (dilation 1, stride 1 or 2) case with bfloat16 activations on either
+ * side, for nets that store their activations as bfloat16: `in` / `out` hold
+ * bfloat16 cells when the matching flag is set, fp32 otherwise; weights and
+ * arithmetic are fp32.  No fused residual.                                    */
+int mcb200_conv_depthwise_bf16_supported(const mcb200_conv_shape* s);
+int mcb200_conv_depthwise_bf16(const mcb200_conv_shape* s, const void* in, int in_is_bf16, const float* packed_w,
+                               void* out, int out_is_bf16, const mcb200_epilogue* ep, void* stream);
 
 /* ------------------------------------------------------------------ layout */
 /* (N,C,H,W) -> (N,H,W,c_stride) with channels c..c_stride-1 zero-filled, and back. */

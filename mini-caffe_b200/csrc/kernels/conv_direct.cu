@@ -84,10 +84,30 @@ __global__ void depthwise_vec4_kernel(const float* __restrict__ in, const float*
 // per output instead of 9), the nine weight vectors sit in registers, and the
 // index arithmetic is 32-bit.  Consecutive threads take consecutive channel
 // groups, so a warp's loads are contiguous runs of the channels-last rows.
-template <int STRIDE>
+//
+// IN_HALF / OUT_HALF: the activations are read / the result is stored as
+// bfloat16 (four channels = one 8-byte access), for nets with bfloat16
+// storage; weights and arithmetic stay fp32.
+__device__ __forceinline__ float4 load4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4_bf16(const uint16_t* p) {
+  const uint2 w = __ldg(reinterpret_cast<const uint2*>(p));
+  return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xFFFF0000u), __uint_as_float(w.y << 16),
+                     __uint_as_float(w.y & 0xFFFF0000u));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <int STRIDE, bool IN_HALF, bool OUT_HALF>
 __global__ void __launch_bounds__(256)
-depthwise3x3_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
+depthwise3x3_kernel(const void* __restrict__ in_any, const float* __restrict__ w, void* __restrict__ out_any,
                     mcb200_conv_shape s, mcb200_epilogue ep) {
+  const float* in = static_cast<const float*>(in_any);
+  const uint16_t* in16 = static_cast<const uint16_t*>(in_any);
+  float* out = static_cast<float*>(out_any);
+  uint16_t* out16 = static_cast<uint16_t*>(out_any);
   constexpr int kOut = 4;                      // output pixels per thread
   constexpr int kCols = kOut * STRIDE + 2;     // input columns they need (3 x 3 window)
   const unsigned cg = s.c >> 2;
@@ -109,17 +129,18 @@ depthwise3x3_kernel(const float* __restrict__ in, const float* __restrict__ w, f
     float4 acc[kOut];
 #pragma unroll
     for (int o = 0; o < kOut; ++o) acc[o] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float* image = in + static_cast<size_t>(n) * s.h * s.w * s.c_stride + g * 4;
+    const size_t image = static_cast<size_t>(n) * s.h * s.w * s.c_stride + g * 4;   // element offset
 #pragma unroll
     for (int r = 0; r < 3; ++r) {
       const int y = y0 + r;
       if (y < 0 || y >= s.h) continue;
-      const float* row = image + static_cast<size_t>(y) * s.w * s.c_stride;
+      const size_t row = image + static_cast<size_t>(y) * s.w * s.c_stride;
       float4 v[kCols];
 #pragma unroll
       for (int c = 0; c < kCols; ++c) {
         const int x = x0 + c;
-        v[c] = (x >= 0 && x < s.w) ? __ldg(reinterpret_cast<const float4*>(row + static_cast<size_t>(x) * s.c_stride))
+        const size_t at = row + static_cast<size_t>(x) * s.c_stride;
+        v[c] = (x >= 0 && x < s.w) ? (IN_HALF ? load4_bf16(in16 + at) : load4(in + at))
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
@@ -147,7 +168,11 @@ depthwise3x3_kernel(const float* __restrict__ in, const float* __restrict__ w, f
       r4.y = tail(acc[o].y, c0 + 1, ep, res);
       r4.z = tail(acc[o].z, c0 + 2, ep, res);
       r4.w = tail(acc[o].w, c0 + 3, ep, res);
-      *reinterpret_cast<float4*>(out + pixel * s.c + c0) = r4;
+      if (OUT_HALF) {
+        *reinterpret_cast<uint2*>(out16 + pixel * s.c + c0) = make_uint2(pack2_bf16(r4.x, r4.y), pack2_bf16(r4.z, r4.w));
+      } else {
+        *reinterpret_cast<float4*>(out + pixel * s.c + c0) = r4;
+      }
     }
   }
 }
@@ -232,14 +257,55 @@ extern "C" int mcb200_conv_depthwise(const mcb200_conv_shape* s, const float* in
     const long long threads = static_cast<long long>(shape.n) * shape.ho * ((shape.wo + 3) / 4) * (shape.c / 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (shape.stride_h == 1) {
-      depthwise3x3_kernel<1><<<grid_for(threads, 256), 256, 0, st>>>(in, packed_w, out, shape, e);
+      depthwise3x3_kernel<1, false, false><<<grid_for(threads, 256), 256, 0, st>>>(in, packed_w, out, shape, e);
     } else {
-      depthwise3x3_kernel<2><<<grid_for(threads, 256), 256, 0, st>>>(in, packed_w, out, shape, e);
+      depthwise3x3_kernel<2, false, false><<<grid_for(threads, 256), 256, 0, st>>>(in, packed_w, out, shape, e);
     }
   } else {
     depthwise_vec4_kernel<<<grid_for(items, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, packed_w, out,
                                                                                               shape, e);
   }
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_conv_depthwise_bf16_supported(const mcb200_conv_shape* s) {
+  if (!s || s->group != s->c || s->cout != s->c || (s->c & 3) || (s->c_stride & 3)) return 0;
+  return (s->kh == 3 && s->kw == 3 && s->dil_h == 1 && s->dil_w == 1 && s->stride_h == s->stride_w &&
+          (s->stride_h == 1 || s->stride_h == 2))
+             ? 1
+             : 0;
+}
+
+extern "C" int mcb200_conv_depthwise_bf16(const mcb200_conv_shape* s, const void* in, int in_is_bf16,
+                                          const float* packed_w, void* out, int out_is_bf16,
+                                          const mcb200_epilogue* ep, void* stream) {
+  if (!s || !in || !packed_w || !out) return -1;
+  if (!mcb200_conv_depthwise_bf16_supported(s)) return -2;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(packed_w)) & 15)
+    return -3;
+  mcb200_conv_shape shape = *s;
+  if (mcb200_conv_out_shape(&shape) != 0) return -4;
+  const mcb200_epilogue e = ep ? *ep : default_epilogue();
+  if (e.act == 2 && !e.prelu) return -5;
+  if (e.residual) return -6;   // the fused residual of this kernel is fp32 only
+  const long long threads = static_cast<long long>(shape.n) * shape.ho * ((shape.wo + 3) / 4) * (shape.c / 4);
+  if (threads == 0) return 0;
+  if (threads >= 0x7fffffffLL) return -7;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(threads, 256);
+  const bool ih = in_is_bf16 != 0, oh = out_is_bf16 != 0;
+#define MCB200_DW(STRIDE)                                                                                        \
+  if (ih && oh) depthwise3x3_kernel<STRIDE, true, true><<<grid, 256, 0, st>>>(in, packed_w, out, shape, e);       \
+  else if (ih) depthwise3x3_kernel<STRIDE, true, false><<<grid, 256, 0, st>>>(in, packed_w, out, shape, e);       \
+  else if (oh) depthwise3x3_kernel<STRIDE, false, true><<<grid, 256, 0, st>>>(in, packed_w, out, shape, e);       \
+  else depthwise3x3_kernel<STRIDE, false, false><<<grid, 256, 0, st>>>(in, packed_w, out, shape, e)
+  if (shape.stride_h == 1) {
+    MCB200_DW(1);
+  } else {
+    MCB200_DW(2);
+  }
+#undef MCB200_DW
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -69,19 +69,44 @@ __device__ unsigned long long block_kth_smallest(Fetch fetch, int n, int k, int*
       }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int cum = 0, bin = 0;
-      for (; bin < 255; ++bin) {
-        if (cum + hist[bin] >= remaining) break;
-        cum += hist[bin];
+    if (threadIdx.x < 32) {
+      // Warp 0 finds the bin that holds the `remaining`-th key: lane l sums bins
+      // 8 l .. 8 l + 7, a shuffle scan gives the keys in front of each lane's
+      // range, the lane whose range contains the key walks its eight bins.
+      int own[8];
+      int sum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        own[j] = hist[lane * 8 + j];
+        sum += own[j];
       }
-      const unsigned long long next = prefix | (static_cast<unsigned long long>(bin) << shift);
-      if (cum + hist[bin] == remaining) {   // the whole bin is wanted: done
-        bcast[0] = next | ((1ull << shift) - 1ull);
-        bcast[1] = 0ull;
-      } else {
-        bcast[0] = next;
-        bcast[1] = static_cast<unsigned long long>(remaining - cum);
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const int excl = incl - sum;
+      const bool mine = excl < remaining && remaining <= incl;
+      const unsigned who = __ballot_sync(0xffffffffu, mine);
+      // Fewer keys than asked for: the walk ends in the last bin, as a serial scan would.
+      const int chosen = who ? __ffs(who) - 1 : 31;
+      if (lane == chosen) {
+        int cum = excl, bin = lane * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          bin = lane * 8 + j;
+          if (bin == 255 || cum + own[j] >= remaining) break;
+          cum += own[j];
+        }
+        const unsigned long long next = prefix | (static_cast<unsigned long long>(bin) << shift);
+        if (cum + hist[bin] == remaining) {   // the whole bin is wanted: done
+          bcast[0] = next | ((1ull << shift) - 1ull);
+          bcast[1] = 0ull;
+        } else {
+          bcast[0] = next;
+          bcast[1] = static_cast<unsigned long long>(remaining - cum);
+        }
       }
     }
     __syncthreads();

@@ -191,9 +191,26 @@ detout_class_kernel(const float* __restrict__ loc, const float* __restrict__ con
   }
   __syncthreads();
   const float* scores = conf + static_cast<size_t>(image) * p.num_priors * p.num_classes + cls;
-  for (int i = threadIdx.x; i < p.num_priors; i += blockDim.x) {
-    const float s = scores[static_cast<size_t>(i) * p.num_classes];
-    if (s > p.confidence_threshold) cand[atomicAdd(&num_cand, 1)] = make_key(s, static_cast<uint32_t>(i));
+  // Append the passing priors, one shared-memory counter update per warp (with
+  // near-uniform scores nearly every prior passes, and 8732 single updates of
+  // one counter would serialise).  The order of the list does not matter.
+  for (int base = 0; base < p.num_priors; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    float s = 0.f;
+    bool pass = false;
+    if (i < p.num_priors) {
+      s = scores[static_cast<size_t>(i) * p.num_classes];
+      pass = s > p.confidence_threshold;
+    }
+    const unsigned passing = __ballot_sync(0xffffffffu, pass);
+    if (passing) {
+      const int lane = threadIdx.x & 31;
+      const int leader = __ffs(passing) - 1;
+      int first = 0;
+      if (lane == leader) first = atomicAdd(&num_cand, __popc(passing));
+      first = __shfl_sync(0xffffffffu, first, leader);
+      if (pass) cand[first + __popc(passing & ((1u << lane) - 1u))] = make_key(s, static_cast<uint32_t>(i));
+    }
   }
   __syncthreads();
   const int m = num_cand;
@@ -309,8 +326,12 @@ detout_class_kernel(const float* __restrict__ loc, const float* __restrict__ con
 
 // ---------------------------------------------------------------- B. per image
 
+// `staged`: the keys of all of the image's detections fit into dynamic shared
+// memory and are gathered there once (all of a thread's loads in flight
+// together); the passes of the radix select then read shared memory.
 __global__ void __launch_bounds__(256)
-detout_image_kernel(mcb200_detout_params p, Workspace ws) {
+detout_image_kernel(mcb200_detout_params p, Workspace ws, int staged) {
+  extern __shared__ unsigned long long image_keys[];
   __shared__ int hist[256];
   __shared__ unsigned long long bcast[2];
   __shared__ int offsets[1025];   // first row of each class among the image's rows
@@ -331,17 +352,21 @@ detout_image_kernel(mcb200_detout_params p, Workspace ws) {
   }
   __syncthreads();
   const int total = offsets[classes];
-  // Flat index e over (class, rank); key = (descending score, e).
-  auto fetch = [&](int e) {
+  // Flat index e over (class, rank); key = (descending score, class * limit + rank).
+  auto load_key = [&](int e) {
     int c = 0;
     while (offsets[c + 1] <= e) ++c;
     const int j = e - offsets[c];
     return make_key(entries[static_cast<size_t>(c) * limit + j].score, static_cast<uint32_t>(c * limit + j));
   };
-  unsigned long long threshold = kPadKey;
-  if (p.keep_top_k > -1 && total > p.keep_top_k) {
-    threshold = block_kth_smallest(fetch, total, p.keep_top_k, hist, bcast);
+  const bool select = p.keep_top_k > -1 && total > p.keep_top_k;
+  if (staged && select) {
+    for (int e = threadIdx.x; e < total; e += blockDim.x) image_keys[e] = load_key(e);
+    __syncthreads();
   }
+  auto fetch = [&](int e) { return staged ? image_keys[e] : load_key(e); };
+  unsigned long long threshold = kPadKey;
+  if (select) threshold = block_kth_smallest(fetch, total, p.keep_top_k, hist, bcast);
   // Within a class the entries are in descending score order, so the kept ones
   // are a prefix of it; its length is the number of the class's keys <= threshold.
   for (int c = threadIdx.x; c < classes; c += blockDim.x) selected[c] = 0;
@@ -349,9 +374,8 @@ detout_image_kernel(mcb200_detout_params p, Workspace ws) {
   for (int e = threadIdx.x; e < total; e += blockDim.x) {
     int c = 0;
     while (offsets[c + 1] <= e) ++c;
-    const int j = e - offsets[c];
-    if (make_key(entries[static_cast<size_t>(c) * limit + j].score, static_cast<uint32_t>(c * limit + j)) <= threshold)
-      atomicAdd(&selected[c], 1);
+    // Without a selection every detection is kept (the threshold is the largest key).
+    if (!select || fetch(e) <= threshold) atomicAdd(&selected[c], 1);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -468,7 +492,22 @@ extern "C" int mcb200_detout_forward(const mcb200_detout_params* p, int batch, c
   }
   detout_class_kernel<<<dim3(p->num_classes, batch), 256, smem, st>>>(loc, conf, prior, *p, ws, padded, p->eta);
   count_launch();
-  detout_image_kernel<<<batch, 256, 0, st>>>(*p, ws);
+  {
+    // Keys of one image: at most (classes x per-class limit) of 8 bytes.
+    const size_t key_bytes = static_cast<size_t>(p->num_classes) * ws.per_class * 8;
+    const size_t kImageSharedLimit = 200 * 1024;
+    const int staged = key_bytes <= kImageSharedLimit ? 1 : 0;
+    static size_t configured_image[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (staged && dev >= 0 && dev < 64 && configured_image[dev] < key_bytes) {
+      cudaError_t e = cudaFuncSetAttribute(detout_image_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(kImageSharedLimit));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured_image[dev] = kImageSharedLimit;
+    }
+    detout_image_kernel<<<batch, 256, staged ? key_bytes : 0, st>>>(*p, ws, staged);
+  }
   count_launch();
   detout_compact_kernel<<<batch, 256, 0, st>>>(ws, batch, out, total);
   count_launch();

@@ -129,25 +129,36 @@ __global__ void proposal_decode_kernel(const float* __restrict__ score_maps, con
 
 // ---------------------------------------------------------------- 2. top-k + sort
 
+// One block per image.  The score halves of the keys (the index half of key i
+// is i itself) are copied to shared memory once, with all loads of a thread in
+// flight together; the passes of the radix select, which test one key after the
+// other with a warp vote in between, and the compaction then run out of shared
+// memory instead of paying an L2 round trip per key and pass.  `staged` = 0 (the
+// keys do not fit beside the sort buffer): they are read from global memory.
 __global__ void __launch_bounds__(1024, 1)
-proposal_topk_sort_kernel(Workspace ws, int padded) {
-  extern __shared__ unsigned long long sorted[];   // `padded` keys
+proposal_topk_sort_kernel(Workspace ws, int padded, int staged) {
+  extern __shared__ unsigned long long sorted[];   // `padded` keys, then (staged) n 32-bit score keys
   __shared__ int hist[256];
   __shared__ unsigned long long bcast[2];
   __shared__ int fill;
   const int image = blockIdx.x;
   const unsigned long long* keys = ws.keys + static_cast<size_t>(image) * ws.n;
   const int n = ws.n, k = ws.k;
-
-  unsigned long long threshold = kPadKey;
-  if (k < n) {
-    threshold = block_kth_smallest([&](int i) { return keys[i]; }, n, k, hist, bcast);
+  uint32_t* score_key = reinterpret_cast<uint32_t*>(sorted + padded);
+  if (staged) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) score_key[i] = static_cast<uint32_t>(keys[i] >> 32);
   }
   if (threadIdx.x == 0) fill = 0;
   for (int i = threadIdx.x; i < padded; i += blockDim.x) sorted[i] = kPadKey;
   __syncthreads();
+  auto key_at = [&](int i) {
+    return staged ? ((static_cast<unsigned long long>(score_key[i]) << 32) | static_cast<uint32_t>(i)) : keys[i];
+  };
+
+  unsigned long long threshold = kPadKey;
+  if (k < n) threshold = block_kth_smallest(key_at, n, k, hist, bcast);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const unsigned long long key = keys[i];
+    const unsigned long long key = key_at(i);
     if (key <= threshold) {
       const int slot = atomicAdd(&fill, 1);
       if (slot < padded) sorted[slot] = key;
@@ -369,17 +380,22 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
   }
   {
     const int padded = det::next_pow2(ws.k);
-    const size_t smem = static_cast<size_t>(padded) * 8;
+    const size_t sort_bytes = static_cast<size_t>(padded) * 8;
+    const size_t staged_bytes = sort_bytes + static_cast<size_t>(ws.n) * 4;
+    const size_t kSortSharedLimit = 220 * 1024;
+    if (sort_bytes > kSortSharedLimit) return -8;
+    const int staged = staged_bytes <= kSortSharedLimit ? 1 : 0;
+    const size_t smem = staged ? staged_bytes : sort_bytes;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
       cudaError_t e = cudaFuncSetAttribute(proposal_topk_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           16384 * 8);
+                                           static_cast<int>(kSortSharedLimit));
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[dev] = true;
     }
-    proposal_topk_sort_kernel<<<batch, 1024, smem, st>>>(ws, padded);
+    proposal_topk_sort_kernel<<<batch, 1024, smem, st>>>(ws, padded, staged);
     count_launch();
   }
   {

@@ -308,6 +308,9 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
       } else {
         KERNEL_CHECK(mcb200_conv_tc_launch(&slot.plan, out, s.cout, &ep, ctx.status_word(), ctx.stream_ptr()));
       }
+    } else if (path_ == kDepthwise && (half || half_out)) {
+      KERNEL_CHECK(mcb200_conv_depthwise_bf16(&s, in, half ? 1 : 0, packed_weights_.Reserve(0), out, half_out ? 1 : 0,
+                                              &ep, ctx.stream_ptr()));
     } else if (path_ == kDepthwise) {
       KERNEL_CHECK(mcb200_conv_depthwise(&s, in, packed_weights_.Reserve(0), out, &ep, ctx.stream_ptr()));
     } else {

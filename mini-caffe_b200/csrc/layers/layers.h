@@ -45,8 +45,14 @@ class ConvolutionLayer : public Layer {
   bool EqualNumBottomTopBlobs() const override { return true; }
   bool AcceptsFusedTail() const override { return true; }
   void SetFusedTail(const FusedTail& tail) override { tail_ = tail; tail_version_ = 0; }
-  bool HalfOperandsCapable() const override { return path_ == kTensorCore && !use_rows_ && shape_.c % 8 == 0; }
-  bool HalfTopCapable() const override { return path_ == kTensorCore && shape_.cout % 8 == 0; }
+  bool HalfOperandsCapable() const override {
+    if (path_ == kDepthwise) return DepthwiseHalfCapable();
+    return path_ == kTensorCore && !use_rows_ && shape_.c % 8 == 0;
+  }
+  bool HalfTopCapable() const override {
+    if (path_ == kDepthwise) return DepthwiseHalfCapable();
+    return path_ == kTensorCore && shape_.cout % 8 == 0;
+  }
   void SetHalfStorage(bool operands, bool top) override {
     if (operands != half_operands_) weight_version_ = 0;   // the packed weight image differs
     half_operands_ = operands;
@@ -58,6 +64,10 @@ class ConvolutionLayer : public Layer {
   void RefreshParameters();
   void FillEpilogue(mcb200_epilogue* ep);
 
+  // The depthwise 3x3 kernel reads and writes bfloat16 cells (fp32 weights and arithmetic).
+  bool DepthwiseHalfCapable() const {
+    return tail_.residual == nullptr && mcb200_conv_depthwise_bf16_supported(&shape_) != 0 && shape_.c % 8 == 0;
+  }
   bool half_operands_ = false;   // bfloat16 activations, weights and residual (tcgen05 kind::f16)
   bool half_top_ = false;        // the result is stored as bfloat16
 

@@ -169,3 +169,74 @@ def test_ssd300_heads(monkeypatch, capi, gpu_engine, reflib):
     for name in outs:
         assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
         print(name, error_stats(narrow[name], want[name]), error_stats(wide[name], want[name]))
+
+
+def _forward(capi, engine, builder, weights, feed, outs, marks=()):
+    net = capi.Net(engine, builder.text(), None, from_buffer=True)
+    for m in marks:
+        net.mark_output(m)
+    net.set_params(weights)
+    net.forward(**feed)
+    res = {o: net.blob(o).data.copy() for o in outs}
+    net.close()
+    return res
+
+
+def test_full_size_batches_are_batch_invariant(monkeypatch, capi, gpu_engine):
+    """ResNet-50 at batch 64 and SSD300 at batch 32 with bfloat16 storage: every image comes out bit for
+    bit as it does in a small batch (whose results the tests above compare with the reference)."""
+    wl = pkg("workloads")
+    monkeypatch.setenv("MINICAFFE_PRECISION", "bf16")
+    weights = wl.init_params(wl.resnet50(4).params, seed=0)
+    x = wl.image_input(64, seed=0)["data"]
+    big = _forward(capi, gpu_engine, wl.resnet50(64), weights, {"data": x}, ["fc1000", "prob"])
+    ref = _forward(capi, gpu_engine, wl.resnet50(4), weights, {"data": x[60:64]}, ["fc1000"])
+    assert np.isfinite(big["fc1000"]).all()
+    assert np.abs(big["prob"].sum(axis=1) - 1.0).max() < 1e-4
+    assert np.array_equal(big["fc1000"][60:64].view(np.uint32), ref["fc1000"].view(np.uint32))
+
+    weights = wl.init_params(wl.ssd300_vgg16(2).params, seed=0)
+    x = wl.ssd_input(32, seed=0)["data"]
+    outs = ["mbox_loc", "mbox_conf_flatten"]
+    big = _forward(capi, gpu_engine, wl.ssd300_vgg16(32), weights, {"data": x}, outs + ["detection_out"], marks=outs)
+    ref = _forward(capi, gpu_engine, wl.ssd300_vgg16(2), weights, {"data": x[30:32]}, outs, marks=outs)
+    for name in outs:
+        assert np.array_equal(big[name][30:32].view(np.uint32), ref[name].view(np.uint32)), name
+    rows = big["detection_out"]
+    assert rows.shape[-1] == 7 and np.isfinite(rows).all()
+
+
+def test_mobilenet_v1_and_depthwise_shapes(monkeypatch, capi, gpu_engine, reflib):
+    """Depthwise 3x3 layers (stride 1 and 2, odd sizes) read and write bfloat16 between bfloat16
+    pointwise convolutions; MobileNet-v1 end to end."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("dw_chain")
+    b.input([("data", (2, 16, 23, 17))])
+    b.conv("pw0", "data", "pw0", 16, 24, 1)
+    b.relu("r0", "pw0")
+    b.conv("dw1", "pw0", "dw1", 24, 24, 3, stride=2, pad=1, group=24)
+    b.relu("r1", "dw1")
+    b.conv("pw1", "dw1", "pw1", 24, 40, 1)
+    b.relu("r2", "pw1")
+    b.conv("dw2", "pw1", "dw2", 40, 40, 3, stride=1, pad=1, group=40)
+    b.conv("pw2", "dw2", "pw2", 40, 16, 1)
+    weights = wl.init_params(b.params, seed=41)
+    x = {"data": np.random.default_rng(42).standard_normal((2, 16, 23, 17)).astype(np.float32)}
+    for marks in ([], ["dw1", "pw1"]):
+        outs = ["pw2"] + marks
+        wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs, marks=marks)
+        want = run_net(capi, reflib, b, weights, x, outs, marks=marks)
+        for name in outs:
+            assert_close(wide[name], want[name], "tf32 " + name)
+            assert_close(narrow[name], want[name], "bf16 " + name, atol=BF16_ATOL, rtol=BF16_RTOL)
+        assert not np.array_equal(wide["pw2"], narrow["pw2"])
+
+    b = wl.mobilenet_v1(2)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.normal_image_input(2, seed=7)
+    outs = ["prob"]
+    wide, narrow = run_both_precisions(monkeypatch, capi, gpu_engine, b, weights, x, outs)
+    want = run_net(capi, reflib, b, weights, x, outs)
+    assert_close(narrow["prob"], want["prob"], "bf16 mobilenet prob", atol=BF16_ATOL, rtol=BF16_RTOL)
+    assert not np.array_equal(wide["prob"], narrow["prob"])
+    print("mobilenet prob", error_stats(narrow["prob"], want["prob"]), error_stats(wide["prob"], want["prob"]))
