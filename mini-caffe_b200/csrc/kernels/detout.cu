@@ -227,7 +227,7 @@ detout_class_kernel(const float* __restrict__ loc, const float* __restrict__ con
     }
   }
   __syncthreads();
-  block_bitonic_sort(sel, padded);
+  block_sort_keys(sel, padded);
 
   // Decode only the boxes that compete.
   const int loc_classes = p.share_location ? 1 : p.num_classes;

@@ -165,7 +165,7 @@ proposal_topk_sort_kernel(Workspace ws, int padded, int staged) {
     }
   }
   __syncthreads();
-  block_bitonic_sort(sorted, padded);
+  block_sort_keys(sorted, padded);
   const float4* boxes = ws.boxes + static_cast<size_t>(image) * n;
   const float* scores = ws.scores + static_cast<size_t>(image) * n;
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
