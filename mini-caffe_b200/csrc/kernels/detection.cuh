@@ -155,39 +155,45 @@ __device__ inline void block_bitonic_sort_regs(unsigned long long* keys) {
   for (int j = 0; j < E; ++j) v[j] = keys[t * E + j];
   __syncthreads();   // the array is scratch from here on
   for (int size = 2; size <= count; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      if (stride >= E * 32) {
+    int stride = size >> 1;
+    for (; stride >= E * 32; stride >>= 1) {   // partner in another warp
 #pragma unroll
-        for (int j = 0; j < E; ++j) keys[j * threads + t] = v[j];
-        __syncthreads();
-        const int partner = t ^ (stride / E);
+      for (int j = 0; j < E; ++j) keys[j * threads + t] = v[j];
+      __syncthreads();
+      const int partner = t ^ (stride / E);
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const int e = t * E + j;
+        const unsigned long long other = keys[j * threads + partner];
+        const bool keep_small = ((e & stride) == 0) == ((e & size) == 0);
+        v[j] = keep_small ? (v[j] < other ? v[j] : other) : (v[j] > other ? v[j] : other);
+      }
+      __syncthreads();
+    }
+    for (; stride >= E; stride >>= 1) {        // partner in another lane
+      const int lanes = stride / E;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const int e = t * E + j;
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v[j], lanes);
+        const bool keep_small = ((e & stride) == 0) == ((e & size) == 0);
+        v[j] = keep_small ? (v[j] < other ? v[j] : other) : (v[j] > other ? v[j] : other);
+      }
+    }
+    // Partner in the same thread: the strides are compile-time constants so
+    // that the keys stay in registers (an index computed at run time would put
+    // the array into local memory).
+#pragma unroll
+    for (int st = E / 2; st > 0; st >>= 1) {
+      if (st <= stride) {
 #pragma unroll
         for (int j = 0; j < E; ++j) {
-          const int e = t * E + j;
-          const unsigned long long other = keys[j * threads + partner];
-          const bool keep_small = ((e & stride) == 0) == ((e & size) == 0);
-          v[j] = keep_small ? (v[j] < other ? v[j] : other) : (v[j] > other ? v[j] : other);
-        }
-        __syncthreads();
-      } else if (stride >= E) {
-        const int lanes = stride / E;
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const int e = t * E + j;
-          const unsigned long long other = __shfl_xor_sync(0xffffffffu, v[j], lanes);
-          const bool keep_small = ((e & stride) == 0) == ((e & size) == 0);
-          v[j] = keep_small ? (v[j] < other ? v[j] : other) : (v[j] > other ? v[j] : other);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          if ((j & stride) == 0 && (j | stride) < E) {
+          if ((j & st) == 0) {
             const int e = t * E + j;
-            const unsigned long long a = v[j], b = v[j | stride];
-            if ((a > b) == ((e & size) == 0)) {
-              v[j] = b;
-              v[j | stride] = a;
-            }
+            const unsigned long long a = v[j], b = v[j | st];
+            const bool swap = (a > b) == ((e & size) == 0);
+            v[j] = swap ? b : a;
+            v[j | st] = swap ? a : b;
           }
         }
       }

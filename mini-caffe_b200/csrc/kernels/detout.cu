@@ -18,6 +18,8 @@
 #include <float.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../../include/mcb200_kernels.h"
 #include "detection.cuh"
 #include "launch_count.h"
@@ -481,6 +483,8 @@ extern "C" int mcb200_detout_forward(const mcb200_detout_params* p, int batch, c
   if (smem > 200 * 1024) return -7;
   {
     static size_t configured[64] = {0};
+    static std::mutex configure_mu;   // nets on several host threads may make their first call together
+    std::lock_guard<std::mutex> lock(configure_mu);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
@@ -498,6 +502,8 @@ extern "C" int mcb200_detout_forward(const mcb200_detout_params* p, int batch, c
     const size_t kImageSharedLimit = 200 * 1024;
     const int staged = key_bytes <= kImageSharedLimit ? 1 : 0;
     static size_t configured_image[64] = {0};
+    static std::mutex configure_mu;
+    std::lock_guard<std::mutex> lock(configure_mu);
     int dev = 0;
     cudaGetDevice(&dev);
     if (staged && dev >= 0 && dev < 64 && configured_image[dev] < key_bytes) {

@@ -387,6 +387,8 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
     const int staged = staged_bytes <= kSortSharedLimit ? 1 : 0;
     const size_t smem = staged ? staged_bytes : sort_bytes;
     static bool configured[64] = {false};
+    static std::mutex configure_mu;   // nets on several host threads may make their first call together
+    std::lock_guard<std::mutex> lock(configure_mu);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -406,6 +408,8 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
     int dev = 0;
     cudaGetDevice(&dev);
     static bool configured[64] = {false};
+    static std::mutex configure_mu;
+    std::lock_guard<std::mutex> lock(configure_mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
       const cudaError_t e = cudaFuncSetAttribute(proposal_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  220 * 1024);
