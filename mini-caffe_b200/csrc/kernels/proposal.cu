@@ -157,11 +157,24 @@ proposal_topk_sort_kernel(Workspace ws, int padded, int staged) {
 
   unsigned long long threshold = kPadKey;
   if (k < n) threshold = block_kth_smallest(key_at, n, k, hist, bcast);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const unsigned long long key = key_at(i);
-    if (key <= threshold) {
-      const int slot = atomicAdd(&fill, 1);
-      if (slot < padded) sorted[slot] = key;
+  // Append the selected keys, one update of the shared counter per warp.
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    unsigned long long key = 0;
+    bool take = false;
+    if (i < n) {
+      key = key_at(i);
+      take = key <= threshold;
+    }
+    const unsigned taking = __ballot_sync(0xffffffffu, take);
+    if (taking) {
+      const int lane = threadIdx.x & 31;
+      const int leader = __ffs(taking) - 1;
+      int first = 0;
+      if (lane == leader) first = atomicAdd(&fill, __popc(taking));
+      first = __shfl_sync(0xffffffffu, first, leader);
+      const int slot = first + __popc(taking & ((1u << lane) - 1u));
+      if (take && slot < padded) sorted[slot] = key;
     }
   }
   __syncthreads();
