@@ -181,10 +181,28 @@ proposal_topk_sort_kernel(Workspace ws, int padded, int staged) {
   block_sort_keys(sorted, padded);
   const float4* boxes = ws.boxes + static_cast<size_t>(image) * n;
   const float* scores = ws.scores + static_cast<size_t>(image) * n;
-  for (int i = threadIdx.x; i < k; i += blockDim.x) {
-    const uint32_t index = static_cast<uint32_t>(sorted[i] & 0xFFFFFFFFull);
-    ws.sorted_boxes[static_cast<size_t>(image) * k + i] = boxes[index];
-    ws.sorted_scores[static_cast<size_t>(image) * k + i] = scores[index];
+  // Gather in groups of four per thread: the four box and score loads (random
+  // rows, an L2 round trip each) are issued before the first store.
+  for (int base = threadIdx.x; base < k; base += 4 * blockDim.x) {
+    float4 box[4];
+    float score[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = base + u * blockDim.x;
+      if (i < k) {
+        const uint32_t index = static_cast<uint32_t>(sorted[i] & 0xFFFFFFFFull);
+        box[u] = boxes[index];
+        score[u] = scores[index];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = base + u * blockDim.x;
+      if (i < k) {
+        ws.sorted_boxes[static_cast<size_t>(image) * k + i] = box[u];
+        ws.sorted_scores[static_cast<size_t>(image) * k + i] = score[u];
+      }
+    }
   }
 }
 
