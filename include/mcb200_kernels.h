@@ -260,6 +260,15 @@ int mcb200_proposal_forward(const mcb200_proposal_params* p, int batch, const fl
                             const float* im_info, const float* anchors, void* workspace, float* rois,
                             float* roi_scores, int* counts, void* stream);
 
+/* Closes the gaps between the images' row blocks of a batched
+ * mcb200_proposal_forward result in place: image b's counts[b] valid rows move
+ * from row b * post_nms_topn to row counts[0] + ... + counts[b-1] (rois and,
+ * when not NULL, roi_scores).  One kernel; source and destination ranges may
+ * overlap.  (mini-caffe's layer takes one image per call,
+ * src/layers/proposal_layer.cpp:269, and so has nothing to compact.)           */
+int mcb200_proposal_compact(float* rois, float* roi_scores, const int* counts, int batch, int post_nms_topn,
+                            void* stream);
+
 /* The same computation as mcb200_proposal_forward for callers that cannot
  * allocate device memory.  (It has no counterpart in mini-caffe.)
  *
@@ -271,21 +280,35 @@ int mcb200_proposal_forward(const mcb200_proposal_params* p, int batch, const fl
  * their hands.
  *
  * The scratch is a fixed 8 MiB array inside the library's device image (each
- * GPU that loads the library holds it until the process exits).  That covers
- * one image with up to 65536 proposals and pre_nms_topn up to 6000 (the stock
- * R-FCN / Faster-RCNN settings need 1.1 MB per image); a request that needs more returns
- * -20 and prints the required size.  The function calls no cudaMalloc, cudaFree
+ * GPU that loads the library holds it until the process exits).  The largest
+ * single image the kernels accept (65536 proposals, pre_nms_topn 6000) takes
+ * 1.9 MB of it, an image of the stock R-FCN setting (63 x 38 map, 15 anchors)
+ * 1.1 MB, and a batch takes that many times as much; a request that needs more
+ * than 8 MiB returns -20 and prints the required size.  The function calls no cudaMalloc, cudaFree
  * or any other allocating routine.
  *
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress) and keeps it; make that first call before starting any
- * stream capture.  All calls share the one array: two calls whose kernels may
+ * (cudaGetSymbolAddress) and keeps it; make that first call (or a call of
+ * mcb200_proposal_static_warmup, below) before starting any stream capture and
+ * before the host takes the rest of the device memory.  All calls share the one array: two calls whose kernels may
  * overlap on the GPU (different streams, or different host threads without
  * ordering) race on it -- serialise them.  Nothing in the array needs to be
  * zero on entry, it is not cleared, and it keeps the last call's contents.     */
 int mcb200_proposal_forward_static(const mcb200_proposal_params* p, int batch, const float* scores,
                                    const float* deltas, const float* im_info, const float* anchors, float* rois,
                                    float* roi_scores, int* counts, void* stream);
+
+/* Does what the first call of mcb200_proposal_forward_static on the current
+ * device would do besides computing: loads the library's device code (with
+ * CUDA's default lazy loading that is the moment the driver sets the 8 MiB
+ * array aside, and it synchronises the device), looks up the array's address
+ * and opts the kernels into their shared-memory size.  Launches nothing.  A
+ * host that is about to give all device memory to its own pool, or that must
+ * keep such one-time work out of a latency-critical loop, calls this first,
+ * once per device; without it the first mcb200_proposal_forward_static call
+ * does the same work and can fail with an out-of-memory error if no device
+ * memory is left by then.  (No counterpart in mini-caffe.)                      */
+int mcb200_proposal_static_warmup(void);
 
 /* ------------------------------------------------------------------ SSD detection output */
 typedef struct mcb200_detout_params {

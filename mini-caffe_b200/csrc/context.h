@@ -42,6 +42,8 @@ class Context {
   void Activate();
   cudaStream_t stream() { Activate(); return stream_; }
   void* stream_ptr() { return static_cast<void*>(stream()); }
+  // The stream if this thread has one already, else NULL (never creates one, never throws).
+  void* stream_if_active() const { return active_ ? static_cast<void*>(stream_) : nullptr; }
   // Device int that kernels raise on a timed-out wait; checked by Net::Forward.
   int* status_word() { Activate(); return status_dev_; }
   // Blocks until the stream is idle and throws if a kernel raised the status word.

@@ -386,6 +386,60 @@ static int validate(const mcb200_proposal_params* p, int batch) {
   return 0;
 }
 
+constexpr size_t kSortSharedLimit = 220 * 1024;
+
+// The top-k and the NMS kernel use more dynamic shared memory than a kernel gets
+// by default; the opt-in is per device and is made on a device's first call
+// (nets on several host threads may make that call at the same time).
+static cudaError_t configure_kernels() {
+  static bool configured[64] = {false};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 0 || dev >= 64 || configured[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(proposal_topk_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSortSharedLimit));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(proposal_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  if (e != cudaSuccess) return e;
+  configured[dev] = true;
+  return cudaSuccess;
+}
+
+// Moves the valid rows of images 1 .. batch-1 up against those of the image in
+// front (rows of image b start at b * post and move to the sum of the counts
+// before it).  A row never moves to a higher address and images are handled in
+// order, so what is overwritten has been moved already; inside an image the
+// block copies `blockDim.x` values at a time, reading a piece completely before
+// writing it (source and destination ranges may overlap).
+static __global__ void proposal_compact_kernel(float* __restrict__ rois, float* __restrict__ roi_scores,
+                                        const int* __restrict__ counts, int batch, int post) {
+  int total = counts[0];
+  for (int b = 1; b < batch; ++b) {
+    const int rows = counts[b];
+    if (rows > 0 && total != b * post) {
+      for (int pass = 0; pass < 2; ++pass) {
+        float* base = pass == 0 ? rois : roi_scores;
+        if (!base) continue;
+        const int width = pass == 0 ? 5 : 1;
+        const float* src = base + static_cast<size_t>(b) * post * width;
+        float* dst = base + static_cast<size_t>(total) * width;
+        const int values = rows * width;
+        for (int i0 = 0; i0 < values; i0 += blockDim.x) {
+          const int i = i0 + threadIdx.x;
+          const float v = i < values ? src[i] : 0.f;
+          __syncthreads();
+          if (i < values) dst[i] = v;
+          __syncthreads();
+        }
+      }
+    }
+    total += rows;
+  }
+}
+
 extern "C" size_t mcb200_proposal_workspace_bytes(const mcb200_proposal_params* p, int batch) {
   if (validate(p, batch) != 0) return 0;
   return carve(*p, batch, nullptr, nullptr);
@@ -399,6 +453,8 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
   if (!scores || !deltas || !im_info || !anchors || !workspace || !rois || !counts) return -5;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return -6;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const cudaError_t configured = configure_kernels();
+  if (configured != cudaSuccess) return static_cast<int>(configured);
   Workspace ws;
   carve(*p, batch, static_cast<char*>(workspace), &ws);
 
@@ -413,21 +469,9 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
     const int padded = det::next_pow2(ws.k);
     const size_t sort_bytes = static_cast<size_t>(padded) * 8;
     const size_t staged_bytes = sort_bytes + static_cast<size_t>(ws.n) * 4;
-    const size_t kSortSharedLimit = 220 * 1024;
     if (sort_bytes > kSortSharedLimit) return -8;
     const int staged = staged_bytes <= kSortSharedLimit ? 1 : 0;
     const size_t smem = staged ? staged_bytes : sort_bytes;
-    static bool configured[64] = {false};
-    static std::mutex configure_mu;   // nets on several host threads may make their first call together
-    std::lock_guard<std::mutex> lock(configure_mu);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(proposal_topk_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kSortSharedLimit));
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured[dev] = true;
-    }
     proposal_topk_sort_kernel<<<batch, 1024, smem, st>>>(ws, padded, staged);
     count_launch();
   }
@@ -436,17 +480,6 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
     const int staged = ws.col_blocks * 64 <= kNmsStagedBoxes ? 1 : 0;
     const size_t smem = nms_kept_bytes(p->post_nms_topn) + (staged ? static_cast<size_t>(ws.col_blocks) * 64 * 20 : 0);
     if (smem > 220 * 1024) return -7;   // post_nms_topn beyond 10000 with staged boxes: not a detector's setting
-    int dev = 0;
-    cudaGetDevice(&dev);
-    static bool configured[64] = {false};
-    static std::mutex configure_mu;
-    std::lock_guard<std::mutex> lock(configure_mu);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-      const cudaError_t e = cudaFuncSetAttribute(proposal_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 220 * 1024);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured[dev] = true;
-    }
     proposal_nms_kernel<<<batch, kNmsThreads, smem, st>>>(ws, p->nms_thresh, p->post_nms_topn, staged, rois, roi_scores,
                                                            counts);
     count_launch();
@@ -454,14 +487,59 @@ extern "C" int mcb200_proposal_forward(const mcb200_proposal_params* p, int batc
   return static_cast<int>(cudaGetLastError());
 }
 
+extern "C" int mcb200_proposal_compact(float* rois, float* roi_scores, const int* counts, int batch,
+                                       int post_nms_topn, void* stream) {
+  if (!rois || !counts || batch < 1 || post_nms_topn < 1) return -1;
+  if (batch == 1) return 0;
+  proposal_compact_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(rois, roi_scores, counts, batch,
+                                                                             post_nms_topn);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ------------------------------------------------------------------ variant without allocation
 
 // Scratch of mcb200_proposal_forward_static.  It lives in the library's device
 // image: every GPU that loads the library carries these 8 MiB until the process
-// exits.  Enough for one image with up to 65536 proposals of which up to 6000
-// go to NMS (1.9 MB); larger requests are refused.
+// exits.  The largest single image the kernels accept (65536 proposals of which
+// 6000 go to NMS) takes 1.9 MB of it, an image of the stock R-FCN setting (63 x 38
+// map, 15 anchors) 1.1 MB; a call whose batch needs more than the array holds
+// is refused.
 static constexpr size_t kStaticScratchBytes = static_cast<size_t>(8) << 20;
 static __device__ __align__(256) unsigned char g_proposal_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+// Device address of the scratch array on the current device, looked up once per device.
+// In host code the array's name is only a handle; the address has to be asked for
+// with that device current.
+int static_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -21;
+  static void* scratch_of_device[64] = {nullptr};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!scratch_of_device[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_proposal_static_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (!ptr) return -22;
+    scratch_of_device[dev] = ptr;
+  }
+  *out = scratch_of_device[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int mcb200_proposal_static_warmup(void) {
+  void* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != 0) return rc;
+  return static_cast<int>(configure_kernels());
+}
 
 extern "C" int mcb200_proposal_forward_static(const mcb200_proposal_params* p, int batch, const float* scores,
                                               const float* deltas, const float* im_info, const float* anchors,
@@ -476,26 +554,9 @@ extern "C" int mcb200_proposal_forward_static(const mcb200_proposal_params* p, i
             need, kStaticScratchBytes);
     return -20;
   }
-  // In host code the array's name is only a handle; the device address has to be
-  // asked for, once per device, with that device current.
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 0 || dev >= 64) return -21;
-  static void* scratch_of_device[64] = {nullptr};
-  static std::mutex mu;
   void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!scratch_of_device[dev]) {
-      void* ptr = nullptr;
-      e = cudaGetSymbolAddress(&ptr, g_proposal_static_scratch);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      if (!ptr) return -22;
-      scratch_of_device[dev] = ptr;
-    }
-    scratch = scratch_of_device[dev];
-  }
+  const int found = static_scratch(&scratch);
+  if (found != 0) return found;
   // Every scratch word the kernels read is written earlier in the same call
   // (keys, boxes and scores for all proposals, the sorted copies for the best
   // pre_nms_topn), so nothing has to be cleared between calls.

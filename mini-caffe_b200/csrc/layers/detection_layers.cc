@@ -218,21 +218,15 @@ void ProposalLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>
   KERNEL_CHECK(mcb200_proposal_forward(&params_, batch, bottom[0]->gpu_data(), bottom[1]->gpu_data(),
                                        bottom[2]->gpu_data(), anchors_.get(), ws, rois, roi_scores,
                                        counts_->mutable_gpu_data(), ctx.stream_ptr()));
+  // Close the gaps between the images' row blocks on the device (the ranges a
+  // row block leaves and enters may overlap, so this is a kernel, not a copy).
+  if (batch > 1) {
+    KERNEL_CHECK(mcb200_proposal_compact(rois, roi_scores, counts_->gpu_data(), batch, post, ctx.stream_ptr()));
+  }
   // The output row count is data dependent: fetch the counts (a few bytes).
   const int* counts = counts_->cpu_data();
-  int total = counts[0];
-  for (int b = 1; b < batch; ++b) {
-    // Close the gaps between the images' row blocks.
-    if (counts[b] > 0 && total != b * post) {
-      CUDA_CHECK(cudaMemcpyAsync(rois + static_cast<size_t>(total) * 5, rois + static_cast<size_t>(b) * post * 5,
-                                 sizeof(float) * 5 * counts[b], cudaMemcpyDeviceToDevice, ctx.stream()));
-      if (want_scores) {
-        CUDA_CHECK(cudaMemcpyAsync(roi_scores + total, roi_scores + static_cast<size_t>(b) * post,
-                                   sizeof(float) * counts[b], cudaMemcpyDeviceToDevice, ctx.stream()));
-      }
-    }
-    total += counts[b];
-  }
+  int total = 0;
+  for (int b = 0; b < batch; ++b) total += counts[b];
   top[0]->Reshape(vector<int>{total, 5});
   if (want_scores) top[1]->Reshape(vector<int>{total});
 }

@@ -2,6 +2,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <set>
 
 #include "context.h"
 #include "mcb200_kernels.h"
@@ -10,16 +11,40 @@ namespace caffe {
 
 // ---------------------------------------------------------------- MemoryPool
 
+// Pools that exist right now.  A block returned by a thread that does not own
+// it finds out here whether its pool is still there; the lock is held while the
+// block is handed over, so a pool cannot disappear in the middle of that.
+static std::mutex& LivePoolsLock() {
+  static std::mutex* mu = new std::mutex();   // outlives every thread-local pool
+  return *mu;
+}
+static std::set<MemoryPool*>& LivePools() {
+  static std::set<MemoryPool*>* pools = new std::set<MemoryPool*>();
+  return *pools;
+}
+
 MemoryPool* MemoryPool::Get() {
   static thread_local MemoryPool pool;
   return &pool;
 }
 
-MemoryPool::~MemoryPool() { Clear(); }
+MemoryPool::MemoryPool() {
+  std::lock_guard<std::mutex> lock(LivePoolsLock());
+  LivePools().insert(this);
+}
+
+MemoryPool::~MemoryPool() {
+  {
+    std::lock_guard<std::mutex> lock(LivePoolsLock());
+    LivePools().erase(this);
+  }
+  Clear();
+}
 
 static bool Reusable(size_t has, size_t wants) { return has / 2 <= wants; }
 
 MemBlock MemoryPool::RequestCPU(size_t size) {
+  std::lock_guard<std::mutex> lock(mu_);
   auto it = cpu_free_.lower_bound(size);
   if (it != cpu_free_.end() && Reusable(it->second.size, size)) {
     MemBlock b = it->second;
@@ -30,6 +55,7 @@ MemBlock MemoryPool::RequestCPU(size_t size) {
   MemBlock b;
   b.size = size;
   b.device = -1;
+  b.pool = this;
   if (DeviceCount() > 0) {
     // Pinned, so that host<->device copies can run asynchronously on the stream.
     CUDA_CHECK(cudaMallocHost(&b.ptr, size));
@@ -42,21 +68,27 @@ MemBlock MemoryPool::RequestCPU(size_t size) {
 
 void MemoryPool::ReturnCPU(MemBlock block) {
   if (!block.ptr) return;
+  std::lock_guard<std::mutex> lock(mu_);
   cpu_unused_ += static_cast<long long>(block.size);
   cpu_free_.insert(std::make_pair(block.size, block));
 }
 
 MemBlock MemoryPool::RequestGPU(size_t size, int device) {
+  void* stream = Context::Get().stream_ptr();   // the requesting thread's work will use the block
+  std::lock_guard<std::mutex> lock(mu_);
   auto it = gpu_free_.lower_bound(std::make_pair(device, size));
   if (it != gpu_free_.end() && it->second.device == device && Reusable(it->second.size, size)) {
     MemBlock b = it->second;
     gpu_free_.erase(it);
     gpu_unused_ -= static_cast<long long>(b.size);
+    b.stream = stream;
     return b;
   }
   MemBlock b;
   b.size = size;
   b.device = device;
+  b.pool = this;
+  b.stream = stream;
   int current = 0;
   CUDA_CHECK(cudaGetDevice(&current));
   if (current != device) CUDA_CHECK(cudaSetDevice(device));
@@ -68,12 +100,62 @@ MemBlock MemoryPool::RequestGPU(size_t size, int device) {
 
 void MemoryPool::ReturnGPU(MemBlock block) {
   if (!block.ptr) return;
+  std::lock_guard<std::mutex> lock(mu_);
   gpu_unused_ += static_cast<long long>(block.size);
   gpu_free_.insert(std::make_pair(std::make_pair(block.device, block.size), block));
 }
 
+void MemoryPool::Release(MemBlock block) {
+  if (!block.ptr) return;
+  MemoryPool* mine = MemoryPool::Get();
+  const bool gpu = block.device >= 0;
+  if (block.pool == mine || block.pool == nullptr) {
+    if (gpu) {
+      mine->ReturnGPU(block);
+    } else {
+      mine->ReturnCPU(block);
+    }
+    return;
+  }
+  // Another thread allocated this block.  Work that uses it may be queued on
+  // that thread's stream and on this thread's; the owner's pool will hand it to
+  // work on the owner's stream only, so both are drained before it goes back.
+  const bool have_device = DeviceCount() > 0;
+  if (have_device) {
+    try { Context::Get().Sync(); } catch (...) {}
+    if (block.stream) cudaStreamSynchronize(static_cast<cudaStream_t>(block.stream));
+    cudaGetLastError();   // the owner's stream may be gone already
+  }
+  std::lock_guard<std::mutex> lock(LivePoolsLock());
+  if (LivePools().count(block.pool)) {
+    if (gpu) {
+      block.pool->ReturnGPU(block);
+    } else {
+      block.pool->ReturnCPU(block);
+    }
+    return;
+  }
+  // The owning thread has ended and taken its pool with it.
+  if (gpu) {
+    int current = 0;
+    if (cudaGetDevice(&current) == cudaSuccess) {
+      if (current != block.device) cudaSetDevice(block.device);
+      cudaDeviceSynchronize();
+      cudaFree(block.ptr);
+      if (current != block.device) cudaSetDevice(current);
+    }
+    cudaGetLastError();
+  } else if (have_device) {
+    cudaFreeHost(block.ptr);
+    cudaGetLastError();
+  } else {
+    free(block.ptr);
+  }
+}
+
 void MemoryPool::Clear() {
   const bool have_device = DeviceCount() > 0;
+  std::lock_guard<std::mutex> lock(mu_);
   for (auto& kv : cpu_free_) {
     if (have_device) {
       cudaFreeHost(kv.second.ptr);
@@ -105,6 +187,7 @@ void MemoryPool::Clear() {
 static int Saturate(long long v) { return v > 0x7fffffffLL ? 0x7fffffff : static_cast<int>(v); }
 
 MemPoolState MemoryPool::GetState() const {
+  std::lock_guard<std::mutex> lock(mu_);
   MemPoolState st;
   st.cpu_mem = Saturate(cpu_total_);
   st.gpu_mem = Saturate(gpu_total_);
@@ -127,17 +210,23 @@ SyncedMemory::~SyncedMemory() {
   // Kernels queued on the stream may still use the device blocks; the pool
   // hands them out again only to work queued on the same stream, which is
   // ordered after those kernels.
-  MemoryPool* pool = MemoryPool::Get();
+  // ordered after those kernels.  (MemoryPool::Release covers the case that
+  // another thread than the allocating one runs this destructor.)
   if (host_.ptr) {
     // A pinned block may be the target of a copy that is still in flight.
     if (valid_ & (kDevice | kDeviceNhwc | kDeviceNhwcHalf)) {
       try { Context::Get().Sync(); } catch (...) {}
+      void* stream = dev_.ptr ? dev_.stream : (nhwc_.ptr ? nhwc_.stream : half_.stream);
+      if (stream && stream != Context::Get().stream_if_active()) {
+        cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+        cudaGetLastError();
+      }
     }
-    pool->ReturnCPU(host_);
+    MemoryPool::Release(host_);
   }
-  if (dev_.ptr) pool->ReturnGPU(dev_);
-  if (nhwc_.ptr) pool->ReturnGPU(nhwc_);
-  if (half_.ptr) pool->ReturnGPU(half_);
+  MemoryPool::Release(dev_);
+  MemoryPool::Release(nhwc_);
+  MemoryPool::Release(half_);
 }
 
 void SyncedMemory::EnsureHost() {

@@ -20,15 +20,23 @@
 
 #include <cstddef>
 #include <map>
+#include <mutex>
 
 #include "caffe/base.hpp"
 
 namespace caffe {
 
+class MemoryPool;
+
 struct MemBlock {
   void* ptr = nullptr;
   size_t size = 0;
   int device = -1;  // -1: host
+  // The pool the block was taken from and the stream its user's work is queued
+  // on (the requesting thread's).  A block always goes back to this pool, also
+  // when another thread destroys the object that holds it.
+  MemoryPool* pool = nullptr;
+  void* stream = nullptr;
 };
 
 class MemoryPool {
@@ -38,12 +46,20 @@ class MemoryPool {
   void ReturnCPU(MemBlock block);
   MemBlock RequestGPU(size_t size, int device);
   void ReturnGPU(MemBlock block);
+  // Gives a block back to the pool it came from, from whichever thread.  The
+  // pool's reuse rule rests on blocks being reused by work on the stream that
+  // used them last; when the calling thread is not the owner, both threads'
+  // streams are drained first, and if the owning thread (and its pool) is gone
+  // the block is freed.
+  static void Release(MemBlock block);
   void Clear();
   MemPoolState GetState() const;
   ~MemoryPool();
 
  private:
-  MemoryPool() {}
+  MemoryPool();
+  void Insert(const MemBlock& block);
+  mutable std::mutex mu_;   // the owner allocates, any thread may return
   std::multimap<size_t, MemBlock> cpu_free_;
   std::multimap<std::pair<int, size_t>, MemBlock> gpu_free_;
   long long cpu_total_ = 0, gpu_total_ = 0, cpu_unused_ = 0, gpu_unused_ = 0;

@@ -16,6 +16,9 @@ if ROOT not in sys.path:
 
 ENGINE_LIB = os.path.join(ROOT, "mini-caffe_b200", "lib", "libcaffe.so")
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libcaffe_ref.so")
+# A checkout of the reference project (its example models and callers are test inputs where present):
+# MINI_CAFFE_REFERENCE, else a directory `reference` beside this repository.
+REFERENCE_CHECKOUT = os.environ.get("MINI_CAFFE_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def pytest_configure(config):
@@ -49,10 +52,22 @@ def kernels():
     return ctypes.CDLL(ENGINE_LIB, mode=ctypes.RTLD_LOCAL)
 
 
-@pytest.fixture(scope="session")
-def reflib(capi):
-    """The reference project's CPU build (oracle/_ref).  Tests that need it are
-    skipped when it has not been built (it needs the reference checkout)."""
+_reference_library = {}
+
+
+@pytest.fixture
+def reflib(request, capi):
+    """The reference project's CPU build (oracle/_ref), the checker of the parity tests.
+
+    Without it a GPU parity test has nothing to compare with, so for a test marked `gpu` its absence
+    is a failure (a run in which the checker did not travel with the repository must not look green).
+    Host-only tests are skipped instead: the library can only be built where a checkout of the
+    reference project is present."""
     if not os.path.isfile(REF_LIB):
-        pytest.skip("oracle/_ref/libcaffe_ref.so not built")
-    return capi.CaffeLibrary(REF_LIB)
+        message = "oracle/_ref/libcaffe_ref.so is not built (build it with `make -C oracle REF=<mini-caffe checkout>`)"
+        if request.node.get_closest_marker("gpu") is not None:
+            pytest.fail(message)
+        pytest.skip(message)
+    if "lib" not in _reference_library:
+        _reference_library["lib"] = capi.CaffeLibrary(REF_LIB)
+    return _reference_library["lib"]

@@ -8,9 +8,9 @@ import re
 import numpy as np
 import pytest
 
-from conftest import ENGINE_LIB, ROOT, pkg
+from conftest import ENGINE_LIB, REFERENCE_CHECKOUT, ROOT, pkg
 
-REFERENCE_MODELS = "/root/reference/example/models"
+REFERENCE_MODELS = os.path.join(REFERENCE_CHECKOUT, "example", "models")
 
 
 def test_every_declared_symbol_is_exported(kernels):
@@ -251,3 +251,47 @@ def test_cli_built_on_public_headers_fails_loudly_without_a_device(tmp_path):
     assert "no CPU compute path" in run.stderr
     usage = subprocess.run([exe], capture_output=True, text=True, timeout=60)
     assert usage.returncode == 2 and "Usage" in usage.stderr
+
+
+@pytest.mark.parametrize("owner_alive", [True, False])
+def test_net_destroyed_by_another_thread_than_its_creator(capi, engine, owner_alive):
+    """CaffeNetCreate on a worker thread, CaffeNetDestroy on the main thread (a common pattern).
+    The memory pool is per thread: the blocks must find their way back to the pool they came from
+    while that thread lives, and be freed when it has ended; the main thread's pool must neither
+    receive them nor hand them out."""
+    import threading
+    wl = pkg("workloads")
+    b = wl.conv_relu(2)
+    weights = wl.init_params(b.params, seed=0)
+    box = {}
+    created, release = threading.Event(), threading.Event()
+
+    def worker():
+        net = capi.Net(engine, b.text(), None, from_buffer=True)
+        net.set_params(weights)                      # host blocks of the parameters come from this thread's pool
+        net.blob("data").data[...] = 1.0             # and the input's
+        box["net"] = net
+        created.set()
+        if owner_alive:
+            release.wait(30)
+            # the pool took its blocks back: a new net of the same shapes reuses them
+            again = capi.Net(engine, b.text(), None, from_buffer=True)
+            again.set_params(weights)
+            box["again"] = float(dict(again.params())["conv_0"].data.sum())
+            again.close()
+
+    t = threading.Thread(target=worker)
+    t.start()
+    assert created.wait(60)
+    if not owner_alive:
+        t.join()
+    box["net"].close()                               # destroyed here, on the main thread
+    release.set()
+    t.join()
+    if owner_alive:
+        assert box["again"] == pytest.approx(float(weights["conv_0"].sum()), rel=1e-5)
+    # the main thread's own pool still works
+    own = capi.Net(engine, b.text(), None, from_buffer=True)
+    own.set_params(weights)
+    assert np.array_equal(dict(own.params())["conv_1"].data, weights["conv_1"])
+    own.close()

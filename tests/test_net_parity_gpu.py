@@ -144,3 +144,56 @@ def test_folded_model_files_run_the_same(capi, gpu_engine, tmp_path):
         net.close()
     for name in ("gap", "c3"):
         assert_close(outs["fold"][name], outs["orig"][name], name)
+
+
+def test_net_destroyed_by_another_thread_while_its_creator_keeps_working(capi, gpu_engine):
+    """A net is created and run on a worker thread and destroyed on the main thread while the
+    worker's stream is still busy with other nets.  Streams and memory pools are per thread: the
+    destroyed net's device blocks must go back to the worker's pool only after the work that uses
+    them has drained, so the worker's later results are what they were before."""
+    import threading
+    wl = pkg("workloads")
+    b = small_residual_net(wl, 8, False)
+    weights = wl.init_params(b.params, seed=21, bn_identity=False)
+    x = np.random.default_rng(22).standard_normal((8, 3, 32, 32)).astype(np.float32)
+    box = {"results": []}
+    created, destroyed = threading.Event(), threading.Event()
+
+    def run_once():
+        net = capi.Net(gpu_engine, b.text(), None, from_buffer=True)
+        net.set_params(weights)
+        net.forward(data=x)
+        out = net.blob("prob").data.copy()
+        return net, out
+
+    def worker():
+        try:
+            gpu_engine.set_mode(True, 0)
+            keep, first = run_once()
+            box["first"] = first
+            box["net"] = keep
+            created.set()
+            for _ in range(6):                       # keeps the stream busy around the foreign destroy
+                net, out = run_once()
+                box["results"].append(out)
+                net.close()
+            destroyed.wait(60)
+            for _ in range(3):                       # these allocations may reuse the returned blocks
+                net, out = run_once()
+                box["results"].append(out)
+                net.close()
+        except BaseException as exc:                 # noqa: BLE001
+            box["error"] = exc
+            created.set()
+
+    t = threading.Thread(target=worker)
+    t.start()
+    assert created.wait(120)
+    assert "error" not in box, box.get("error")
+    box["net"].close()                               # on the main thread
+    destroyed.set()
+    t.join()
+    assert "error" not in box, box.get("error")
+    assert len(box["results"]) == 9
+    for out in box["results"]:
+        assert np.array_equal(out.view(np.uint32), box["first"].view(np.uint32))

@@ -62,6 +62,17 @@ def _run(lib, static, params, inputs, anchors):
     return n, rois[:n].cpu().numpy(), roi_scores[:n].cpu().numpy()
 
 
+def test_static_scratch_warmup_is_repeatable(kernels):
+    """The warm-up entry point does the one-time work of the first call (device code loaded, array
+    address looked up, kernels opted into their shared-memory size) and launches nothing; hosts call
+    it before they take the device memory for their own pool.  Calling it again changes nothing."""
+    kernels.mcb200_launch_count.restype = ctypes.c_longlong
+    before = kernels.mcb200_launch_count()
+    assert kernels.mcb200_proposal_static_warmup() == 0
+    assert kernels.mcb200_proposal_static_warmup() == 0
+    assert kernels.mcb200_launch_count() == before
+
+
 def test_static_scratch_variant_matches_workspace_variant(kernels):
     wl = pkg("workloads")
     calls = [
