@@ -45,7 +45,7 @@ extern "C" void mcb200_kernel_timing_begin(void) {
   s.enabled = true;
 }
 
-extern "C" long long mcb200_kernel_timing_end(double* total_ms) {
+extern "C" long long mcb200_kernel_timing_end_each(double* total_ms, double* each_ms, long long capacity) {
   mcb200::TimerState& s = mcb200::State();
   s.enabled = false;
   double sum = 0.0;
@@ -53,9 +53,14 @@ extern "C" long long mcb200_kernel_timing_end(double* total_ms) {
     float ms = 0.f;
     if (cudaEventSynchronize(s.end[i]) == cudaSuccess && cudaEventElapsedTime(&ms, s.begin[i], s.end[i]) == cudaSuccess)
       sum += ms;
+    if (each_ms && i < capacity) each_ms[i] = ms;
   }
   if (total_ms) *total_ms = sum;
   const long long n = s.used;
   s.used = 0;
   return n;
+}
+
+extern "C" long long mcb200_kernel_timing_end(double* total_ms) {
+  return mcb200_kernel_timing_end_each(total_ms, nullptr, 0);
 }

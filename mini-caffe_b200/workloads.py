@@ -523,3 +523,39 @@ def extra_layers_input(batch=2, seed=0):
     rng = np.random.default_rng(seed + 7000)
     return {"data": rng.standard_normal((batch, 6, 9, 7)).astype(np.float32),
             "like": np.zeros((batch, 4, 13, 11), dtype=np.float32)}
+
+
+# ----------------------------------------------------------------- algorithmic work of a generated network
+
+def conv_work(builder, blob_shapes):
+    """FLOPs and algorithmic bytes of the Convolution / InnerProduct layers of a generated network.
+
+    blob_shapes: {blob name: shape} as the library reports them for this prototxt (Net construction
+    needs no device).  Per layer, with fp32 elements:
+        flops = 2 * N * Cout * Ho * Wo * (Cin / group) * Kh * Kw            (InnerProduct: 2 * M * N * K)
+        bytes = 4 * (input elements + output elements + weight elements + Cout)
+    every tensor counted once per layer (an activation written by one layer and read by the next is
+    counted by both: each kernel has to move it once).  Fused residual inputs are not known at this
+    level and are left out.  Returns {"flops", "bytes", "layers"}."""
+    import re
+    weights = {name: shape for name, shape, _, _ in builder.params}
+    flops = 0
+    nbytes = 0
+    layers = 0
+    for line in builder.lines:
+        m = re.match(r'layer \{ name: "([^"]+)" type: "(Convolution|InnerProduct)"', line)
+        if not m:
+            continue
+        name = m.group(1)
+        bottom = re.search(r'bottom: "([^"]+)"', line).group(1)
+        top = re.search(r'top: "([^"]+)"', line).group(1)
+        w = weights[name + "_0"]
+        n_in = int(np.prod(blob_shapes[bottom]))
+        n_out = int(np.prod(blob_shapes[top]))
+        n_w = int(np.prod(w))
+        cout = w[0]
+        # every output element takes (weight elements / Cout) multiply-adds
+        flops += 2 * n_out * (n_w // cout)
+        nbytes += 4 * (n_in + n_out + n_w + cout)
+        layers += 1
+    return {"flops": flops, "bytes": nbytes, "layers": layers}
