@@ -84,13 +84,17 @@ typedef struct mcb200_conv_plan {
   uint64_t tma_res[16];     /* and rebuilt when the pointers below change          */
   mcb200_conv_shape shape;
   int m, k_iters, c_blocks, block_n;
-  int im2col;               /* 0 matrix rows, 1 im2col tensor map, 2 row mode      */
+  int im2col;               /* 0 matrix rows, 1 im2col tensor map, 2 row mode, 3 halo mode (the taps
+                               of a filter row share one strip of input pixels)   */
   int out_ld, res_ld;
   int cta_pair;             /* 1: launched as two-CTA clusters (tcgen05 cta_group::2) */
   int operand_bf16;         /* 1: built by mcb200_conv_tc_plan_bf16                 */
   int out_bf16;             /* element type the cached output tile map was built for */
   const float* out_ptr;
   const float* res_ptr;
+  int m_virtual;            /* halo mode: positions of the virtual output grid (rows widened by
+                               (kw - 1) * dil_w); else m                            */
+  int strip_rows;           /* halo mode: pixels per activation load (128 + (kw - 1) * dil_w) */
 } __attribute__((aligned(64))) mcb200_conv_plan;
 
 /* Implicit-GEMM convolution on the tensor cores (tcgen05.mma kind::tf32,

@@ -83,10 +83,87 @@ static void UpgradeNetInput(NetParameter* net) {
   net->clear_input_dim();
 }
 
+namespace {
+
+// Type string of the current format for a V1 enumerator (the number is the wire value of
+// V1LayerParameter.LayerType).  Only the types the V1 format shares with this project's schema
+// appear; anything else is an error, as in src/util/upgrade_proto.cpp:210-262.
+const char* V1TypeName(int type) {
+  static const struct { int value; const char* name; } kNames[] = {
+      {0, ""},          {35, "AbsVal"},      {2, "BNLL"},     {3, "Concat"},        {4, "Convolution"},
+      {39, "Deconvolution"}, {6, "Dropout"}, {25, "Eltwise"}, {38, "Exp"},          {8, "Flatten"},
+      {14, "InnerProduct"},  {15, "LRN"},    {34, "MVN"},     {17, "Pooling"},      {26, "Power"},
+      {18, "ReLU"},     {19, "Sigmoid"},     {20, "Softmax"}, {22, "Split"},        {33, "Slice"},
+      {23, "TanH"},     {31, "Threshold"},
+  };
+  for (const auto& entry : kNames)
+    if (entry.value == type) return entry.name;
+  LOG(FATAL) << "Unknown V1LayerParameter layer type: " << type;
+  return "";
+}
+
+ParamSpec* ParamAt(LayerParameter* layer, int i) {
+  while (layer->param_size() <= i) layer->add_param();
+  return layer->mutable_param(i);
+}
+
+// One V1 `layers { ... }` entry as a `layer { ... }` entry: same bottoms, tops, name, rules,
+// blobs and per-type parameter blocks; the enumerated type becomes its string; the parallel
+// per-blob arrays (share name, share mode, learning-rate and decay multipliers) become ParamSpecs.
+void UpgradeV1Layer(const V1LayerParameter& v1, LayerParameter* layer) {
+  layer->Clear();
+  for (int i = 0; i < v1.bottom_size(); ++i) layer->add_bottom(v1.bottom(i));
+  for (int i = 0; i < v1.top_size(); ++i) layer->add_top(v1.top(i));
+  if (v1.has_name()) layer->set_name(v1.name());
+  for (int i = 0; i < v1.include_size(); ++i) layer->add_include()->CopyFrom(v1.include(i));
+  for (int i = 0; i < v1.exclude_size(); ++i) layer->add_exclude()->CopyFrom(v1.exclude(i));
+  if (v1.has_type()) layer->set_type(V1TypeName(static_cast<int>(v1.type())));
+  for (int i = 0; i < v1.blobs_size(); ++i) layer->add_blobs()->CopyFrom(v1.blobs(i));
+  for (int i = 0; i < v1.param_size(); ++i) ParamAt(layer, i)->set_name(v1.param(i));
+  for (int i = 0; i < v1.blob_share_mode_size(); ++i) {
+    const int mode = static_cast<int>(v1.blob_share_mode(i));
+    CHECK(mode == 0 || mode == 1) << "Unknown blob_share_mode: " << mode;
+    ParamAt(layer, i)->set_share_mode(mode == 0 ? ParamSpec_DimCheckMode_STRICT : ParamSpec_DimCheckMode_PERMISSIVE);
+  }
+  for (int i = 0; i < v1.blobs_lr_size(); ++i) ParamAt(layer, i)->set_lr_mult(v1.blobs_lr(i));
+  for (int i = 0; i < v1.weight_decay_size(); ++i) ParamAt(layer, i)->set_decay_mult(v1.weight_decay(i));
+  for (int i = 0; i < v1.loss_weight_size(); ++i) layer->add_loss_weight(v1.loss_weight(i));
+#define MCB200_COPY_BLOCK(field) \
+  if (v1.has_##field()) layer->mutable_##field()->CopyFrom(v1.field())
+  MCB200_COPY_BLOCK(concat_param);
+  MCB200_COPY_BLOCK(convolution_param);
+  MCB200_COPY_BLOCK(dropout_param);
+  MCB200_COPY_BLOCK(eltwise_param);
+  MCB200_COPY_BLOCK(exp_param);
+  MCB200_COPY_BLOCK(inner_product_param);
+  MCB200_COPY_BLOCK(lrn_param);
+  MCB200_COPY_BLOCK(mvn_param);
+  MCB200_COPY_BLOCK(pooling_param);
+  MCB200_COPY_BLOCK(power_param);
+  MCB200_COPY_BLOCK(relu_param);
+  MCB200_COPY_BLOCK(sigmoid_param);
+  MCB200_COPY_BLOCK(softmax_param);
+  MCB200_COPY_BLOCK(slice_param);
+  MCB200_COPY_BLOCK(tanh_param);
+  MCB200_COPY_BLOCK(threshold_param);
+  MCB200_COPY_BLOCK(loss_param);
+#undef MCB200_COPY_BLOCK
+}
+
+// `layers { type: ENUM }` entries (the V1 format) become `layer { type: "String" }` entries in
+// the same order (src/util/upgrade_proto.cpp:61-82).  A file that mixes both is refused.
+void UpgradeV1Net(const string& source, NetParameter* net) {
+  CHECK_EQ(net->layer_size(), 0)
+      << source << ": refusing to upgrade an inconsistent net definition: it has both 'layer' and 'layers' "
+      << "fields. The current format is layer { type: 'Layer' ... }, not layers { type: LAYER ... }";
+  for (int i = 0; i < net->layers_size(); ++i) UpgradeV1Layer(net->layers(i), net->add_layer());
+  net->clear_layers();
+}
+
+}  // namespace
+
 bool UpgradeNetAsNeeded(const string& source, NetParameter* param) {
-  CHECK_EQ(param->layers_size(), 0)
-      << source << ": V1 'layers { type: ENUM }' definitions are not supported by this engine; "
-      << "convert the model to the 'layer { type: \"String\" }' format first";
+  if (param->layers_size() > 0) UpgradeV1Net(source, param);
   if (param->input_size() > 0) UpgradeNetInput(param);
   return true;
 }

@@ -25,8 +25,9 @@ void WriteProtoToBinaryFile(const Message& proto, const char* filename);
 // Rewrites deprecated constructs in place:
 //  * top-level `input:` / `input_shape` / `input_dim` become an "Input" layer
 //    placed first (src/util/upgrade_proto.cpp:271-306);
-//  * V1 `layers { type: CONVOLUTION }` definitions are not supported by this
-//    engine and fail with a clear message.
+//  * V1 `layers { type: CONVOLUTION }` entries become `layer { type: "Convolution" }`
+//    entries (src/util/upgrade_proto.cpp:18-44, 61-262); a definition with both
+//    kinds is refused.
 bool UpgradeNetAsNeeded(const string& source, NetParameter* param);
 void ReadNetParamsFromTextFileOrDie(const string& file, NetParameter* param);
 void ReadNetParamsFromBinaryFileOrDie(const string& file, NetParameter* param);

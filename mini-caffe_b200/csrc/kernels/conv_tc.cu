@@ -66,6 +66,8 @@ constexpr long long kWaitLimitCycles = 2000000000LL;   // about one second
 constexpr int kModeMatrix = 0;   // rows of a plain [m, c] matrix (1x1 convolution, inner product)
 constexpr int kModeIm2col = 1;   // im2col-mode tensor map: any filter, channels % 4 == 0
 constexpr int kModeRows = 2;     // <= 4 channels: one filter row of 8 pixels x 4 channels per k-iteration
+constexpr int kModeHalo = 3;     // stride-1 filters wider than one tap: the taps of a filter row share one pixel strip
+constexpr int kMaxHaloRows = 16; // extra strip rows ((kw - 1) * dilation) the halo mode takes
 
 struct ConvTcArgs {
   float* out;
@@ -87,6 +89,14 @@ struct ConvTcArgs {
   int slots;         // staging slots per epilogue warp: 1 or 2; 2 .. kMaxSlots when a residual is added
   int res_depth;     // residual sub-tiles a warp requests ahead of the one it works on (1 .. slots - 1)
   int out_half;      // the output is stored as bfloat16 (else fp32), whatever the operands are
+  // Halo mode.  The M index runs over a virtual output grid whose rows are `wp` = wo + (kw - 1) *
+  // dil_w positions wide (the last wp - wo positions of a row are computed and never stored), so
+  // that the taps s = 0 .. kw-1 of a filter row are the same strip of `128 + wp - wo` input
+  // pixels read at row offsets s * dil_w.  `m` then counts virtual positions.
+  int wp;
+  int stage_bytes;     // strip slot + kw weight tiles
+  int stage_b_offset;  // where the weight tiles start inside a stage
+  int vec_store;       // plain-store epilogue: rows are 16-byte aligned, use 128-bit accesses
 };
 
 constexpr int kMaxStages = 8;
@@ -109,7 +119,9 @@ struct SmemPlan {
   // barrier wait and a signal (a few hundred cycles of pure latency), so where
   // a K = 32 step is short (narrow tiles) a stage carries two of them.
   // (Row mode has few, odd numbers of k-iterations per tile: single steps.)
-  static constexpr int kSub = (kMode != kModeRows && kTileABytes + kTileBBytes <= 24 * 1024) ? 2 : 1;
+  // Halo mode: a stage is one pixel strip plus the weight tiles of a whole filter row (sized at run time).
+  static constexpr int kSub =
+      (kMode != kModeRows && kMode != kModeHalo && kTileABytes + kTileBBytes <= 24 * 1024) ? 2 : 1;
   static constexpr int kStageBytes = kSub * (kTileABytes + kTileBBytes);
   static constexpr int kStageBOffset = kSub * kTileABytes;   // [A sub-tiles][B sub-tiles]
   static constexpr int staging_bytes(int slots, int slot_bytes) { return kEpilogueWarps * slots * slot_bytes; }
@@ -186,7 +198,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
   const uint32_t raw_addr = smem_addr(smem_raw);
   uint8_t* tiles = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint8_t* staging_base = tiles + stages * Plan::kStageBytes;
+  const int stage_bytes = kMode == kModeHalo ? args.stage_bytes : Plan::kStageBytes;
+  const int stage_b_offset = kMode == kModeHalo ? args.stage_b_offset : Plan::kStageBOffset;
+  uint8_t* staging_base = tiles + stages * stage_bytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -296,6 +310,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           base_w = q * args.stride_w - args.pad_w;
           base_h = p * args.stride_h - args.pad_h;
         }
+        if (kMode == kModeHalo) {
+          // m0 is a position of the virtual output grid (rows of wp positions, stride 1)
+          const int t = m0 / args.wp;
+          base_n = t / args.ho;
+          base_w = m0 - t * args.wp - args.pad_w;
+          base_h = t - base_n * args.ho - args.pad_h;
+        }
         // Position inside the filter, advanced incrementally: channel block,
         // then tap column, then tap row.
         int c0 = 0, sx = 0;
@@ -307,7 +328,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
-          uint8_t* a_dst = tiles + pos.stage * Plan::kStageBytes;
+          uint8_t* a_dst = tiles + pos.stage * stage_bytes;
           uint64_t* bar = &full_bar[pos.stage];
           const uint32_t bar_leader = full_bar_leader + static_cast<uint32_t>(pos.stage) * 8u;
           if (rank == 0u) mbar_expect_tx(bar, announce * static_cast<uint32_t>(nsub));
@@ -318,6 +339,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               // A sub-tile is one filter row: tile_rows pixels x (8 pixels x 4 channels) of a padded input row.
               tma_load_4d(&map_a, bar, a_dst, 0, base_w, row_h, base_n);   // pixels past the row read as zero
               row_h += args.dil_h;
+            } else if (kMode == kModeHalo) {
+              // One strip of 128 + halo pixels x one channel block, at filter row off_h: every tap
+              // of that row reads it (k-iterations run over filter rows x channel blocks).
+              if (kPair) {
+                if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c0, base_w, base_h, base_n, 0, off_h);
+              } else {
+                tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, 0, off_h);
+              }
+              c0 += kElemsK;
+              if (c0 >= args.c_blocks * kElemsK) {
+                c0 = 0;
+                off_h = static_cast<uint16_t>(off_h + args.dil_h);
+              }
             } else if (kMode == kModeIm2col) {
               if (kPair) {
                 if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
@@ -360,15 +394,39 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // A CTA of a pair fetches the half of the weight tile that matches its rank.
         const int n0 = (tile % n_tiles) * BN + static_cast<int>(rank) * Plan::kTileBRows;
         int k0 = 0;
+        int halo_cb = 0, halo_row_k0 = 0;   // halo mode: channel block and first packed-weight column of the filter row
         for (int k = 0; k < args.k_iters; k += Plan::kSub) {
           if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
             alive = false;
             break;
           }
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
-          uint8_t* b_dst = tiles + pos.stage * Plan::kStageBytes + Plan::kStageBOffset;
+          uint8_t* b_dst = tiles + pos.stage * stage_bytes + stage_b_offset;
           uint64_t* bar = &full_bar[pos.stage];
           const uint32_t bar_leader = full_bar_leader + static_cast<uint32_t>(pos.stage) * 8u;
+          if (kMode == kModeHalo) {
+            // The weight tiles of the kw taps of this filter row for this channel block.  Packed
+            // weight columns run [tap][channel block]; tap = row * kw + s.
+            const int row_stride = args.c_blocks * kElemsK;
+            if (rank == 0u) mbar_expect_tx(bar, (kPair ? 2u : 1u) * Plan::kTileBBytes * static_cast<uint32_t>(args.kw));
+            int kcol = halo_row_k0 + halo_cb * kElemsK;
+            for (int s = 0; s < args.kw; ++s) {
+              if (kPair) {
+                tma_load_2d_pair(&map_b, bar_leader, b_dst, kcol, n0);
+              } else {
+                tma_load_2d(&map_b, bar, b_dst, kcol, n0);
+              }
+              kcol += row_stride;
+              b_dst += Plan::kTileBBytes;
+            }
+            if (++halo_cb == args.c_blocks) {
+              halo_cb = 0;
+              halo_row_k0 += args.kw * row_stride;
+            }
+            ++issued;
+            pos.advance(stages);
+            continue;
+          }
           // Rank 0 announces both halves of a paired weight tile.
           if (rank == 0u) mbar_expect_tx(bar, (kPair ? 2u : 1u) * Plan::kTileBBytes * static_cast<uint32_t>(nsub));
 #pragma unroll
@@ -412,11 +470,40 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           tc_fence_after_sync();
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
-          const uint32_t a_addr = tiles_addr + static_cast<uint32_t>(pos.stage * Plan::kStageBytes);
+          const uint32_t a_addr = tiles_addr + static_cast<uint32_t>(pos.stage * stage_bytes);
           uint64_t desc_a = umma_desc_k_sw128(a_addr);
-          uint64_t desc_b = umma_desc_k_sw128(a_addr + Plan::kStageBOffset);
+          uint64_t desc_b = umma_desc_k_sw128(a_addr + stage_b_offset);
+          if (kMode == kModeHalo) {
+            // Tap s of the filter row reads the strip s * dil_w pixel rows (128 bytes each) further
+            // down: the same swizzled bytes, another start address.  The swizzle is a function of
+            // the shared-memory address itself (TMA wrote the strip that way and the tensor core
+            // reads it that way), so a start address that is not a multiple of the 1024-byte
+            // pattern needs nothing else: the descriptor's base-offset field stays 0 (measured:
+            // results equal the im2col mode's; with (address >> 7) & 7 in that field they are wrong).
+            const uint32_t tap_step = static_cast<uint32_t>(args.dil_w) * 128u;
+            for (int s = 0; s < args.kw; ++s) {
+              const uint64_t da = umma_desc_k_sw128(a_addr + static_cast<uint32_t>(s) * tap_step);
+#pragma unroll
+              for (int kk = 0; kk < kMmaPerBlock; ++kk) {
+                if (kHalf) {
+                  if (kPair) {
+                    umma_bf16_pair(tmem_acc, da + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+                  } else {
+                    umma_bf16(tmem_acc, da + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+                  }
+                } else if (kPair) {
+                  umma_tf32_pair(tmem_acc, da + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+                } else {
+                  umma_tf32(tmem_acc, da + 2 * kk, desc_b + 2 * kk, idesc, accumulate);
+                }
+                accumulate = 1u;
+              }
+              desc_b += Plan::kTileBBytes >> 4;
+            }
+          }
 #pragma unroll
           for (int j = 0; j < Plan::kSub; ++j) {
+            if (kMode == kModeHalo) break;
             if (j >= nsub) break;
 #pragma unroll
             for (int kk = 0; kk < kMmaPerBlock; ++kk) {
@@ -548,6 +635,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // First output row (pixel) of this warp's 32-row slice, and how many of the 32 exist.
       const int row0 = (kMode == kModeRows ? row_of(mt) * args.wo + seg_start(mt) : mt * kBlockM) + quad * 32;
       const int rows_here = kMode == kModeRows ? min(args.tile_rows, args.wo - seg_start(mt)) - quad * 32 : args.m - row0;
+      // Row of the output matrix this lane stores in the plain-store epilogue, and whether it exists.
+      int out_row = row0 + lane;
+      bool row_ok = lane < rows_here;
+      if (kMode == kModeHalo) {
+        const int t = out_row / args.wp;           // (image, output row); out_row counts virtual positions
+        const int j = out_row - t * args.wp;
+        row_ok = row_ok && j < args.wo;
+        out_row = t * args.wo + j;
+      }
       // tcgen05.ld is warp-collective: the whole warp takes the same branch.
       alive = __all_sync(0xffffffffu, mbar_wait_bounded(&tmem_full_bar[ab], use, abort, kWaitLimitCycles));
       if (!alive) break;
@@ -738,44 +834,103 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tma_store_commit();
           }
         } else {
-          // ---- plain stores (rows not 16-byte aligned) ----
-          const int row = row0 + lane;
-          if (lane < rows_here) {
-            const size_t out_off = static_cast<size_t>(row) * args.out_ld;
-            const size_t res_off = static_cast<size_t>(row) * ep.residual_ld;
-            auto residual_at = [&](int c) {
-              if (kHalf) {
-                return __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(ep.residual)[res_off + c])
-                                       << 16);
-              }
-              return ep.residual[res_off + c];
-            };
-            auto store_at = [&](int c, float value) {
-              if (args.out_half) {
-                reinterpret_cast<uint16_t*>(args.out)[out_off + c] = static_cast<uint16_t>(pack_bf16x2(value, 0.f));
-              } else {
-                args.out[out_off + c] = value;
-              }
-            };
+          // ---- plain stores: rows that are not 16-byte aligned, and halo mode, whose tiles are
+          // pieces of the virtual output grid (a lane's row may be one of the positions that are
+          // computed and dropped) ----
+          if (row_ok) {
+            const size_t out_off = static_cast<size_t>(out_row) * args.out_ld;
+            const size_t res_off = static_cast<size_t>(out_row) * ep.residual_ld;
+            if (args.vec_store && col0 + 32 <= args.cout) {
+              // A lane owns 32 consecutive outputs of its row: 128 bytes (64 as bfloat16).
+              float4 v[8];
+              auto fill = [&](auto act_tag) {
+                if (!has_res) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int c = col0 + j * 4;
-              if (c >= args.cout) break;
-              float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (has_res) {
-                r.x = residual_at(c);
-                if (c + 1 < args.cout) r.y = residual_at(c + 1);
-                if (c + 2 < args.cout) r.z = residual_at(c + 2);
-                if (c + 3 < args.cout) r.w = residual_at(c + 3);
+                  for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+                } else if (kHalf) {
+                  const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.residual) + res_off + col0);
+                  uint4 w[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) w[q] = rp[q];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    v[2 * q] = finish4(act_tag, 2 * q,
+                                       make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)), true);
+                    v[2 * q + 1] = finish4(act_tag, 2 * q + 1,
+                                           make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
+                                           true);
+                  }
+                } else {
+                  const float4* rp = reinterpret_cast<const float4*>(ep.residual + res_off + col0);
+                  float4 r[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) r[j] = rp[j];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, r[j], true);
+                }
+              };
+              if (act_mode == 1) {
+                fill(ActTag<1>());
+              } else if (act_mode == 0) {
+                fill(ActTag<0>());
+              } else {
+                fill(ActTag<2>());
               }
-              float4 v = act_mode == 1   ? finish4(ActTag<1>(), j, r, has_res)
-                         : act_mode == 0 ? finish4(ActTag<0>(), j, r, has_res)
-                                         : finish4(ActTag<2>(), j, r, has_res);
-              if (ep.round_tf32) round4(v);
-              store_at(c, v.x);
-              if (c + 1 < args.cout) store_at(c + 1, v.y);
-              if (c + 2 < args.cout) store_at(c + 2, v.z);
-              if (c + 3 < args.cout) store_at(c + 3, v.w);
+              if (ep.round_tf32) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) round4(v[j]);
+              }
+              if (args.out_half) {
+                uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + out_off + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 w;
+                  w.x = pack_bf16x2(v[2 * q].x, v[2 * q].y);
+                  w.y = pack_bf16x2(v[2 * q].z, v[2 * q].w);
+                  w.z = pack_bf16x2(v[2 * q + 1].x, v[2 * q + 1].y);
+                  w.w = pack_bf16x2(v[2 * q + 1].z, v[2 * q + 1].w);
+                  op[q] = w;
+                }
+              } else {
+                float4* op = reinterpret_cast<float4*>(args.out + out_off + col0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) op[j] = v[j];
+              }
+            } else {
+              auto residual_at = [&](int c) {
+                if (kHalf) {
+                  return __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(ep.residual)[res_off + c])
+                                         << 16);
+                }
+                return ep.residual[res_off + c];
+              };
+              auto store_at = [&](int c, float value) {
+                if (args.out_half) {
+                  reinterpret_cast<uint16_t*>(args.out)[out_off + c] = static_cast<uint16_t>(pack_bf16x2(value, 0.f));
+                } else {
+                  args.out[out_off + c] = value;
+                }
+              };
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int c = col0 + j * 4;
+                if (c >= args.cout) break;
+                float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (has_res) {
+                  r.x = residual_at(c);
+                  if (c + 1 < args.cout) r.y = residual_at(c + 1);
+                  if (c + 2 < args.cout) r.z = residual_at(c + 2);
+                  if (c + 3 < args.cout) r.w = residual_at(c + 3);
+                }
+                float4 v = act_mode == 1   ? finish4(ActTag<1>(), j, r, has_res)
+                           : act_mode == 0 ? finish4(ActTag<0>(), j, r, has_res)
+                                           : finish4(ActTag<2>(), j, r, has_res);
+                if (ep.round_tf32) round4(v);
+                store_at(c, v.x);
+                if (c + 1 < args.cout) store_at(c + 1, v.y);
+                if (c + 2 < args.cout) store_at(c + 2, v.z);
+                if (c + 3 < args.cout) store_at(c + 3, v.w);
+              }
             }
           }
         }
@@ -910,9 +1065,9 @@ const DriverApi& driver_api() {
 // (operand bytes per iteration grow with BN) plus an epilogue proportional to BN.
 // Wide tiles re-read the activations less often, narrow tiles fill the machine
 // when there are few output pixels; take the cheapest of the three.
-int pick_block_n(int cout, long long m, int k_iters) {
+int pick_block_n(int cout, long long m, int k_iters, double* cost_out = nullptr) {
   const char* force = getenv("MCB200_BLOCK_N");   // "64" / "128" / "256": override for experiments and tests
-  if (force) {
+  if (force && !cost_out) {
     const int bn = atoi(force);
     if (bn == 64 || bn == 128 || bn == 256) return bn;
   }
@@ -930,6 +1085,50 @@ int pick_block_n(int cout, long long m, int k_iters) {
       best_cost = cost;
     }
   }
+  if (cost_out) *cost_out = best_cost;
+  return best;
+}
+
+// Shared memory a CTA can give to the operand ring, roughly (the exact figure depends on the
+// kernel variant's static shared memory; the launch computes it).
+constexpr int kRingBudget = kSharedLimit - 10 * 1024;
+
+// Halo mode: tile width, pairing and cost by the same model (a CTA's time is its operand bytes).
+// A stage holds the pixel strip and the weight tiles of the kw taps of a filter row; widths whose
+// stage does not fit three times are left out.  Returns 0 when no width is usable.
+int pick_block_n_halo(int cout, long long m_virtual, int k_iters, int kw, int strip_bytes, int* pair_out,
+                      double* cost_out) {
+  const char* force = getenv("MCB200_BLOCK_N");
+  const int forced = force ? atoi(force) : 0;
+  const char* force_pair = getenv("MCB200_CTA_PAIR");
+  const long long m_tiles = (m_virtual + kBlockM - 1) / kBlockM;
+  const int strip_slot = (strip_bytes + 1023) / 1024 * 1024;
+  int best = 0;
+  double best_cost = 0.0;
+  for (int bn = 64; bn <= 256; bn *= 2) {
+    if (bn > 64 && bn / 2 >= cout) break;
+    if ((forced == 64 || forced == 128 || forced == 256) && bn != forced) continue;
+    for (int pair = 0; pair <= 1; ++pair) {
+      if (pair && (bn < 128 || m_tiles < 2)) continue;
+      if (force_pair && (force_pair[0] == '0' || force_pair[0] == '1') && bn >= 128 && pair != force_pair[0] - '0')
+        continue;
+      const int stage = strip_slot + kw * (pair ? bn / 2 : bn) * 128;
+      if (kRingBudget / stage < 3) continue;
+      const long long units = pair ? (m_tiles + 1) / 2 : m_tiles;
+      const long long tiles = units * ((cout + bn - 1) / bn);
+      const long long workers = pair ? 74 : 148;
+      const long long waves = (tiles + workers - 1) / workers;
+      // the pair's cluster-wide synchronisation costs about two k-iterations per tile
+      const double per_tile = static_cast<double>(k_iters + (pair ? 2 : 0)) * stage + 8192.0 * (bn / 32);
+      const double cost = static_cast<double>(waves) * per_tile;
+      if (best == 0 || cost < best_cost * 0.97) {
+        best = bn;
+        best_cost = cost;
+        *pair_out = pair;
+      }
+    }
+  }
+  if (cost_out) *cost_out = best_cost;
   return best;
 }
 
@@ -998,7 +1197,7 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   }
   const long long m_tiles = kMode == kModeRows
                                 ? static_cast<long long>(plan->shape.n) * plan->shape.ho * args.row_segments
-                                : (plan->m + kBlockM - 1) / kBlockM;
+                                : (static_cast<long long>(args.m) + kBlockM - 1) / kBlockM;   // halo: virtual positions
   const long long m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
   const long long tiles = static_cast<long long>((plan->shape.cout + BN - 1) / BN) * m_units;
   if (tiles > 0x3fffffffLL) return cudaErrorInvalidConfiguration;
@@ -1024,11 +1223,21 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     if (args.res_depth > args.slots - 1) args.res_depth = args.slots - 1;
   }
   const int slot_bytes = (kHalf && args.out_half) ? 2048 : 4096;
-  int stages = (dynamic_limit - 1024 - Plan::staging_bytes(args.slots, slot_bytes)) / Plan::kStageBytes;
+  int stage_bytes = Plan::kStageBytes;
+  int staging_bytes = Plan::staging_bytes(args.slots, slot_bytes);
+  if (kMode == kModeHalo) {
+    // A stage = the pixel strip (rounded up to the 1024-byte swizzle period) + the weight tiles of
+    // the kw taps of one filter row.  The epilogue stores from registers: no staging.
+    args.stage_b_offset = (args.a_bytes + 1023) / 1024 * 1024;
+    args.stage_bytes = args.stage_b_offset + plan->shape.kw * Plan::kTileBBytes;
+    stage_bytes = args.stage_bytes;
+    staging_bytes = 0;
+  }
+  int stages = (dynamic_limit - 1024 - staging_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   args.stages = stages;
-  const int dynamic_bytes = Plan::dynamic_bytes(args.stages, args.slots, slot_bytes);
+  const int dynamic_bytes = stages * stage_bytes + staging_bytes + 1024;
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
   const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);
@@ -1172,6 +1381,34 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   const bool pointwise = s->kh == 1 && s->kw == 1 && s->stride_h == 1 && s->stride_w == 1 && s->pad_h == 0 &&
                          s->pad_w == 0;
   plan->im2col = pointwise ? 0 : 1;
+  plan->m_virtual = plan->m;
+  plan->strip_rows = 0;
+  // Halo mode for stride-1 filters with more than one tap per row: see ConvTcArgs.  The choice
+  // depends on the layer's geometry only, never on the batch size: the two modes sum over K in
+  // different orders, and an image's result must not depend on how many images run with it.
+  // Taken when the widened rows cost at most half again as many positions (3 x 3 / pad 1 from 4
+  // pixels of width up).
+  const int halo_w = (s->kw - 1) * s->dil_w;
+  const char* halo_env = getenv("MCB200_HALO");   // "0" / "1": override for experiments and tests
+  const bool halo_forced = halo_env && halo_env[0] == '1';
+  if (!pointwise && s->stride_h == 1 && s->stride_w == 1 && s->kw > 1 && halo_w <= kMaxHaloRows &&
+      !(halo_env && halo_env[0] == '0') && (halo_forced || 2 * halo_w <= plan->shape.wo)) {
+    const long long mv = static_cast<long long>(s->n) * plan->shape.ho * (plan->shape.wo + halo_w);
+    const int halo_k_iters = s->kh * plan->c_blocks;
+    int pair = 0;
+    const int bn = mv <= 0x7fffffffLL ? pick_block_n_halo(s->cout, mv, halo_k_iters, s->kw, (kBlockM + halo_w) * 128,
+                                                          &pair, nullptr)
+                                      : 0;
+    if (bn != 0) {
+      plan->im2col = kModeHalo;
+      plan->m_virtual = static_cast<int>(mv);
+      plan->strip_rows = kBlockM + halo_w;
+      plan->k_iters = halo_k_iters;
+      plan->block_n = bn;
+      plan->cta_pair = pair;
+    }
+  }
+  const bool halo = plan->im2col == kModeHalo;
 
   CUtensorMap* ma = reinterpret_cast<CUtensorMap*>(plan->tma_a);
   CUtensorMap* mb = reinterpret_cast<CUtensorMap*>(plan->tma_b);
@@ -1193,10 +1430,12 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
     // Window of base pixels (top-left filter corners): starts at -pad and ends
     // where the last tap still lies inside the padded image.
     const int lower[2] = {-s->pad_w, -s->pad_h};
-    const int upper[2] = {s->pad_w - (s->kw - 1) * s->dil_w, s->pad_h - (s->kh - 1) * s->dil_h};
+    // Halo mode walks every position of the padded row (w + 2 * pad_w of them), not only the wo
+    // positions a filter's left edge can take: the extra ones are the taps' halo.
+    const int upper[2] = {halo ? s->pad_w : s->pad_w - (s->kw - 1) * s->dil_w, s->pad_h - (s->kh - 1) * s->dil_h};
     const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(s->stride_w), static_cast<cuuint32_t>(s->stride_h), 1};
     r = api.im2col(ma, dtype, 4, const_cast<void*>(in), dims, strides, lower, upper,
-                   static_cast<cuuint32_t>(kelems), kBlockM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   static_cast<cuuint32_t>(kelems), halo ? static_cast<cuuint32_t>(plan->strip_rows) : kBlockM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     // Drivers up to CUDA 13.1 encode a flag in im2col descriptors of tensors
     // smaller than 128 KiB that makes the load misbehave; NVIDIA's CUTLASS
@@ -1208,7 +1447,7 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   }
   if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
   {
-    const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kelems;
+    const cuuint64_t kp = static_cast<cuuint64_t>(s->kh) * s->kw * plan->c_blocks * kelems;
     const cuuint64_t dims[2] = {kp, static_cast<cuuint64_t>(s->cout)};
     const cuuint64_t strides[1] = {kp * es};
     // A CTA of a pair fetches half of the weight tile.
@@ -1285,6 +1524,15 @@ int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, co
   const bool res_ok = !a.ep.residual || ((a.ep.residual_ld % (half ? 8 : 4) == 0) && a.ep.residual_ld >= plan->shape.cout &&
                                          ((reinterpret_cast<uintptr_t>(a.ep.residual) & 15) == 0));
   a.tma_epilogue = (out_ok && res_ok) ? 1 : 0;
+  a.vec_store = a.tma_epilogue;
+  a.wp = plan->shape.wo;
+  a.stage_bytes = a.stage_b_offset = 0;
+  if (plan->im2col == kModeHalo) {
+    // Tiles are pieces of the virtual output grid: results leave through plain (128-bit) stores.
+    a.tma_epilogue = 0;
+    a.m = plan->m_virtual;
+    a.wp = plan->m_virtual / (plan->shape.n * plan->shape.ho);
+  }
   if (a.tma_epilogue) {
     const bool rows = plan->im2col == kModeRows;
     const long long per_group = rows ? plan->shape.wo : plan->m;
@@ -1308,18 +1556,21 @@ int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   a.tile_rows = plan->im2col == kModeRows ? (plan->shape.wo < kBlockM ? plan->shape.wo : kBlockM) : kBlockM;
   a.row_segments = plan->im2col == kModeRows ? (plan->shape.wo + a.tile_rows - 1) / a.tile_rows : 1;
-  a.a_bytes = a.tile_rows * kBlockK * 4;
+  a.a_bytes = (plan->im2col == kModeHalo ? plan->strip_rows : a.tile_rows) * kBlockK * 4;
   cudaError_t e = cudaErrorInvalidValue;
   const int mode = plan->im2col;
 #define MCB200_DISPATCH(BN)                                                               \
   e = mode == kModeRows     ? launch_variant<BN, kModeRows, false, false>(plan, a, st)    \
       : mode == kModeIm2col ? launch_variant<BN, kModeIm2col, false, false>(plan, a, st)  \
+      : mode == kModeHalo   ? launch_variant<BN, kModeHalo, false, false>(plan, a, st)    \
                             : launch_variant<BN, kModeMatrix, false, false>(plan, a, st)
 #define MCB200_DISPATCH_PAIR(BN)                                                          \
   e = mode == kModeIm2col ? launch_variant<BN, kModeIm2col, true, false>(plan, a, st)     \
+      : mode == kModeHalo ? launch_variant<BN, kModeHalo, true, false>(plan, a, st)       \
                           : launch_variant<BN, kModeMatrix, true, false>(plan, a, st)
 #define MCB200_DISPATCH_HALF(BN, PAIR)                                                    \
   e = mode == kModeIm2col ? launch_variant<BN, kModeIm2col, PAIR, true>(plan, a, st)      \
+      : mode == kModeHalo ? launch_variant<BN, kModeHalo, PAIR, true>(plan, a, st)        \
                           : launch_variant<BN, kModeMatrix, PAIR, true>(plan, a, st)
   if (half) {
     if (mode == kModeRows) return -3;
@@ -1471,6 +1722,8 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
   plan->m = static_cast<int>(m_ll);
+  plan->m_virtual = plan->m;
+  plan->strip_rows = 0;
   plan->c_blocks = 1;
   plan->k_iters = s->kh;
   plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);

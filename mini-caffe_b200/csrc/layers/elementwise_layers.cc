@@ -126,50 +126,73 @@ REGISTER_LAYER_CLASS(BatchNorm);
 
 // ---------------------------------------------------------------- Scale / Bias
 
+// Shape of a factor blob that spans `num_axes` axes of bottom[0] from `axis` on (-1: to the end).
+static vector<int> BroadcastShape(const Blob& bottom, int axis, int num_axes, const char* what) {
+  CHECK_GE(num_axes, -1) << "num_axes must be non-negative, or -1 to extend to the end of bottom[0]";
+  if (num_axes == -1) return vector<int>(bottom.shape().begin() + axis, bottom.shape().end());
+  CHECK_GE(bottom.num_axes(), axis + num_axes)
+      << what << " blob's shape extends past bottom[0]'s shape when applied starting with bottom[0] axis = " << axis;
+  return vector<int>(bottom.shape().begin() + axis, bottom.shape().begin() + axis + num_axes);
+}
+
+// Checks that `factors` matches bottom[0]'s axes from `axis` on and returns (dim, inner) of
+// y[o, d, i] = f(x[o, d, i], factors[d]).  A blob without axes applies to everything (axis 0).
+static void BroadcastDims(const Blob& bottom, const Blob& factors, int* axis, int* dim, int* inner, const char* what) {
+  if (factors.num_axes() == 0) *axis = 0;
+  CHECK_GE(bottom.num_axes(), *axis + factors.num_axes())
+      << what << " blob's shape extends past bottom[0]'s shape when applied starting with bottom[0] axis = " << *axis;
+  for (int i = 0; i < factors.num_axes(); ++i) {
+    CHECK_EQ(bottom.shape(*axis + i), factors.shape(i))
+        << "dimension mismatch between bottom[0]->shape(" << *axis + i << ") and " << what << "->shape(" << i << ")";
+  }
+  *dim = factors.count();
+  *inner = bottom.count(*axis + factors.num_axes());
+}
+
 void ScaleLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   const ScaleParameter& p = layer_param_.scale_param();
-  CHECK_EQ(bottom.size(), 1u) << "Scale with the factors in a second bottom is not implemented in this engine";
   bias_term_ = p.bias_term();
   const int axis = bottom[0]->CanonicalAxisIndex(p.axis());
-  const int num_axes = p.num_axes();
-  CHECK_GE(num_axes, -1) << "num_axes must be non-negative, or -1 to extend to the end of bottom[0]";
-  vector<int> shape;
-  if (num_axes == -1) {
-    shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().end());
-  } else {
-    CHECK_GE(bottom[0]->num_axes(), axis + num_axes)
-        << "scale blob's shape extends past bottom[0]'s shape when applied starting with bottom[0] axis = " << axis;
-    shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().begin() + axis + num_axes);
-  }
+  const bool learned = bottom.size() == 1;
+  // The factors: a learned blob over `num_axes` axes, or the second bottom.  The optional bias is
+  // always learned and has the factors' shape (src/layers/scale_layer.cpp:13-61).
+  const vector<int> bias_shape = learned ? BroadcastShape(*bottom[0], axis, p.num_axes(), "scale")
+                                         : BroadcastShape(*bottom[0], axis, bottom[1]->num_axes(), "scale");
   if (blobs_.empty()) {
-    blobs_.resize(bias_term_ ? 2 : 1);
-    blobs_[0].reset(new Blob(shape));
-    FillerParameter filler(p.filler());
-    if (!p.has_filler()) {
-      filler.set_type("constant");
-      filler.set_value(1);
+    if (learned) {
+      blobs_.emplace_back(new Blob(bias_shape));
+      FillerParameter filler(p.filler());
+      if (!p.has_filler()) {
+        filler.set_type("constant");
+        filler.set_value(1);
+      }
+      FillBlob(filler, blobs_[0].get());
     }
-    FillBlob(filler, blobs_[0].get());
     if (bias_term_) {
-      blobs_[1].reset(new Blob(shape));
-      FillBlob(p.bias_filler(), blobs_[1].get());
+      blobs_.emplace_back(new Blob(bias_shape));
+      FillBlob(p.bias_filler(), blobs_.back().get());
     }
   } else {
-    CHECK_EQ(blobs_.size(), static_cast<size_t>(bias_term_ ? 2 : 1)) << "Incorrect number of Scale blobs";
+    CHECK_EQ(blobs_.size(), static_cast<size_t>((learned ? 1 : 0) + (bias_term_ ? 1 : 0))) << "Incorrect number of Scale blobs";
   }
-  per_channel_ = axis == 1 && blobs_[0]->num_axes() == 1;
-  CHECK(per_channel_ || blobs_[0]->num_axes() == 0)
-      << "Scale: only per-channel (axis 1, one axis) or scalar factors are implemented in this engine";
+  per_channel_ = learned && axis == 1 && blobs_[0]->num_axes() == 1;
+  scalar_ = learned && blobs_[0]->num_axes() == 0;
+  general_ = !(per_channel_ || scalar_);
 }
 
 void ScaleLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   if (per_channel_) {
     CHECK_EQ(bottom[0]->shape(1), blobs_[0]->shape(0)) << "dimension mismatch between bottom[0]->shape(1) and scale->shape(0)";
   }
+  if (general_) {
+    axis_ = bottom[0]->CanonicalAxisIndex(layer_param_.scale_param().axis());
+    BroadcastDims(*bottom[0], bottom.size() > 1 ? *bottom[1] : *blobs_[0], &axis_, &scale_dim_, &inner_dim_, "scale");
+  }
   ChannelwiseLayer::Reshape(bottom, top);
 }
 
 bool ScaleLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) {
+  if (general_) return false;
   if (per_channel_ && blobs_[0]->count() != channels) return false;
   if (!scale) return true;
   const float* g = blobs_[0]->cpu_data();
@@ -183,40 +206,51 @@ bool ScaleLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::
   return true;
 }
 
+void ScaleLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  if (!general_) {
+    ChannelwiseLayer::Forward_gpu(bottom, top);
+    return;
+  }
+  if (bottom[0]->count() == 0) return;
+  Context& ctx = Context::Get();
+  const float* factors = bottom.size() > 1 ? bottom[1]->gpu_data() : blobs_[0]->gpu_data();
+  const float* bias = bias_term_ ? blobs_.back()->gpu_data() : nullptr;
+  const float* x = bottom[0]->gpu_data();
+  float* y = top[0]->mutable_gpu_data();
+  mcb200_epilogue ep = mcb200_epilogue();
+  KERNEL_CHECK(mcb200_channel_affine_act(x, y, bottom[0]->count(), scale_dim_, inner_dim_, factors, bias, &ep,
+                                         ctx.stream_ptr()));
+}
+
 REGISTER_LAYER_CLASS(Scale);
 
 void BiasLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   const BiasParameter& p = layer_param_.bias_param();
-  CHECK_EQ(bottom.size(), 1u) << "Bias with the offsets in a second bottom is not implemented in this engine";
   const int axis = bottom[0]->CanonicalAxisIndex(p.axis());
-  const int num_axes = p.num_axes();
-  CHECK_GE(num_axes, -1) << "num_axes must be non-negative, or -1 to extend to the end of bottom[0]";
-  if (blobs_.empty()) {
-    vector<int> shape;
-    if (num_axes == -1) {
-      shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().end());
-    } else {
-      CHECK_GE(bottom[0]->num_axes(), axis + num_axes)
-          << "bias blob's shape extends past bottom[0]'s shape when applied starting with bottom[0] axis = " << axis;
-      shape.assign(bottom[0]->shape().begin() + axis, bottom[0]->shape().begin() + axis + num_axes);
-    }
+  const bool learned = bottom.size() == 1;
+  if (learned && blobs_.empty()) {
     blobs_.resize(1);
-    blobs_[0].reset(new Blob(shape));
+    blobs_[0].reset(new Blob(BroadcastShape(*bottom[0], axis, p.num_axes(), "bias")));
     FillBlob(p.filler(), blobs_[0].get());
   }
-  per_channel_ = axis == 1 && blobs_[0]->num_axes() == 1;
-  CHECK(per_channel_ || blobs_[0]->num_axes() == 0)
-      << "Bias: only per-channel (axis 1, one axis) or scalar offsets are implemented in this engine";
+  per_channel_ = learned && axis == 1 && blobs_[0]->num_axes() == 1;
+  scalar_ = learned && blobs_[0]->num_axes() == 0;
+  general_ = !(per_channel_ || scalar_);
 }
 
 void BiasLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   if (per_channel_) {
     CHECK_EQ(bottom[0]->shape(1), blobs_[0]->shape(0)) << "dimension mismatch between bottom[0]->shape(1) and bias->shape(0)";
   }
+  if (general_) {
+    axis_ = bottom[0]->CanonicalAxisIndex(layer_param_.bias_param().axis());
+    BroadcastDims(*bottom[0], bottom.size() > 1 ? *bottom[1] : *blobs_[0], &axis_, &bias_dim_, &inner_dim_, "bias");
+  }
   ChannelwiseLayer::Reshape(bottom, top);
 }
 
 bool BiasLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) {
+  if (general_) return false;
   if (per_channel_ && blobs_[0]->count() != channels) return false;
   if (!scale) return true;
   const float* b = blobs_[0]->cpu_data();
@@ -224,6 +258,19 @@ bool BiasLayer::AsChannelAffine(int channels, std::vector<double>* scale, std::v
   shift->resize(channels);
   for (int c = 0; c < channels; ++c) (*shift)[c] = b[per_channel_ ? c : 0];
   return true;
+}
+
+void BiasLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
+  if (!general_) {
+    ChannelwiseLayer::Forward_gpu(bottom, top);
+    return;
+  }
+  if (bottom[0]->count() == 0) return;
+  Context& ctx = Context::Get();
+  const float* offsets = bottom.size() > 1 ? bottom[1]->gpu_data() : blobs_[0]->gpu_data();
+  mcb200_epilogue ep = mcb200_epilogue();
+  KERNEL_CHECK(mcb200_channel_affine_act(bottom[0]->gpu_data(), top[0]->mutable_gpu_data(), bottom[0]->count(), bias_dim_,
+                                         inner_dim_, nullptr, offsets, &ep, ctx.stream_ptr()));
 }
 
 REGISTER_LAYER_CLASS(Bias);

@@ -171,9 +171,16 @@ class ScaleLayer : public ChannelwiseLayer {
   int MinBottomBlobs() const override { return 1; }
   int MaxBottomBlobs() const override { return 2; }
   bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
  private:
   bool per_channel_ = false;  // learned scale of shape [C] applied on axis 1
+  bool scalar_ = false;       // learned scale with no axes
   bool bias_term_ = false;
+  // Factors in a second bottom, or a learned blob over other axes than the channel axis: the layer
+  // cannot be folded into its producer; y[o, d, i] = x[o, d, i] * scale[d] (+ bias[d]) over the
+  // (N, C, H, W)-ordered data (src/layers/scale_layer.cpp:47,72-113).
+  bool general_ = false;
+  int axis_ = 1, scale_dim_ = 1, inner_dim_ = 1;
 };
 
 class BiasLayer : public ChannelwiseLayer {
@@ -185,8 +192,12 @@ class BiasLayer : public ChannelwiseLayer {
   int MinBottomBlobs() const override { return 1; }
   int MaxBottomBlobs() const override { return 2; }
   bool AsChannelAffine(int channels, std::vector<double>* scale, std::vector<double>* shift) override;
+  void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
  private:
   bool per_channel_ = false;
+  bool scalar_ = false;
+  bool general_ = false;      // offsets in a second bottom or over other axes (src/layers/bias_layer.cpp:40,45-83)
+  int axis_ = 1, bias_dim_ = 1, inner_dim_ = 1;
 };
 
 class ReLULayer : public ChannelwiseLayer {

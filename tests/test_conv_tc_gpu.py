@@ -36,7 +36,7 @@ class ConvPlan(ctypes.Structure):
                 ("block_n", ctypes.c_int), ("im2col", ctypes.c_int), ("out_ld", ctypes.c_int),
                 ("res_ld", ctypes.c_int), ("cta_pair", ctypes.c_int), ("operand_bf16", ctypes.c_int),
                 ("out_bf16", ctypes.c_int), ("out_ptr", ctypes.c_void_p),
-                ("res_ptr", ctypes.c_void_p)]
+                ("res_ptr", ctypes.c_void_p), ("m_virtual", ctypes.c_int), ("strip_rows", ctypes.c_int)]
 
 
 def aligned_plan():
@@ -157,11 +157,13 @@ def test_conv_tc_fused_tail(kernels):
         assert (err <= 2e-2 + 1e-2 * want.abs()).all(), (act, slope, float(err.max()))
 
 
-def _with_planner(block_n, pairing, fn):
-    """Runs fn() with the planner's tile-width and CTA-pair overrides set."""
-    saved = {k: os.environ.get(k) for k in ("MCB200_BLOCK_N", "MCB200_CTA_PAIR")}
+def _with_planner(block_n, pairing, fn, halo="0"):
+    """Runs fn() with the planner's tile-width, CTA-pair and halo-mode overrides set (halo mode is
+    off unless asked for: the tests that compare variants bit for bit need the same K order)."""
+    saved = {k: os.environ.get(k) for k in ("MCB200_BLOCK_N", "MCB200_CTA_PAIR", "MCB200_HALO")}
     os.environ["MCB200_BLOCK_N"] = str(block_n)
     os.environ["MCB200_CTA_PAIR"] = pairing
+    os.environ["MCB200_HALO"] = halo
     try:
         return fn()
     finally:
@@ -314,3 +316,78 @@ def test_conv_tc_bfloat16_storage(kernels, case):
     err = (got - want).abs()
     bound = 2e-5 * float(want.abs().max()) + (want.abs() * 2.0 ** -8 if out_bf16 else 0.0)
     assert (err <= bound).all(), (name, float(err.max()), plan.block_n, plan.cta_pair)
+
+
+HALO_CASES = [
+    # name, N, C, H, W, Cout, k, pad, dil
+    ("cfg1_3x3", 2, 64, 56, 56, 64, 3, 1, 1),
+    ("wide_rows_3x3", 1, 32, 9, 300, 40, 3, 1, 1),       # rows longer than a tile (SSD300's first layers)
+    ("seven_wide", 4, 512, 7, 7, 512, 3, 1, 1),          # 2 of 9 virtual positions per row are dropped
+    ("odd_sizes", 3, 20, 13, 17, 24, 3, 1, 1),           # partial channel block, ragged Cout
+    ("5x5_pad2", 2, 32, 9, 11, 96, 5, 2, 1),
+    ("dilated6", 1, 512, 19, 19, 1024, 3, 6, 6),         # SSD fc6: taps 6 pixel rows apart in the strip
+    ("no_padding", 2, 64, 20, 20, 200, 3, 0, 1),
+    ("one_row", 2, 16, 1, 50, 32, 3, 1, 1),              # H = 1: two of three filter rows read only padding
+]
+
+
+@pytest.mark.parametrize("case", HALO_CASES, ids=[c[0] for c in HALO_CASES])
+def test_halo_mode_matches_fp32(kernels, case):
+    """Halo mode (the taps of a filter row read one shared strip of input pixels at shifted
+    shared-memory addresses; tiles run over a virtual output grid with widened rows) against the
+    same fp64 reference as the im2col mode, for every tile width / pairing it can run with."""
+    name, n, c, h, w, cout, k, pad, dil = case
+    g = torch.Generator().manual_seed(4321)
+    x = torch.randn((n, c, h, w), generator=g)
+    wt = torch.randn((cout, c, k, k), generator=g) * (2.0 / (c * k * k)) ** 0.5
+    want = reference(x, wt, stride=1, pad=pad, dil=dil, scale=None, shift=None, residual=None, res_coeff=1.0, act=0,
+                     slope=0.0, prelu=None)
+    ran = 0
+    for block_n, pairing in ((64, "0"), (128, "0"), (128, "1"), (256, "1")):
+        if block_n > 64 and block_n // 2 >= cout:
+            continue
+        got, plan = _with_planner(block_n, pairing, lambda: run_conv(kernels, x.cuda(), wt, stride=1, pad=pad, dil=dil),
+                                  halo="1")
+        if plan.im2col != 3:       # this width's stage does not fit three times (wide filters): im2col mode ran
+            continue
+        ran += 1
+        assert plan.block_n == block_n and plan.cta_pair == int(pairing)
+        assert plan.strip_rows == 128 + (k - 1) * dil
+        got = got.cpu()
+        assert torch.isfinite(got).all()        # the output was NaN-filled: every element was stored
+        err = (got - want).abs()
+        assert (err <= 2e-2 + 1e-2 * want.abs()).all(), (block_n, pairing, float(err.max()))
+        assert float(err.max() / want.abs().max()) < 2e-3
+    assert ran >= 1
+
+
+def test_halo_mode_fused_tail_and_unaligned_rows(kernels):
+    """Scale / shift / residual / activations through the halo mode's store path, with 16-byte
+    aligned rows (128-bit accesses) and with a channel count that is not a multiple of four
+    (element-wise accesses)."""
+    g = torch.Generator().manual_seed(8)
+    for cout in (200, 70):
+        n, c, h, w = 2, 64, 20, 20
+        x = torch.randn((n, c, h, w), generator=g)
+        wt = torch.randn((cout, c, 3, 3), generator=g) * 0.05
+        scale = torch.rand(cout, generator=g) + 0.5
+        shift = torch.randn(cout, generator=g)
+        res = torch.randn((n, cout, h, w), generator=g)
+        prelu = torch.rand(cout, generator=g) * 0.3
+        for act, slope in ((0, 0.0), (1, 0.0), (1, 0.1), (2, 0.0)):
+            kw = dict(stride=1, pad=1, dil=1, scale=scale, shift=shift, residual=res, res_coeff=0.75, act=act,
+                      slope=slope, prelu=prelu if act == 2 else None)
+            got, plan = _with_planner(128, "0", lambda: run_conv(kernels, x.cuda(), wt, **kw), halo="1")
+            assert plan.im2col == 3
+            want = reference(x, wt, **kw)
+            err = (got.cpu() - want).abs()
+            assert (err <= 2e-2 + 1e-2 * want.abs()).all(), (cout, act, slope, float(err.max()))
+
+
+def test_planner_takes_halo_mode_for_the_benchmark_layers(kernels):
+    """Without overrides the 3 x 3 layers of the benchmark networks run in halo mode."""
+    for n, c, hw, cout in ((32, 64, 56, 64), (8, 128, 28, 128), (8, 256, 14, 256), (8, 512, 7, 512)):
+        x = torch.zeros((n, c, hw, hw), device="cuda")
+        wt = torch.zeros((cout, c, 3, 3))
+        _, plan = run_conv(kernels, x, wt, stride=1, pad=1, dil=1)
+        assert plan.im2col == 3, (c, hw, plan.im2col)

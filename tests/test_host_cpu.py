@@ -295,3 +295,44 @@ def test_net_destroyed_by_another_thread_than_its_creator(capi, engine, owner_al
     own.set_params(weights)
     assert np.array_equal(dict(own.params())["conv_1"].data, weights["conv_1"])
     own.close()
+
+
+V1_NET = """
+name: "v1_style"
+input: "data" input_dim: 2 input_dim: 3 input_dim: 16 input_dim: 16
+layers { name: "conv1" type: CONVOLUTION bottom: "data" top: "conv1" blobs_lr: 1 blobs_lr: 2 weight_decay: 1 weight_decay: 0
+         convolution_param { num_output: 8 kernel_size: 3 pad: 1 } }
+layers { name: "relu1" type: RELU bottom: "conv1" top: "conv1" }
+layers { name: "pool1" type: POOLING bottom: "conv1" top: "pool1" pooling_param { pool: MAX kernel_size: 2 stride: 2 } }
+layers { name: "norm1" type: LRN bottom: "pool1" top: "norm1" lrn_param { local_size: 3 alpha: 0.0001 beta: 0.75 } }
+layers { name: "fc" type: INNER_PRODUCT bottom: "norm1" top: "fc" inner_product_param { num_output: 5 } }
+layers { name: "prob" type: SOFTMAX bottom: "fc" top: "prob" }
+"""
+
+
+def test_v1_layers_definitions_are_upgraded(capi, engine):
+    """`layers { type: ENUM }` files (the format before `layer { type: "String" }`) load like in the
+    reference (src/util/upgrade_proto.cpp:18-44): text definitions and binary weight files."""
+    rng = np.random.default_rng(2)
+    w = rng.standard_normal((8, 3, 3, 3)).astype(np.float32)
+    bias = rng.standard_normal(8).astype(np.float32)
+    # a V1 weight file: NetParameter.layers = 2; V1LayerParameter.name = 4, .type = 5 (CONVOLUTION = 4), .blobs = 6
+    v1_layer = _len(4, b"conv1") + _field(5, 0, _varint(4)) + _len(6, encode_blob(w, legacy=True)) + \
+        _len(6, encode_blob(bias, legacy=True))
+    model = _len(1, b"v1_weights") + _len(2, v1_layer)
+    net = capi.Net(engine, V1_NET, model, from_buffer=True)
+    blobs = dict(net.blobs())
+    assert blobs["data"].shape == (2, 3, 16, 16)
+    assert blobs["pool1"].shape == (2, 8, 8, 8) and blobs["norm1"].shape == (2, 8, 8, 8)
+    assert blobs["prob"].shape == (2, 5)
+    params = dict(net.params())
+    assert np.array_equal(params["conv1_0"].data, w) and np.array_equal(params["conv1_1"].data, bias)
+    assert params["fc_0"].shape == (5, 8 * 8 * 8)
+    net.close()
+
+
+def test_mixed_v1_and_current_layer_definitions_are_refused(capi, engine):
+    text = V1_NET + 'layer { name: "extra" type: "ReLU" bottom: "fc" top: "fc" }\n'
+    with pytest.raises(capi.CaffeError) as err:
+        capi.Net(engine, text, None, from_buffer=True)
+    assert "both 'layer' and 'layers'" in str(err.value)

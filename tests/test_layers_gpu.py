@@ -235,3 +235,33 @@ def test_resnet50_batch16(capi, gpu_engine, reflib):
     top = np.sort(want["fc1000"], axis=1)
     clear = (top[:, -1] - top[:, -2]) > 2e-2 * np.abs(top[:, -1])
     assert (np.argmax(got["fc1000"], 1)[clear] == np.argmax(want["fc1000"], 1)[clear]).all()
+
+
+def test_scale_and_bias_with_the_factors_in_a_second_bottom(capi, gpu_engine, reflib):
+    """Scale / Bias whose factors are data (a second bottom) or a learned blob over other axes than
+    the channel axis (src/layers/scale_layer.cpp:47,72-113, bias_layer.cpp:40,45-83): per channel,
+    per (image, channel), per (channel, row, column), scalar."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("scale2")
+    b.input([("data", (2, 6, 5, 8)), ("per_channel", (6,)), ("per_image_channel", (2, 6)), ("per_pixel", (6, 5, 8))])
+    b.conv("c", "data", "c", 6, 6, 3, pad=1)                                   # a tensor-core layer in front
+    b.raw("s_ch", "Scale", ["c", "per_channel"], ["s_ch"], "scale_param { axis: 1 }")
+    b.raw("s_nc", "Scale", ["c", "per_image_channel"], ["s_nc"], "scale_param { axis: 0 bias_term: true }")
+    b.params.append(("s_nc_0", (2, 6), "uniform", 0))                          # the learned bias over (image, channel)
+    b.raw("s_px", "Scale", ["s_ch", "per_pixel"], ["s_px"], "scale_param { axis: 1 }")
+    b.raw("b_ch", "Bias", ["s_px", "per_channel"], ["b_ch"], "bias_param { axis: 1 }")
+    b.raw("b_nc", "Bias", ["b_ch", "per_image_channel"], ["b_nc"], "bias_param { axis: 0 }")
+    b.raw("s_all", "Scale", ["b_nc"], ["s_all"], "scale_param { axis: 0 num_axes: -1 bias_term: true }")
+    b.params.append(("s_all_0", (2, 6, 5, 8), "uniform", 0))                   # learned, one factor per element
+    b.params.append(("s_all_1", (2, 6, 5, 8), "uniform", 0))
+    b.raw("s_one", "Scale", ["s_all"], ["s_one"], "scale_param { num_axes: 0 filler { value: 3 } }")
+    weights = wl.init_params(b.params, seed=5)
+    rng = np.random.default_rng(6)
+    x = {"data": rng.standard_normal((2, 6, 5, 8)).astype(np.float32),
+         "per_channel": rng.uniform(0.5, 1.5, (6,)).astype(np.float32),
+         "per_image_channel": rng.uniform(-1.0, 1.0, (2, 6)).astype(np.float32),
+         "per_pixel": rng.uniform(0.5, 1.5, (6, 5, 8)).astype(np.float32)}
+    outs = ["s_ch", "s_nc", "s_px", "b_ch", "b_nc", "s_all", "s_one"]
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, outs, marks=outs)
+    for name in outs:
+        assert_close(got[name], want[name], name)
