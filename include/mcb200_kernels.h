@@ -111,6 +111,19 @@ int mcb200_conv_tc_plan(const mcb200_conv_shape* s, const float* in, const float
 int mcb200_conv_tc_launch(mcb200_conv_plan* plan, float* out, int out_ld,
                           const mcb200_epilogue* ep, int* status, void* stream);
 
+/* Every wait of the convolution kernel on a hardware barrier is bounded: after `cycles` SM clock
+ * cycles (default 2e9, about a second) the CTA raises an abort flag, its roles leave their loops,
+ * copies in flight get a bounded grace period, tensor memory is freed and *status is set to 1;
+ * the launch returns normally and the context stays usable.  Sets the bound for later launches
+ * of the process and returns the previous one (cycles <= 0 restores the default).
+ * (No counterpart in mini-caffe, whose kernels have no device-side waits.)                     */
+long long mcb200_conv_set_wait_limit(long long cycles);
+/* Test hook: in the calling thread's next convolution launch the weight producer leaves out the
+ * loads of the last k-iteration of its last tile, so that nothing ever completes that stage's
+ * barrier and the bounded waits above run out.  This is how the abort path is exercised
+ * without faulting, trapping or hanging anything; combine with a short wait limit.            */
+void mcb200_conv_test_drop_weight_load(void);
+
 /* bfloat16 storage (opt-in; the reference computes in fp32 throughout, so these
  * have no counterpart there).  Activations, the packed weights and the residual
  * are bfloat16, the tensor cores run tcgen05.mma kind::f16 with fp32
@@ -163,6 +176,16 @@ int mcb200_conv_direct(const mcb200_conv_shape* s, const float* in, const float*
 int mcb200_dw_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed, void* stream);
 int mcb200_conv_depthwise(const mcb200_conv_shape* s, const float* in, const float* packed_w, float* out,
                           const mcb200_epilogue* ep, void* stream);
+
+/* The same layer for 3 x 3 filters, dilation 1, stride 1 or 2, fp32 in and out, with the input
+ * staged in shared memory by TMA (tiles of 8 x 16 output pixels x 32 channels, zero fill outside
+ * the image, two boxes per CTA in flight): what a CTA has in flight no longer depends on its
+ * registers.  `status` (device int, may be NULL) is set to 1 if a bounded wait on a box runs out.
+ * No fused residual (mcb200_conv_depthwise takes those).  Replaces the same reference code,
+ * src/layers/conv_dw_layer.cpp:104-152.                                                  */
+int mcb200_conv_depthwise_tma_supported(const mcb200_conv_shape* s);
+int mcb200_conv_depthwise_tma(const mcb200_conv_shape* s, const float* in, const float* packed_w, float* out,
+                              const mcb200_epilogue* ep, int* status, void* stream);
 /* The 3x3 (dilation 1, stride 1 or 2) case with bfloat16 activations on either
  * side, for nets that store their activations as bfloat16: `in` / `out` hold
  * bfloat16 cells when the matching flag is set, fp32 otherwise; weights and
@@ -375,6 +398,20 @@ int mcb200_psroi_pool(const float* data_nchw, const float* rois, float* out, int
 int mcb200_deconv_out_shape(mcb200_conv_shape* s);
 int mcb200_deconv_direct(const mcb200_conv_shape* s, const float* in_nchw, const float* w_iohw, const float* bias,
                          float* out_nchw, void* stream);
+
+/* Deconvolution on the tensor-core convolution kernel.  A transposed convolution with stride s
+ * is the stride-1 convolution, with the filter's taps reversed and padding dil*(k-1) - pad, of the
+ * input with its pixels spread s apart over zeros (what col2im's scatter-add computes, read from
+ * the output's side; src/layers/deconv_layer.cpp:27-44, src/util/im2col.cpp:57-90).
+ *   mcb200_deconv_as_conv_shape  the equivalent convolution's shape (input = the spread tensor,
+ *                                c_stride = c rounded up to 4); -3 when pad exceeds dil*(k-1)
+ *   mcb200_deconv_spread_input   channels-last input (c floats per pixel) -> the spread tensor
+ *   mcb200_deconv_flip_weights   [c, cout/g, kh, kw] -> [cout, c/g, kh, kw], taps reversed
+ * followed by mcb200_conv_pack_weights / mcb200_conv_tc_plan / mcb200_conv_tc_launch on that
+ * shape (groups included).                                                              */
+int mcb200_deconv_as_conv_shape(const mcb200_conv_shape* deconv, mcb200_conv_shape* conv);
+int mcb200_deconv_spread_input(const mcb200_conv_shape* deconv, const float* in_nhwc, float* spread, void* stream);
+int mcb200_deconv_flip_weights(const mcb200_conv_shape* deconv, const float* w_iohw, float* w_oihw, void* stream);
 
 /* Crop: out[idx] = in[idx + offsets] over up to six axes
  * (src/layers/crop_layer.cpp:57-100).                                         */

@@ -48,6 +48,13 @@ long long mcb200_kernel_timing_end_each(double* total_ms, double* each_ms, long 
  * aligned, device memory; keep it below the L2 size to measure L2 -> shared memory),
  * `stages` (1..8) loads in flight per SM.  *gbs is the aggregate rate of the
  * quickest of `reps` launches after one launch that warms the cache.             */
+/* Diagnostic build only (`make -C mini-caffe_b200/csrc trace` -> lib/libcaffe_trace.so): the
+ * convolution kernel's roles of CTA 0 stamp the SM's cycle counter at fixed points of their loops
+ * (activation producer, weight producer, MMA issuer: two stamps per k-iteration; first epilogue
+ * warp: two per tile).  Copies 4 x 2048 values (role-major, zero where nothing was recorded) to
+ * `out`, clears the device array and returns 2048; the ordinary library returns 0.              */
+int mcb200_conv_trace_read(long long* out);
+
 int mcb200_probe_mma_peak(int bf16, int block_n, int cta_pair, int steps, int reps, double* ms, double* tflops,
                           void* stream);
 int mcb200_probe_tma_l2_pull(void* buffer, size_t bytes, int loads_per_cta, int stages, int reps, double* ms,

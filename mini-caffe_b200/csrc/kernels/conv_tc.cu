@@ -61,7 +61,7 @@ constexpr int kWarpLoadB = 2;
 constexpr int kFirstEpilogueWarp = 3;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;   // 352
-constexpr long long kWaitLimitCycles = 2000000000LL;   // about one second
+constexpr long long kDefaultWaitLimitCycles = 2000000000LL;   // about one second
 // How the activation tile of a k-iteration is fetched.
 constexpr int kModeMatrix = 0;   // rows of a plain [m, c] matrix (1x1 convolution, inner product)
 constexpr int kModeIm2col = 1;   // im2col-mode tensor map: any filter, channels % 4 == 0
@@ -97,7 +97,36 @@ struct ConvTcArgs {
   int stage_bytes;     // strip slot + kw weight tiles
   int stage_b_offset;  // where the weight tiles start inside a stage
   int vec_store;       // plain-store epilogue: rows are 16-byte aligned, use 128-bit accesses
+  // Grouped convolution (group_cout > 0): output columns [g * group_cout, (g + 1) * group_cout)
+  // read input channels [g * group_cin, (g + 1) * group_cin).  An N tile multiplies the channels
+  // its groups span (from `c_origin`, rounded down to 16 bytes) by a block-diagonal weight tile:
+  // the packed weights hold zeros where an output column's group does not own the channel.
+  int group_cout, group_cin;
+  int l2_prefetch;               // ask L2 for the next tile's activations a tile ahead
+  int halo_staged;               // halo mode: results pass through a shared-memory slot so that the stores are
+                                 // whole 128-byte rows (fp32 output with 16-byte aligned rows)
+  long long wait_limit;          // bound of every barrier wait, in SM cycles
+  int drop_last_weight_load;     // test hook: the weight producer leaves out its last k-iteration (see
+                                 // mcb200_conv_test_drop_weight_load): the waits on that stage run out
 };
+
+// Optional cycle-counter trace (build with -DMCB200_CONV_TRACE): the single-thread roles and the
+// first epilogue warp of CTA 0 stamp clock64() at fixed points of their loops into a device
+// array that mcb200_conv_trace_read copies out.  Role 0: activation producer (per k-iteration:
+// stage free, loads issued); 1: weight producer (same); 2: MMA issuer (per k-iteration: stage
+// full, MMAs issued and committed); 3: epilogue warp 0 (per tile: accumulator ready, tile stored).
+#ifdef MCB200_CONV_TRACE
+constexpr int kTraceSlots = 2048;
+__device__ long long g_conv_trace[4 * kTraceSlots];
+#define MCB200_TRACE_DECL int trace_n = 0
+#define MCB200_TRACE(role)                                                                         \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && trace_n < kTraceSlots) g_conv_trace[(role) * kTraceSlots + trace_n++] = clock64(); \
+  } while (0)
+#else
+#define MCB200_TRACE_DECL
+#define MCB200_TRACE(role)
+#endif
 
 constexpr int kMaxStages = 8;
 constexpr int kMaxSlots = 4;     // every barrier here is static shared memory that the operand ring cannot use
@@ -181,6 +210,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int kElemsK = kHalf ? kBlockKHalf : kBlockK;   // channels per k-iteration
   const int stages = args.stages;
   const int slots = args.slots;
+  const long long wait_limit = args.wait_limit;   // SM cycles a barrier wait may take before the CTA gives up
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[kMaxStages];    // both operand tiles of a stage have landed (two producers)
@@ -270,7 +300,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int j = first; j < issued; ++j) {
       const long long start = clock64();
       while (!mbar_try_wait(&full_bar[j % stages], static_cast<uint32_t>(j / stages) & 1u)) {
-        if (clock64() - start > kWaitLimitCycles / 8) break;
+        if (clock64() - start > wait_limit / 8) break;
       }
     }
   };
@@ -283,6 +313,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       RingPos pos;
       int issued = 0;
       bool alive = true;
+      MCB200_TRACE_DECL;
       const uint32_t a_bytes = static_cast<uint32_t>(args.a_bytes);
       for (int tile = worker; tile < num_tiles && alive; tile += workers) {
         const int mt = unit_to_mt(tile / n_tiles);
@@ -317,16 +348,66 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           base_w = m0 - t * args.wp - args.pad_w;
           base_h = t - base_n * args.ho - args.pad_h;
         }
+        // First channel the tile's weight columns refer to (grouped layers: the first channel of
+        // the first group the N tile touches, rounded down to a 16-byte boundary of the pixel).
+        int c_origin = 0;
+        if (args.group_cout > 0) {
+          const int n0 = (tile % n_tiles) * BN;
+          c_origin = ((n0 / args.group_cout) * args.group_cin) & ~((kHalf ? 8 : 4) - 1);
+        }
+        // The activations of this CTA's next tile are asked for now, a tile ahead (L2 prefetch, no
+        // shared memory, nothing to wait for).  A tile always brings pixels nobody has read yet,
+        // the ring looks only a few stages ahead, and a load that waits for DRAM holds up the whole
+        // in-order ring behind it.  Of the CTAs that share an M tile (one per N tile) the one
+        // with N tile 0 asks; grouped layers read other channels per N tile, so there every CTA asks.
+        if (args.l2_prefetch && kMode != kModeRows) {
+          const int next = tile + workers;
+          const int n_index = next % n_tiles;
+          const int mt2 = next < num_tiles ? unit_to_mt(next / n_tiles) : m_tiles;
+          if (mt2 < m_tiles && (n_index == 0 || args.group_cout > 0)) {
+            const int origin2 = args.group_cout > 0
+                                    ? (((n_index * BN) / args.group_cout) * args.group_cin) & ~((kHalf ? 8 : 4) - 1)
+                                    : 0;
+            const int v2 = mt2 * kBlockM;
+            if (kMode == kModeMatrix) {
+              for (int cb = 0; cb < args.c_blocks; ++cb) tma_prefetch_2d(&map_a, origin2 + cb * kElemsK, v2);
+            } else {
+              int w2, h2, n2;
+              if (kMode == kModeHalo) {
+                const int t2 = v2 / args.wp;
+                n2 = t2 / args.ho;
+                w2 = v2 - t2 * args.wp - args.pad_w;
+                h2 = t2 - n2 * args.ho - args.pad_h;
+              } else {
+                n2 = v2 / (args.wo * args.ho);
+                w2 = (v2 % args.wo) * args.stride_w - args.pad_w;
+                h2 = ((v2 / args.wo) % args.ho) * args.stride_h - args.pad_h;
+              }
+              const int kh = kMode == kModeHalo ? args.k_iters / args.c_blocks : args.k_iters / (args.c_blocks * args.kw);
+              // im2col mode: the middle tap column of every filter row touches (nearly) every pixel
+              // the other columns touch; with a stride, its neighbour column takes the pixels between.
+              const int s_mid = kMode == kModeHalo ? 0 : args.kw / 2;
+              const int s_count = (kMode == kModeIm2col && args.stride_w > 1 && args.kw > 1) ? 2 : 1;
+              for (int r = 0; r < kh; ++r)
+                for (int sc = 0; sc < s_count; ++sc)
+                  for (int cb = 0; cb < args.c_blocks; ++cb)
+                    tma_prefetch_im2col_4d(&map_a, origin2 + cb * kElemsK, w2, h2, n2,
+                                           static_cast<uint16_t>(min(s_mid + sc, args.kw - 1) * args.dil_w),
+                                           static_cast<uint16_t>(r * args.dil_h));
+            }
+          }
+        }
         // Position inside the filter, advanced incrementally: channel block,
         // then tap column, then tap row.
         int c0 = 0, sx = 0;
         uint16_t off_w = 0, off_h = 0;
         int row_h = base_h;
         for (int k = 0; k < args.k_iters; k += Plan::kSub) {
-          if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
+          if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, wait_limit)) {
             alive = false;
             break;
           }
+          MCB200_TRACE(0);
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
           uint8_t* a_dst = tiles + pos.stage * stage_bytes;
           uint64_t* bar = &full_bar[pos.stage];
@@ -343,9 +424,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               // One strip of 128 + halo pixels x one channel block, at filter row off_h: every tap
               // of that row reads it (k-iterations run over filter rows x channel blocks).
               if (kPair) {
-                if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c0, base_w, base_h, base_n, 0, off_h);
+                if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c_origin + c0, base_w, base_h, base_n, 0, off_h);
               } else {
-                tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, 0, off_h);
+                tma_load_im2col_4d(&map_a, bar, a_dst, c_origin + c0, base_w, base_h, base_n, 0, off_h);
               }
               c0 += kElemsK;
               if (c0 >= args.c_blocks * kElemsK) {
@@ -354,9 +435,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             } else if (kMode == kModeIm2col) {
               if (kPair) {
-                if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
+                if (live) tma_load_im2col_4d_pair(&map_a, bar_leader, a_dst, c_origin + c0, base_w, base_h, base_n, off_w, off_h);
               } else {
-                tma_load_im2col_4d(&map_a, bar, a_dst, c0, base_w, base_h, base_n, off_w, off_h);
+                tma_load_im2col_4d(&map_a, bar, a_dst, c_origin + c0, base_w, base_h, base_n, off_w, off_h);
               }
               c0 += kElemsK;
               if (c0 >= args.c_blocks * kElemsK) {
@@ -370,14 +451,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             } else {
               if (kPair) {
-                if (live) tma_load_2d_pair(&map_a, bar_leader, a_dst, c0, m0);
+                if (live) tma_load_2d_pair(&map_a, bar_leader, a_dst, c_origin + c0, m0);
               } else {
-                tma_load_2d(&map_a, bar, a_dst, c0, m0);
+                tma_load_2d(&map_a, bar, a_dst, c_origin + c0, m0);
               }
               c0 += kElemsK;
             }
             a_dst += kTileABytes;
           }
+          MCB200_TRACE(0);
           ++issued;
           pos.advance(stages);
         }
@@ -390,14 +472,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       RingPos pos;
       int issued = 0;
       bool alive = true;
+      MCB200_TRACE_DECL;
       for (int tile = worker; tile < num_tiles && alive; tile += workers) {
         // A CTA of a pair fetches the half of the weight tile that matches its rank.
         const int n0 = (tile % n_tiles) * BN + static_cast<int>(rank) * Plan::kTileBRows;
         int k0 = 0;
         int halo_cb = 0, halo_row_k0 = 0;   // halo mode: channel block and first packed-weight column of the filter row
         for (int k = 0; k < args.k_iters; k += Plan::kSub) {
-          if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, kWaitLimitCycles)) {
+          if (!mbar_wait_bounded(&empty_bar[pos.stage], pos.parity ^ 1u, abort, wait_limit)) {
             alive = false;
+            break;
+          }
+          MCB200_TRACE(1);
+          if (args.drop_last_weight_load && tile + workers >= num_tiles && k + Plan::kSub >= args.k_iters) {
+            alive = false;   // nothing arrives on this stage's barrier: every role's wait on it is bounded
             break;
           }
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
@@ -423,6 +511,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               halo_cb = 0;
               halo_row_k0 += args.kw * row_stride;
             }
+            MCB200_TRACE(1);
             ++issued;
             pos.advance(stages);
             continue;
@@ -440,6 +529,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             k0 += kElemsK;
             b_dst += Plan::kTileBBytes;
           }
+          MCB200_TRACE(1);
           ++issued;
           pos.advance(stages);
         }
@@ -454,21 +544,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       RingPos pos;
       int local = 0;   // tiles done by this CTA
       bool alive = true;
+      MCB200_TRACE_DECL;
       const uint32_t tiles_addr = smem_addr(tiles);
       for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
         const int ab = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
         // The epilogue must have drained this accumulator (first use passes).
-        if (!mbar_wait_bounded(&tmem_empty_bar[ab], use ^ 1u, abort, kWaitLimitCycles)) break;
+        if (!mbar_wait_bounded(&tmem_empty_bar[ab], use ^ 1u, abort, wait_limit)) break;
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(ab * BN);
         uint32_t accumulate = 0;
         for (int k = 0; k < args.k_iters; k += Plan::kSub) {
-          if (!mbar_wait_bounded(&full_bar[pos.stage], pos.parity, abort, kWaitLimitCycles)) {
+          if (!mbar_wait_bounded(&full_bar[pos.stage], pos.parity, abort, wait_limit)) {
             alive = false;
             break;
           }
           tc_fence_after_sync();
+          MCB200_TRACE(2);
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
           const uint32_t a_addr = tiles_addr + static_cast<uint32_t>(pos.stage * stage_bytes);
           uint64_t desc_a = umma_desc_k_sw128(a_addr);
@@ -530,6 +622,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           } else {
             umma_commit(&empty_bar[pos.stage]);
           }
+          MCB200_TRACE(2);
           pos.advance(stages);
         }
         if (alive) {
@@ -624,6 +717,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int seq = 0;
     int local = 0;
     bool alive = true;
+    MCB200_TRACE_DECL;
     int table_n0[2] = {-1, -1};          // first column the per-column tables were filled for
     uint32_t table_fills[2] = {0u, 0u};
     for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
@@ -645,9 +739,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         out_row = t * args.wo + j;
       }
       // tcgen05.ld is warp-collective: the whole warp takes the same branch.
-      alive = __all_sync(0xffffffffu, mbar_wait_bounded(&tmem_full_bar[ab], use, abort, kWaitLimitCycles));
+      alive = __all_sync(0xffffffffu, mbar_wait_bounded(&tmem_full_bar[ab], use, abort, wait_limit));
       if (!alive) break;
       tc_fence_after_sync();
+      if (ew == 0 && lane == 0) MCB200_TRACE(3);
       // Per-column constants of the tile's columns go to shared memory, so that the
       // inner loops are a broadcast 16-byte load and fused multiply-adds.  Two
       // copies (tile parity), each kept while the CTA's tiles of that parity stay
@@ -670,7 +765,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // named barrier, so that the wait is bounded like every other one).
         __syncwarp();
         if (lane == 0) mbar_arrive(&col_bar[ab]);
-        alive = __all_sync(0xffffffffu, mbar_wait_bounded(&col_bar[ab], table_fills[ab] & 1u, abort, kWaitLimitCycles));
+        alive = __all_sync(0xffffffffu, mbar_wait_bounded(&col_bar[ab], table_fills[ab] & 1u, abort, wait_limit));
         if (!alive) break;
         ++table_fills[ab];
         table_n0[ab] = n0;
@@ -741,7 +836,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               issue_residual();
             }
             alive = __all_sync(0xffffffffu,
-                               mbar_wait_bounded(&res_bar[ew][slot], cur_parity, abort, kWaitLimitCycles));
+                               mbar_wait_bounded(&res_bar[ew][slot], cur_parity, abort, wait_limit));
             if (!alive) break;
             if (++cur_slot == slots) {
               cur_slot = 0;
@@ -837,49 +932,72 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // ---- plain stores: rows that are not 16-byte aligned, and halo mode, whose tiles are
           // pieces of the virtual output grid (a lane's row may be one of the positions that are
           // computed and dropped) ----
-          if (row_ok) {
-            const size_t out_off = static_cast<size_t>(out_row) * args.out_ld;
-            const size_t res_off = static_cast<size_t>(out_row) * ep.residual_ld;
-            if (args.vec_store && col0 + 32 <= args.cout) {
-              // A lane owns 32 consecutive outputs of its row: 128 bytes (64 as bfloat16).
-              float4 v[8];
-              auto fill = [&](auto act_tag) {
-                if (!has_res) {
+          const size_t out_off = static_cast<size_t>(row_ok ? out_row : 0) * args.out_ld;
+          const size_t res_off = static_cast<size_t>(row_ok ? out_row : 0) * ep.residual_ld;
+          const bool whole_chunk = args.vec_store && col0 + 32 <= args.cout;
+          // The lane's 32 outputs of its row (128 bytes, 64 as bfloat16), fused tail applied.
+          float4 v[8];
+          if (whole_chunk && (row_ok || (kMode == kModeHalo && args.halo_staged))) {
+            const bool add_res = has_res && row_ok;
+            auto fill = [&](auto act_tag) {
+              if (!add_res) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, make_float4(0.f, 0.f, 0.f, 0.f), false);
-                } else if (kHalf) {
-                  const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.residual) + res_off + col0);
-                  uint4 w[4];
+                for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, make_float4(0.f, 0.f, 0.f, 0.f), false);
+              } else if (kHalf) {
+                const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.residual) + res_off + col0);
+                uint4 w[4];
 #pragma unroll
-                  for (int q = 0; q < 4; ++q) w[q] = rp[q];
+                for (int q = 0; q < 4; ++q) w[q] = rp[q];
 #pragma unroll
-                  for (int q = 0; q < 4; ++q) {
-                    v[2 * q] = finish4(act_tag, 2 * q,
-                                       make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)), true);
-                    v[2 * q + 1] = finish4(act_tag, 2 * q + 1,
-                                           make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
-                                           true);
-                  }
-                } else {
-                  const float4* rp = reinterpret_cast<const float4*>(ep.residual + res_off + col0);
-                  float4 r[8];
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) r[j] = rp[j];
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, r[j], true);
+                for (int q = 0; q < 4; ++q) {
+                  v[2 * q] = finish4(act_tag, 2 * q,
+                                     make_float4(bf16_lo(w[q].x), bf16_hi(w[q].x), bf16_lo(w[q].y), bf16_hi(w[q].y)), true);
+                  v[2 * q + 1] = finish4(act_tag, 2 * q + 1,
+                                         make_float4(bf16_lo(w[q].z), bf16_hi(w[q].z), bf16_lo(w[q].w), bf16_hi(w[q].w)),
+                                         true);
                 }
-              };
-              if (act_mode == 1) {
-                fill(ActTag<1>());
-              } else if (act_mode == 0) {
-                fill(ActTag<0>());
               } else {
-                fill(ActTag<2>());
-              }
-              if (ep.round_tf32) {
+                const float4* rp = reinterpret_cast<const float4*>(ep.residual + res_off + col0);
+                float4 r[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) round4(v[j]);
+                for (int j = 0; j < 8; ++j) r[j] = rp[j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = finish4(act_tag, j, r[j], true);
               }
+            };
+            if (act_mode == 1) {
+              fill(ActTag<1>());
+            } else if (act_mode == 0) {
+              fill(ActTag<0>());
+            } else {
+              fill(ActTag<2>());
+            }
+            if (ep.round_tf32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) round4(v[j]);
+            }
+          }
+          if (kMode == kModeHalo && args.halo_staged && whole_chunk) {
+            // Through the warp's shared-memory slot, so that a store instruction writes four whole
+            // 128-byte rows (eight lanes each) instead of 16 bytes of 32 different rows: a lane's
+            // own row may be a dropped position, its neighbours' rows are not.
+            float* slot = slot_ptr(0);
+            const int swz = lane & 7;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(slot + lane * 32 + ((j ^ swz) << 2)) = v[j];
+            __syncwarp();
+            const int piece = lane & 7;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+              const int r = 4 * p + (lane >> 3);
+              const int orow = __shfl_sync(0xffffffffu, out_row, r);
+              const int ok = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, r);
+              const float4 val = *reinterpret_cast<const float4*>(slot + r * 32 + ((piece ^ (r & 7)) << 2));
+              if (ok) *reinterpret_cast<float4*>(args.out + static_cast<size_t>(orow) * args.out_ld + col0 + piece * 4) = val;
+            }
+            __syncwarp();   // the slot is rewritten by the next chunk
+          } else if (row_ok) {
+            if (whole_chunk) {
               if (args.out_half) {
                 uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + out_off + col0);
 #pragma unroll
@@ -936,6 +1054,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       // All of this warp's reads of the accumulator are complete: hand it back.
+      if (ew == 0 && lane == 0) MCB200_TRACE(3);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -1020,6 +1139,52 @@ __global__ void bf16_to_f32_kernel(const uint2* __restrict__ src, float4* __rest
   }
   for (size_t i = quads * 4 + first; i < count; i += stride)
     dst1[i] = __uint_as_float(static_cast<uint32_t>(src1[i]) << 16);
+}
+
+// ------------------------------------------------------------------ grouped layers
+
+// Grouped layers run with 64-column N tiles (the narrowest: the fewest foreign channels under a
+// tile's weight columns).  First channel an N tile's weight columns refer to, and how many
+// channel blocks the widest tile spans.
+constexpr int kGroupedBlockN = 64;
+
+__host__ __device__ inline int grouped_origin(int n0, int group_cout, int group_cin, int align) {
+  return ((n0 / group_cout) * group_cin) & ~(align - 1);
+}
+
+int grouped_c_blocks(const mcb200_conv_shape* s, int kelems, int align) {
+  const int group_cout = s->cout / s->group, group_cin = s->c / s->group;
+  int widest = 0;
+  for (int n0 = 0; n0 < s->cout; n0 += kGroupedBlockN) {
+    const int last = (n0 + kGroupedBlockN < s->cout ? n0 + kGroupedBlockN : s->cout) - 1;
+    const int span = (last / group_cout + 1) * group_cin - grouped_origin(n0, group_cout, group_cin, align);
+    if (span > widest) widest = span;
+  }
+  return (widest + kelems - 1) / kelems;
+}
+
+// Packed image of grouped weights [cout][cin / group][taps]: [cout][taps][c_pad] where column j of
+// an output channel's row stands for input channel origin(tile of the output channel) + j; zero
+// where that channel belongs to another group (or lies beyond the tensor).
+template <bool kHalf>
+__global__ void pack_weights_grouped_kernel(const float* __restrict__ w, void* __restrict__ packed_any, int cout, int taps,
+                                            int c_pad, int group_cout, int group_cin) {
+  const size_t total = static_cast<size_t>(cout) * taps * c_pad;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i % c_pad);
+    const int tap = static_cast<int>((i / c_pad) % taps);
+    const int co = static_cast<int>(i / (static_cast<size_t>(c_pad) * taps));
+    const int origin = grouped_origin(co / kGroupedBlockN * kGroupedBlockN, group_cout, group_cin, kHalf ? 8 : 4);
+    const int local = origin + j - (co / group_cout) * group_cin;   // channel index inside co's group
+    float v = 0.f;
+    if (local >= 0 && local < group_cin) v = w[(static_cast<size_t>(co) * group_cin + local) * taps + tap];
+    if (kHalf) {
+      static_cast<uint16_t*>(packed_any)[i] = static_cast<uint16_t>(pack_bf16x2(v, 0.f));
+    } else {
+      static_cast<float*>(packed_any)[i] = round_to_tf32(v);
+    }
+  }
 }
 
 // ------------------------------------------------------------------ tensor maps
@@ -1231,7 +1396,19 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     args.stage_b_offset = (args.a_bytes + 1023) / 1024 * 1024;
     args.stage_bytes = args.stage_b_offset + plan->shape.kw * Plan::kTileBBytes;
     stage_bytes = args.stage_bytes;
-    staging_bytes = 0;
+    args.halo_staged = (args.vec_store && !args.out_half && !getenv("MCB200_HALO_DIRECT_STORES")) ? 1 : 0;
+    args.slots = 1;
+    staging_bytes = args.halo_staged ? Plan::staging_bytes(1, 4096) : 0;
+  }
+  {
+    // At most 64 prefetch instructions per tile (long-K tiles take long enough for the ring).
+    const int kh = plan->shape.kh, cb = args.c_blocks;
+    const int count = kMode == kModeMatrix ? cb : kh * cb * ((kMode == kModeIm2col && plan->shape.stride_w > 1) ? 2 : 1);
+    // Off unless MCB200_L2_PREFETCH=1: measured on ResNet-50 at batch 64 it costs 2 % (the 1 x 1
+    // reductions lose 8 %: the requests compete with the loads of the tile at hand), and the
+    // layers it was meant for do not gain.
+    const char* pf = getenv("MCB200_L2_PREFETCH");
+    args.l2_prefetch = (kMode != kModeRows && count <= 64 && pf && pf[0] == '1') ? 1 : 0;
   }
   int stages = (dynamic_limit - 1024 - staging_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -1272,6 +1449,20 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
 
 using namespace mcb200;
 
+namespace {
+// Bound of the kernel's barrier waits (process-wide) and the one-shot test hook of the calling thread.
+long long g_wait_limit_cycles = mcb200::kDefaultWaitLimitCycles;
+thread_local int t_drop_weight_load = 0;
+}  // namespace
+
+extern "C" long long mcb200_conv_set_wait_limit(long long cycles) {
+  const long long previous = g_wait_limit_cycles;
+  g_wait_limit_cycles = cycles > 0 ? cycles : mcb200::kDefaultWaitLimitCycles;
+  return previous;
+}
+
+extern "C" void mcb200_conv_test_drop_weight_load(void) { t_drop_weight_load = 1; }
+
 extern "C" int mcb200_conv_out_shape(mcb200_conv_shape* s) {
   if (!s || s->kh < 1 || s->kw < 1 || s->stride_h < 1 || s->stride_w < 1 || s->dil_h < 1 || s->dil_w < 1) return -1;
   const int ext_h = s->dil_h * (s->kh - 1) + 1;
@@ -1285,18 +1476,26 @@ extern "C" int mcb200_conv_out_shape(mcb200_conv_shape* s) {
 }
 
 extern "C" size_t mcb200_conv_packed_weight_count(const mcb200_conv_shape* s) {
-  const size_t c_pad = static_cast<size_t>((s->c + kBlockK - 1) / kBlockK) * kBlockK;
+  const size_t c_pad = s->group > 1 ? static_cast<size_t>(grouped_c_blocks(s, kBlockK, 4)) * kBlockK
+                                    : static_cast<size_t>((s->c + kBlockK - 1) / kBlockK) * kBlockK;
   return static_cast<size_t>(s->cout) * s->kh * s->kw * c_pad;
 }
 
 extern "C" int mcb200_conv_pack_weights(const mcb200_conv_shape* s, const float* w_oihw, float* packed,
                                         void* stream) {
-  if (!s || !w_oihw || !packed || s->group != 1) return -1;
-  const int c_pad = (s->c + kBlockK - 1) / kBlockK * kBlockK;
+  if (!s || !w_oihw || !packed || s->group < 1 || s->c % s->group != 0 || s->cout % s->group != 0) return -1;
   const size_t total = mcb200_conv_packed_weight_count(s);
   const int threads = 256;
   const int blocks = static_cast<int>((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
                                                                                   : 148 * 8);
+  if (s->group > 1) {
+    pack_weights_grouped_kernel<false><<<blocks > 0 ? blocks : 1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        w_oihw, packed, s->cout, s->kh * s->kw, grouped_c_blocks(s, kBlockK, 4) * kBlockK, s->cout / s->group,
+        s->c / s->group);
+    count_launch();
+    return static_cast<int>(cudaGetLastError());
+  }
+  const int c_pad = (s->c + kBlockK - 1) / kBlockK * kBlockK;
   pack_weights_kernel<<<blocks > 0 ? blocks : 1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       w_oihw, packed, s->cout, s->c, s->kh * s->kw, c_pad);
   count_launch();
@@ -1304,18 +1503,26 @@ extern "C" int mcb200_conv_pack_weights(const mcb200_conv_shape* s, const float*
 }
 
 extern "C" size_t mcb200_conv_packed_weight_count_bf16(const mcb200_conv_shape* s) {
-  const size_t c_pad = static_cast<size_t>((s->c + kBlockKHalf - 1) / kBlockKHalf) * kBlockKHalf;
+  const size_t c_pad = s->group > 1 ? static_cast<size_t>(grouped_c_blocks(s, kBlockKHalf, 8)) * kBlockKHalf
+                                    : static_cast<size_t>((s->c + kBlockKHalf - 1) / kBlockKHalf) * kBlockKHalf;
   return static_cast<size_t>(s->cout) * s->kh * s->kw * c_pad;
 }
 
 extern "C" int mcb200_conv_pack_weights_bf16(const mcb200_conv_shape* s, const float* w_oihw, uint16_t* packed,
                                              void* stream) {
-  if (!s || !w_oihw || !packed || s->group != 1) return -1;
-  const int c_pad = (s->c + kBlockKHalf - 1) / kBlockKHalf * kBlockKHalf;
+  if (!s || !w_oihw || !packed || s->group < 1 || s->c % s->group != 0 || s->cout % s->group != 0) return -1;
   const size_t total = mcb200_conv_packed_weight_count_bf16(s);
   const int threads = 256;
   const int blocks = static_cast<int>((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
                                                                                   : 148 * 8);
+  if (s->group > 1) {
+    pack_weights_grouped_kernel<true><<<blocks > 0 ? blocks : 1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        w_oihw, packed, s->cout, s->kh * s->kw, grouped_c_blocks(s, kBlockKHalf, 8) * kBlockKHalf, s->cout / s->group,
+        s->c / s->group);
+    count_launch();
+    return static_cast<int>(cudaGetLastError());
+  }
+  const int c_pad = (s->c + kBlockKHalf - 1) / kBlockKHalf * kBlockKHalf;
   pack_weights_bf16_kernel<<<blocks > 0 ? blocks : 1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       w_oihw, packed, s->cout, s->c, s->kh * s->kw, c_pad);
   count_launch();
@@ -1357,7 +1564,8 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   const int kelems = half ? kBlockKHalf : kBlockK;
   const CUtensorMapDataType dtype = half ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   if (!s || !in || !packed_w || !plan) return -1;
-  if (s->group != 1 || (s->c_stride & (half ? 7 : 3)) != 0 || s->c_stride < s->c) return -2;
+  if (s->group < 1 || s->c % s->group != 0 || s->cout % s->group != 0) return -2;
+  if ((s->c_stride & (half ? 7 : 3)) != 0 || s->c_stride < s->c) return -2;
   if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(packed_w) & 15)) return -3;
   if (s->pad_h > 127 || s->pad_w > 127 || (s->kh - 1) * s->dil_h > 255 || (s->kw - 1) * s->dil_w > 255) return -4;
   const DriverApi& api = driver_api();
@@ -1373,11 +1581,12 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   const long long m_ll = static_cast<long long>(s->n) * plan->shape.ho * plan->shape.wo;
   if (m_ll <= 0 || m_ll > 0x7fffffffLL) return -7;
   plan->m = static_cast<int>(m_ll);
-  plan->c_blocks = (s->c + kelems - 1) / kelems;
+  const bool grouped = s->group > 1;
+  plan->c_blocks = grouped ? grouped_c_blocks(s, kelems, half ? 8 : 4) : (s->c + kelems - 1) / kelems;
   plan->k_iters = s->kh * s->kw * plan->c_blocks;
-  plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
+  plan->block_n = grouped ? kGroupedBlockN : pick_block_n(s->cout, plan->m, plan->k_iters);
   // The pairing rule was measured in 32-channel k-iterations; a bfloat16 k-iteration covers 64.
-  plan->cta_pair = pick_cta_pair(plan->block_n, plan->m, plan->k_iters * (half ? 2 : 1));
+  plan->cta_pair = grouped ? 0 : pick_cta_pair(plan->block_n, plan->m, plan->k_iters * (half ? 2 : 1));
   const bool pointwise = s->kh == 1 && s->kw == 1 && s->stride_h == 1 && s->stride_w == 1 && s->pad_h == 0 &&
                          s->pad_w == 0;
   plan->im2col = pointwise ? 0 : 1;
@@ -1386,23 +1595,35 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   // Halo mode for stride-1 filters with more than one tap per row: see ConvTcArgs.  The choice
   // depends on the layer's geometry only, never on the batch size: the two modes sum over K in
   // different orders, and an image's result must not depend on how many images run with it.
-  // Taken when the widened rows cost at most half again as many positions (3 x 3 / pad 1 from 4
-  // pixels of width up).
+  // Measured on the benchmark networks (ResNet-50 at batch 64, per 3 x 3 layer): 56-pixel rows
+  // 52.8 -> 49.8 us, 28-pixel rows 37.1 -> 33.4, 7-pixel rows 43.0 -> 37.3, but 14-pixel rows 35.3
+  // -> 43.3: there every CTA has a single 256-column tile, and the halo mode's epilogue (plain
+  // stores, since a tile of the virtual grid is not a box of the output tensor) is exposed where
+  // the im2col mode's TMA tile stores are half as long.  Hence: rows of at least 24 output pixels
+  // (several tiles per CTA hide the epilogue) or at most 8 (the strips save the most), and never
+  // when the widened rows would cost more than half again as many positions.
   const int halo_w = (s->kw - 1) * s->dil_w;
   const char* halo_env = getenv("MCB200_HALO");   // "0" / "1": override for experiments and tests
   const bool halo_forced = halo_env && halo_env[0] == '1';
+  const bool halo_pays = 2 * halo_w <= plan->shape.wo && (plan->shape.wo >= 24 || plan->shape.wo <= 8);
   if (!pointwise && s->stride_h == 1 && s->stride_w == 1 && s->kw > 1 && halo_w <= kMaxHaloRows &&
-      !(halo_env && halo_env[0] == '0') && (halo_forced || 2 * halo_w <= plan->shape.wo)) {
+      !(halo_env && halo_env[0] == '0') && (halo_forced || halo_pays)) {
     const long long mv = static_cast<long long>(s->n) * plan->shape.ho * (plan->shape.wo + halo_w);
     const int halo_k_iters = s->kh * plan->c_blocks;
     int pair = 0;
-    const int bn = mv <= 0x7fffffffLL ? pick_block_n_halo(s->cout, mv, halo_k_iters, s->kw, (kBlockM + halo_w) * 128,
-                                                          &pair, nullptr)
-                                      : 0;
+    // (grouped layers keep their 64-column tiles: a strip and kw weight tiles of that width always fit)
+    const int bn = mv > 0x7fffffffLL ? 0
+                   : grouped         ? (s->kw <= 7 ? kGroupedBlockN : 0)
+                                     : pick_block_n_halo(s->cout, mv, halo_k_iters, s->kw, (kBlockM + halo_w) * 128, &pair,
+                                                         nullptr);
     if (bn != 0) {
       plan->im2col = kModeHalo;
       plan->m_virtual = static_cast<int>(mv);
       plan->strip_rows = kBlockM + halo_w;
+      if (const char* rows_env = getenv("MCB200_HALO_STRIP_ROWS")) {   // experiment: a longer strip than needed
+        const int rows = atoi(rows_env);
+        if (rows >= plan->strip_rows && rows <= 256) plan->strip_rows = rows;
+      }
       plan->k_iters = halo_k_iters;
       plan->block_n = bn;
       plan->cta_pair = pair;
@@ -1525,6 +1746,12 @@ int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, co
                                          ((reinterpret_cast<uintptr_t>(a.ep.residual) & 15) == 0));
   a.tma_epilogue = (out_ok && res_ok) ? 1 : 0;
   a.vec_store = a.tma_epilogue;
+  a.l2_prefetch = a.halo_staged = 0;
+  a.wait_limit = g_wait_limit_cycles;
+  a.drop_last_weight_load = t_drop_weight_load;
+  t_drop_weight_load = 0;
+  a.group_cout = plan->shape.group > 1 ? plan->shape.cout / plan->shape.group : 0;
+  a.group_cin = plan->shape.group > 1 ? plan->shape.c / plan->shape.group : 0;
   a.wp = plan->shape.wo;
   a.stage_bytes = a.stage_b_offset = 0;
   if (plan->im2col == kModeHalo) {
@@ -1753,4 +1980,21 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -200 - static_cast<int>(r);
   return 0;
+}
+
+// With -DMCB200_CONV_TRACE: copies the cycle stamps of the last traced launches' CTA 0 (4 roles x
+// 2048 slots, see MCB200_TRACE above) to `out` and clears the device array; returns the number
+// of values per role, or 0 when the library was built without the trace.
+extern "C" int mcb200_conv_trace_read(long long* out) {
+#ifdef MCB200_CONV_TRACE
+  if (!out) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  if (cudaMemcpyFromSymbol(out, mcb200::g_conv_trace, sizeof(long long) * 4 * mcb200::kTraceSlots) != cudaSuccess) return -3;
+  static long long zeros[4 * mcb200::kTraceSlots];
+  if (cudaMemcpyToSymbol(mcb200::g_conv_trace, zeros, sizeof(zeros)) != cudaSuccess) return -4;
+  return mcb200::kTraceSlots;
+#else
+  (void)out;
+  return 0;
+#endif
 }

@@ -177,10 +177,92 @@ channel_batch_stats_kernel(const float* __restrict__ x, long long per_channel, i
   }
 }
 
+// Deconvolution as a convolution, step 1: the input's pixels spread `stride` apart over a zero
+// tensor (channels last, `c_stride` floats per pixel, zero in the pad lanes).  `src` is channels
+// last with `c` floats per pixel.  The destination was cleared beforehand.
+__global__ void deconv_spread_kernel(const float* __restrict__ src, float* __restrict__ dst, int n, int h, int w, int c,
+                                     int c_stride, int stride_h, int stride_w, int hs, int ws) {
+  const long long total = static_cast<long long>(n) * h * w * c;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int ch = static_cast<int>(i % c);
+    long long t = i / c;
+    const int x = static_cast<int>(t % w);
+    t /= w;
+    const int y = static_cast<int>(t % h);
+    const int img = static_cast<int>(t / h);
+    dst[((static_cast<size_t>(img) * hs + static_cast<size_t>(y) * stride_h) * ws + static_cast<size_t>(x) * stride_w) * c_stride +
+        ch] = src[i];
+  }
+}
+
+// Step 2: the filter of the equivalent convolution.  Deconvolution weights are [c_in, c_out / g,
+// kh, kw]; the convolution from c_in to c_out that computes the same thing over the spread input
+// has weights [c_out, c_in / g, kh, kw] with both tap axes reversed.
+__global__ void deconv_flip_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int c_in, int c_out,
+                                           int group, int kh, int kw) {
+  const int cin_g = c_in / group, cout_g = c_out / group;
+  const int total = c_out * cin_g * kh * kw;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int s = i % kw;
+    const int r = (i / kw) % kh;
+    const int ci_local = (i / (kw * kh)) % cin_g;
+    const int co = i / (kw * kh * cin_g);
+    const int g = co / cout_g;
+    const int ci = g * cin_g + ci_local;
+    out[i] = w[((static_cast<size_t>(ci) * cout_g + (co - g * cout_g)) * kh + (kh - 1 - r)) * kw + (kw - 1 - s)];
+  }
+}
+
 }  // namespace
 }  // namespace mcb200
 
 using namespace mcb200;
+
+extern "C" int mcb200_deconv_as_conv_shape(const mcb200_conv_shape* deconv, mcb200_conv_shape* conv) {
+  if (!deconv || !conv) return -1;
+  mcb200_conv_shape d = *deconv;
+  if (mcb200_deconv_out_shape(&d) != 0) return -2;
+  *conv = d;
+  conv->h = (d.h - 1) * d.stride_h + 1;
+  conv->w = (d.w - 1) * d.stride_w + 1;
+  conv->c_stride = (d.c + 3) / 4 * 4;
+  conv->stride_h = conv->stride_w = 1;
+  conv->pad_h = d.dil_h * (d.kh - 1) - d.pad_h;
+  conv->pad_w = d.dil_w * (d.kw - 1) - d.pad_w;
+  if (conv->pad_h < 0 || conv->pad_w < 0) return -3;   // more padding than the filter reaches: the output is a crop
+  conv->ho = d.ho;
+  conv->wo = d.wo;
+  return 0;
+}
+
+extern "C" int mcb200_deconv_spread_input(const mcb200_conv_shape* deconv, const float* in_nhwc, float* spread,
+                                          void* stream) {
+  mcb200_conv_shape c;
+  if (!in_nhwc || !spread || mcb200_deconv_as_conv_shape(deconv, &c) != 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t bytes = static_cast<size_t>(c.n) * c.h * c.w * c.c_stride * sizeof(float);
+  cudaError_t e = cudaMemsetAsync(spread, 0, bytes, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const long long items = static_cast<long long>(deconv->n) * deconv->h * deconv->w * deconv->c;
+  if (items == 0) return 0;
+  deconv_spread_kernel<<<grid_for_items(items, 256), 256, 0, st>>>(in_nhwc, spread, deconv->n, deconv->h, deconv->w,
+                                                                   deconv->c, c.c_stride, deconv->stride_h,
+                                                                   deconv->stride_w, c.h, c.w);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mcb200_deconv_flip_weights(const mcb200_conv_shape* deconv, const float* w_iohw, float* w_oihw,
+                                          void* stream) {
+  if (!deconv || !w_iohw || !w_oihw || deconv->group < 1 || deconv->c % deconv->group || deconv->cout % deconv->group)
+    return -1;
+  const int total = deconv->cout * (deconv->c / deconv->group) * deconv->kh * deconv->kw;
+  deconv_flip_weights_kernel<<<grid_for_items(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      w_iohw, w_oihw, deconv->c, deconv->cout, deconv->group, deconv->kh, deconv->kw);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int mcb200_deconv_out_shape(mcb200_conv_shape* s) {
   if (!s || s->kh < 1 || s->kw < 1 || s->stride_h < 1 || s->stride_w < 1 || s->dil_h < 1 || s->dil_w < 1) return -1;

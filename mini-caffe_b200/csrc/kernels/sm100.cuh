@@ -122,6 +122,23 @@ __device__ __forceinline__ void tma_load_im2col_4d(const CUtensorMap* map, uint6
       : "memory");
 }
 
+// Asks L2 for the lines of an im2col-mode tile without bringing them to shared memory (no
+// barrier, nothing to wait for): issued a tile ahead, the later load finds them in L2.
+__device__ __forceinline__ void tma_prefetch_im2col_4d(const CUtensorMap* map, int c, int w, int h, int n, uint16_t off_w,
+                                                       uint16_t off_h) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.im2col [%0, {%1, %2, %3, %4}], {%5, %6};"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+               : "memory");
+}
+
 // Shared -> global tile store (bulk async group); rows / columns outside the
 // tensor are clipped by the hardware.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {

@@ -1,6 +1,7 @@
 // Convolution and InnerProduct: parameter handling on the host, tensor-core /
 // depthwise / direct kernels on the device, fused tails folded into
 // per-channel scale and shift arrays.
+#include <cstdlib>
 #include <cstring>
 
 #include "../filler.h"
@@ -166,13 +167,16 @@ void ConvolutionLayer::LayerSetUp(const vector<Blob*>& bottom, const vector<Blob
       FillBlob(p.bias_filler(), blobs_[1].get());
     }
   }
-  if (s.group == 1) {
-    path_ = kTensorCore;
-  } else if (s.group == s.c && s.cout == s.c && s.c % 4 == 0) {
+  // Depthwise layers (one channel per group) are pure data movement and have a kernel of their
+  // own; every other layer, grouped or not, is a contraction and runs on the tensor cores (a
+  // grouped layer as block-diagonal weight tiles, src/layers/base_conv_layer.cpp:265-270).
+  if (s.group > 1 && s.group == s.c && s.cout == s.c && s.c % 4 == 0) {
     path_ = kDepthwise;
   } else {
-    path_ = kDirect;
+    path_ = kTensorCore;
   }
+  const char* force_direct = getenv("MCB200_CONV_DIRECT");   // "1": the plain kernel, for comparisons in tests
+  if (force_direct && force_direct[0] == '1' && path_ == kTensorCore) path_ = kDirect;
   // Limits of the im2col tensor map (8-bit signed corners, 8-bit tap offsets).
   if (path_ == kTensorCore && (s.pad_h > 127 || s.pad_w > 127 || (s.kh - 1) * s.dil_h > 255 ||
                                (s.kw - 1) * s.dil_w > 255)) {
@@ -296,6 +300,15 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
           Forward_gpu(bottom, top);
           return;
         }
+        if (rc != 0 && !half && !half_out) {
+          // A shape the tensor maps cannot express (for instance a stride above 8, which the
+          // im2col map refuses as traversal stride): the plain kernel runs it from now on.
+          LOG(WARNING) << "layer " << layer_param_.name() << ": tensor-core plan rejected (" << rc
+                       << "), using the direct kernel";
+          path_ = kDirect;
+          Forward_gpu(bottom, top);
+          return;
+        }
         CHECK_EQ(rc, 0) << "cannot build the tensor-core plan for layer " << layer_param_.name();
         slot.in = in;
         slot.weights = w;
@@ -312,7 +325,13 @@ void ConvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blo
       KERNEL_CHECK(mcb200_conv_depthwise_bf16(&s, in, half ? 1 : 0, packed_weights_.Reserve(0), out, half_out ? 1 : 0,
                                               &ep, ctx.stream_ptr()));
     } else if (path_ == kDepthwise) {
-      KERNEL_CHECK(mcb200_conv_depthwise(&s, in, packed_weights_.Reserve(0), out, &ep, ctx.stream_ptr()));
+      const char* dw_tma = getenv("MCB200_DW_TMA");   // "0": the register-window kernel, for comparisons
+      if (!ep.residual && mcb200_conv_depthwise_tma_supported(&s) && !(dw_tma && dw_tma[0] == '0')) {
+        KERNEL_CHECK(mcb200_conv_depthwise_tma(&s, in, packed_weights_.Reserve(0), out, &ep, ctx.status_word(),
+                                               ctx.stream_ptr()));
+      } else {
+        KERNEL_CHECK(mcb200_conv_depthwise(&s, in, packed_weights_.Reserve(0), out, &ep, ctx.stream_ptr()));
+      }
     } else {
       KERNEL_CHECK(mcb200_conv_direct(&s, in, blobs_[0]->gpu_data(), out, s.cout, &ep, ctx.stream_ptr()));
     }

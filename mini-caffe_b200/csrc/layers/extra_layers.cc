@@ -1,6 +1,8 @@
 // Layer types that the shipped example networks use beyond the benchmark
 // configurations: Deconvolution, Slice, Crop, BN, LRN.
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "../filler.h"
 #include "layers.h"
@@ -60,16 +62,61 @@ void DeconvolutionLayer::Reshape(const vector<Blob*>& bottom, const vector<Blob*
 
 void DeconvolutionLayer::Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) {
   Context& ctx = Context::Get();
+  const char* force_direct = getenv("MCB200_CONV_DIRECT");   // "1": the plain kernel, for comparisons in tests
+  if (plans_.size() < bottom.size()) plans_.resize(bottom.size());
   for (size_t i = 0; i < bottom.size(); ++i) {
     mcb200_conv_shape s = shape_;
     s.n = bottom[i]->num();
     s.h = bottom[i]->height();
     s.w = bottom[i]->width();
+    s.c_stride = s.c;
     mcb200_deconv_out_shape(&s);
     if (top[i]->count() == 0) continue;
-    KERNEL_CHECK(mcb200_deconv_direct(&s, bottom[i]->gpu_data(), blobs_[0]->gpu_data(),
-                                      bias_term_ ? blobs_[1]->gpu_data() : nullptr, top[i]->mutable_gpu_data(),
-                                      ctx.stream_ptr()));
+    mcb200_conv_shape conv;
+    const bool tensor_core = !(force_direct && force_direct[0] == '1') && mcb200_deconv_as_conv_shape(&s, &conv) == 0 &&
+                             conv.pad_h <= 127 && conv.pad_w <= 127 && (conv.kh - 1) * conv.dil_h <= 255 &&
+                             (conv.kw - 1) * conv.dil_w <= 255;
+    if (!tensor_core) {
+      KERNEL_CHECK(mcb200_deconv_direct(&s, bottom[i]->gpu_data(), blobs_[0]->gpu_data(),
+                                        bias_term_ ? blobs_[1]->gpu_data() : nullptr, top[i]->mutable_gpu_data(),
+                                        ctx.stream_ptr()));
+      continue;
+    }
+    // The equivalent convolution's filter, re-laid when the weights change.
+    const unsigned long long wv = blobs_[0]->host_version();
+    if (wv != weight_version_) {
+      float* flipped = flipped_weights_.Reserve(blobs_[0]->count());
+      KERNEL_CHECK(mcb200_deconv_flip_weights(&s, blobs_[0]->gpu_data(), flipped, ctx.stream_ptr()));
+      float* packed = packed_weights_.Reserve(mcb200_conv_packed_weight_count(&conv));
+      KERNEL_CHECK(mcb200_conv_pack_weights(&conv, flipped, packed, ctx.stream_ptr()));
+      weight_version_ = wv;
+      for (auto& slot : plans_) {
+        if (slot) slot->valid = false;
+      }
+    }
+    // Stride 1 with a channel count that is a multiple of four reads the input as it is.
+    const float* in = bottom[i]->gpu_data_nhwc();
+    if (s.stride_h != 1 || s.stride_w != 1 || conv.c_stride != s.c) {
+      float* spread = spread_input_.Reserve(static_cast<size_t>(conv.n) * conv.h * conv.w * conv.c_stride);
+      KERNEL_CHECK(mcb200_deconv_spread_input(&s, in, spread, ctx.stream_ptr()));
+      in = spread;
+    }
+    if (!plans_[i]) plans_[i].reset(new PlanSlot);
+    PlanSlot& slot = *plans_[i];
+    const float* w = packed_weights_.Reserve(0);
+    if (!slot.valid || slot.in != in || slot.weights != w || std::memcmp(&slot.shape, &conv, sizeof(conv)) != 0) {
+      CHECK_EQ(mcb200_conv_tc_plan(&conv, in, w, &slot.plan), 0)
+          << "cannot build the tensor-core plan for layer " << layer_param_.name();
+      slot.in = in;
+      slot.weights = w;
+      slot.shape = conv;
+      slot.valid = true;
+    }
+    mcb200_epilogue ep = mcb200_epilogue();
+    ep.residual_coeff = 1.f;
+    ep.shift = bias_term_ ? blobs_[1]->gpu_data() : nullptr;
+    KERNEL_CHECK(mcb200_conv_tc_launch(&slot.plan, top[i]->mutable_gpu_data_nhwc(), conv.cout, &ep, ctx.status_word(),
+                                       ctx.stream_ptr()));
   }
 }
 REGISTER_LAYER_CLASS(Deconvolution);

@@ -31,9 +31,10 @@ class DeviceScratch {
 
 // ---------------------------------------------------------------- producers
 
-// Convolution, 2-D, any stride / pad / dilation / group.  group == 1 runs on
-// the tensor cores, group == channels on the depthwise kernel, the rest on the
-// direct kernel.  Parameter handling follows src/layers/base_conv_layer.cpp:11-182.
+// Convolution, 2-D, any stride / pad / dilation / group.  Depthwise layers
+// (group == channels) run on a kernel of their own, everything else, grouped
+// layers included, on the tensor cores; the direct kernel is left for shapes the
+// tensor-core kernel's tensor maps cannot express.  Parameter handling follows src/layers/base_conv_layer.cpp:11-182.
 class ConvolutionLayer : public Layer {
  public:
   explicit ConvolutionLayer(const LayerParameter& param) : Layer(param) {}
@@ -456,6 +457,19 @@ class DeconvolutionLayer : public Layer {
   void Forward_gpu(const vector<Blob*>& bottom, const vector<Blob*>& top) override;
   mcb200_conv_shape shape_ = mcb200_conv_shape();
   bool bias_term_ = false;
+  // The layer runs as a convolution on the tensor cores: reversed filter, input spread `stride`
+  // apart over zeros (see mcb200_deconv_as_conv_shape); the direct kernel takes what is left
+  // (more padding than the filter reaches).
+  unsigned long long weight_version_ = 0;
+  DeviceScratch flipped_weights_, packed_weights_, spread_input_;
+  struct PlanSlot {
+    mcb200_conv_plan plan;
+    const float* in = nullptr;
+    const float* weights = nullptr;
+    mcb200_conv_shape shape = mcb200_conv_shape();
+    bool valid = false;
+  };
+  std::vector<std::unique_ptr<PlanSlot> > plans_;  // one per bottom
 };
 
 // top[i] = a range of bottom[0] along one axis (src/layers/slice_layer.cpp:9-96).

@@ -1,6 +1,8 @@
 """Deconvolution, Crop, Slice, BN and LRN (the layer types of the shipped SSH / WGAN / older example
-nets) against the reference project's CPU code.  Copies are compared bit for bit; the arithmetic
-layers are fp32 on both sides (no tensor cores), so they agree to float rounding."""
+nets) against the reference project's CPU code.  Deconvolution runs on the tensor cores (TF32
+tolerance); with MCB200_CONV_DIRECT=1 it runs on the plain fp32 kernel, and then everything here is
+fp32 on both sides and agrees to float rounding.  Copies are compared bit for bit."""
+import contextlib
 import os
 
 import numpy as np
@@ -20,23 +22,46 @@ def gpu_engine(engine):
     return engine
 
 
-def _check(got, want):
+@contextlib.contextmanager
+def plain_kernels(on):
+    """With `on`, Convolution / Deconvolution layers constructed inside run on the fp32 kernels."""
+    saved = os.environ.get("MCB200_CONV_DIRECT")
+    if on:
+        os.environ["MCB200_CONV_DIRECT"] = "1"
+    else:
+        os.environ.pop("MCB200_CONV_DIRECT", None)
+    try:
+        yield
+    finally:
+        if saved is None:
+            os.environ.pop("MCB200_CONV_DIRECT", None)
+        else:
+            os.environ["MCB200_CONV_DIRECT"] = saved
+
+
+def _check(got, want, fp32):
+    from parity import assert_close
     for name in want:
         assert got[name].shape == want[name].shape, name
-        scale = max(1.0, float(np.abs(want[name]).max()))
-        assert float(np.abs(got[name] - want[name]).max()) <= 2e-5 * scale, name
+        if fp32:
+            scale = max(1.0, float(np.abs(want[name]).max()))
+            assert float(np.abs(got[name] - want[name]).max()) <= 2e-5 * scale, name
+        else:
+            assert_close(got[name], want[name], name)
 
 
-def test_extra_layers_against_the_reference(capi, gpu_engine, reflib):
+@pytest.mark.parametrize("fp32", [False, True], ids=["tensor_cores", "plain_kernels"])
+def test_extra_layers_against_the_reference(capi, gpu_engine, reflib, fp32):
     wl = pkg("workloads")
     for batch, seed in ((2, 1), (1, 2), (5, 3)):
         b = wl.extra_layers_net(batch)
         weights = wl.init_params(b.params, seed=5 + seed, bn_identity=False)
         x = wl.extra_layers_input(batch, seed=seed)
         outs = list(wl.EXTRA_LAYER_OUTPUTS)
-        got = run_net(capi, gpu_engine, b, weights, x, outs, marks=outs)
+        with plain_kernels(fp32):
+            got = run_net(capi, gpu_engine, b, weights, x, outs, marks=outs)
         want = run_net(capi, reflib, b, weights, x, outs, marks=outs)
-        _check(got, want)
+        _check(got, want, fp32)
         for name in COPIES:
             # same values moved around: identical wherever the source tensor is identical
             src = "up" if name in ("crop", "crop1", "e0", "e1") else "up_g"
@@ -44,16 +69,18 @@ def test_extra_layers_against_the_reference(capi, gpu_engine, reflib):
                 assert np.array_equal(got[name], want[name]), name
 
 
-def test_extra_layers_golden_fixture(capi, gpu_engine):
+@pytest.mark.parametrize("fp32", [False, True], ids=["tensor_cores", "plain_kernels"])
+def test_extra_layers_golden_fixture(capi, gpu_engine, fp32):
     """The committed fixture (made by the reference itself) does not need the compiled reference."""
     wl = pkg("workloads")
     g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "extra_layers.npz"))
     b = wl.extra_layers_net(2)
     weights = {k[2:]: g[k] for k in g.files if k.startswith("w_")}
     outs = list(wl.EXTRA_LAYER_OUTPUTS)
-    got = run_net(capi, gpu_engine, b, weights, {"data": g["in_data"], "like": np.zeros((2, 4, 13, 11), np.float32)},
-                  outs, marks=outs)
-    _check(got, {name: g["out_" + name] for name in outs})
+    with plain_kernels(fp32):
+        got = run_net(capi, gpu_engine, b, weights, {"data": g["in_data"], "like": np.zeros((2, 4, 13, 11), np.float32)},
+                      outs, marks=outs)
+    _check(got, {name: g["out_" + name] for name in outs}, fp32)
 
 
 def test_ssh_style_upsampling_head(capi, gpu_engine, reflib):
@@ -108,11 +135,20 @@ def test_wgan_style_generator(capi, gpu_engine, reflib):
     b.raw("tanh", "TanH", ["out"], ["image"])
     weights = wl.init_params(b.params, seed=11, bn_identity=False)
     z = {"z": np.random.default_rng(12).standard_normal((batch, 16, 1, 1)).astype(np.float32)}
-    got = run_net(capi, gpu_engine, b, weights, z, ["image"], marks=["deconv1"])
+    from parity import assert_close
+    from test_layers_gpu import tensor_core_launches
     want = run_net(capi, reflib, b, weights, z, ["image"], marks=["deconv1"])
-    assert got["image"].shape == (batch, 3, 32, 32)
-    assert float(np.abs(got["image"] - want["image"]).max()) <= 5e-5
     assert float(np.abs(want["image"]).max()) > 0.05
+    # the four Deconvolution layers on the tensor cores (each as the convolution, with a reversed
+    # filter, of its input spread `stride` apart over zeros)
+    got = run_net(capi, gpu_engine, b, weights, z, ["image"], marks=["deconv1"])
+    assert got["image"].shape == (batch, 3, 32, 32)
+    assert_close(got["image"], want["image"], "generator image")
+    assert tensor_core_launches(capi, gpu_engine, b, weights, z) == 4
+    # and on the plain fp32 kernel: float rounding only
+    with plain_kernels(True):
+        got = run_net(capi, gpu_engine, b, weights, z, ["image"], marks=["deconv1"])
+    assert float(np.abs(got["image"] - want["image"]).max()) <= 5e-5
 
 
 def test_sigmoid(capi, gpu_engine, reflib):

@@ -28,15 +28,63 @@ def test_depthwise_and_grouped_convolution(capi, gpu_engine, reflib):
     b.input([("data", (3, 32, 17, 19))])
     b.conv("dw", "data", "dw", 32, 32, 3, stride=2, pad=1, group=32)          # depthwise kernel
     b.relu("dw_relu", "dw")
-    b.conv("grp", "dw", "grp", 32, 48, 3, stride=1, pad=1, group=4)           # grouped: direct kernel
+    b.conv("grp", "dw", "grp", 32, 48, 3, stride=1, pad=1, group=4)           # grouped: block-diagonal tiles
     b.conv("odd", "grp", "odd", 48, 10, 1)                                    # 10 outputs: unaligned rows
-    b.conv("odd2", "odd", "odd2", 10, 6, 3, pad=1)                            # 10 input channels: direct kernel
+    b.conv("odd2", "odd", "odd2", 10, 6, 3, pad=1)                            # 10 input channels: padded copy
     weights = wl.init_params(b.params, seed=1)
     x = {"data": np.random.default_rng(2).standard_normal((3, 32, 17, 19)).astype(np.float32)}
     outs = ["dw", "grp", "odd", "odd2"]
     got, want = both(capi, gpu_engine, reflib, b, weights, x, outs, marks=outs)
     for name in outs:
         assert_close(got[name], want[name], name)
+    assert tensor_core_launches(capi, gpu_engine, b, weights, x) == 3       # grp, odd, odd2
+
+
+def tensor_core_launches(capi, engine, b, weights, x):
+    """How many launches of the tensor-core convolution kernel one forward pass makes (the library's
+    kernel timer brackets exactly those launches)."""
+    import ctypes
+    L = engine.lib
+    L.mcb200_kernel_timing_end.restype = ctypes.c_longlong
+    L.mcb200_kernel_timing_end.argtypes = [ctypes.POINTER(ctypes.c_double)]
+    net = capi.Net(engine, b.text(), None, from_buffer=True)
+    net.set_params(weights)
+    net.forward(**x)
+    L.mcb200_kernel_timing_begin()
+    net.forward()
+    ms = ctypes.c_double(0.0)
+    count = int(L.mcb200_kernel_timing_end(ctypes.byref(ms)))
+    net.close()
+    return count
+
+
+@pytest.mark.parametrize("case", [
+    # name, N, Cin, H, W, Cout, k, stride, pad, dilation, group
+    ("two_groups_5x5", 2, 96, 27, 27, 256, 5, 1, 2, 1, 2),          # 48 channels and 128 outputs per group
+    ("cardinality_32", 2, 128, 28, 28, 128, 3, 1, 1, 1, 32),        # 4 channels, 4 outputs per group
+    ("pointwise_three_groups", 3, 240, 14, 14, 240, 1, 1, 0, 1, 3),  # 80 channels per group: not a multiple of 32
+    ("stride2_groups", 2, 64, 19, 23, 96, 3, 2, 1, 1, 8),
+    ("channel_multiplier", 2, 24, 16, 16, 48, 3, 1, 1, 1, 24),      # one channel in, two out per group
+    ("six_by_six", 2, 6, 12, 12, 6, 3, 1, 1, 1, 6),                 # depthwise with a channel count not divisible by 4
+    ("dilated_groups", 1, 64, 20, 20, 64, 3, 1, 2, 2, 4),
+    ("ragged_groups", 2, 36, 10, 10, 90, 3, 1, 1, 1, 9),            # 4 channels, 10 outputs per group: tiles cut groups
+], ids=lambda c: c[0])
+def test_grouped_convolution_on_the_tensor_cores(capi, gpu_engine, reflib, case):
+    """Grouped layers (1 < group, not plain depthwise) run the tensor-core kernel: an N tile multiplies
+    the channels of the groups it touches by a block-diagonal weight tile.  Against the reference's
+    per-group GEMM loop (src/layers/base_conv_layer.cpp:265-270), with the fused tail."""
+    name, n, cin, h, w, cout, k, stride, pad, dil, group = case
+    wl = pkg("workloads")
+    b = wl.NetBuilder("grouped")
+    b.input([("data", (n, cin, h, w))])
+    b.conv("c", "data", "c", cin, cout, k, stride=stride, pad=pad, dilation=dil, group=group, bias=True,
+           bias_init="uniform")
+    b.relu("c_relu", "c")
+    weights = wl.init_params(b.params, seed=31)
+    x = {"data": np.random.default_rng(32).standard_normal((n, cin, h, w)).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["c"])
+    assert_close(got["c"], want["c"], name)
+    assert tensor_core_launches(capi, gpu_engine, b, weights, x) == 1
 
 
 @pytest.mark.parametrize("channels,size,k,stride,pad,cout", [

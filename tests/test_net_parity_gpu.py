@@ -197,3 +197,33 @@ def test_net_destroyed_by_another_thread_while_its_creator_keeps_working(capi, g
     assert len(box["results"]) == 9
     for out in box["results"]:
         assert np.array_equal(out.view(np.uint32), box["first"].view(np.uint32))
+
+
+def test_forward_reports_a_kernel_that_gave_up_waiting_and_recovers(capi, gpu_engine):
+    """The status word a convolution kernel raises when its bounded barrier waits run out (made to
+    happen here through the library's test hook, on the host's terms) turns into the API's error:
+    CaffeNetForward returns -1 with a message, like every caffe::Error (src/c_api.cpp:206-223);
+    the next forward pass on the same net and context succeeds with the usual results."""
+    import ctypes
+    wl = pkg("workloads")
+    b = wl.conv_relu(1)
+    weights = wl.init_params(b.params, seed=0)
+    x = wl.conv_relu_input(1, seed=0)
+    L = gpu_engine.lib
+    L.mcb200_conv_set_wait_limit.restype = ctypes.c_longlong
+    L.mcb200_conv_set_wait_limit.argtypes = [ctypes.c_longlong]
+    net = capi.Net(gpu_engine, b.text(), None, from_buffer=True)
+    net.set_params(weights)
+    net.forward(**x)
+    good = net.blob("conv").data.copy()
+    previous = L.mcb200_conv_set_wait_limit(2000000)
+    try:
+        L.mcb200_conv_test_drop_weight_load()
+        with pytest.raises(capi.CaffeError) as err:
+            net.forward(**x)
+        assert "gave up waiting" in str(err.value)
+    finally:
+        L.mcb200_conv_set_wait_limit(previous)
+    net.forward(**x)
+    assert np.array_equal(net.blob("conv").data.view(np.uint32), good.view(np.uint32))
+    net.close()
