@@ -7,7 +7,8 @@
 // CTA walks over tiles of 8 x 16 output pixels x 32 channels; one thread asks the TMA unit for the
 // next tile's input box ((7 * stride + 3) x (15 * stride + 3) pixels x 32 channels, zero-filled
 // outside the image, which is the layer's padding) while all threads compute the current one out of
-// shared memory, so every CTA always has a whole box in flight, independent of its registers.
+// shared memory; a ring of kStages boxes per CTA (requests run kStages - 1 tiles ahead) keeps
+// 70-190 KB per SM in flight, independent of the registers the arithmetic needs.
 //
 // Shared-memory layout: a pixel's 32 channels are one 128-byte row of the box, stored with the
 // 128-byte swizzle; a warp's lanes are 8 channel groups x 4 neighbouring pixels of a row, which
@@ -31,6 +32,7 @@ namespace {
 using namespace sm100;
 
 constexpr int kTileH = 8, kTileW = 16, kChannels = 32;
+constexpr int kMaxDwStages = 4;
 constexpr long long kDwWaitLimitCycles = 2000000000LL;   // about one second
 
 template <int STRIDE>
@@ -56,26 +58,24 @@ struct DwArgs {
   int* status;
 };
 
-__device__ __forceinline__ float dw_tail(float v, int c, const DwArgs& a) {
-  if (a.scale) v *= __ldg(a.scale + c);
-  if (a.shift) v += __ldg(a.shift + c);
-  if (a.act != 0 && v <= 0.f) v *= a.act == 2 ? __ldg(a.prelu + (a.prelu_shared ? 0 : c)) : a.slope;
-  return v;
+__device__ __forceinline__ float dw_tail(float v, float scale, float shift, float slope) {
+  v = fmaf(v, scale, shift);
+  return v > 0.f ? v : v * slope;   // slope 1: no activation, 0: ReLU
 }
 
 template <int STRIDE>
-__global__ void __launch_bounds__(256) depthwise3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const DwArgs a) {
+__global__ void __launch_bounds__(256) depthwise3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const DwArgs a,
+                                                               const int kStages) {
   using Box = DwBox<STRIDE>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[2];
+  __shared__ uint64_t full_bar[kMaxDwStages];
   __shared__ int abort_flag;
   const uint32_t raw = smem_addr(smem_raw);
   uint8_t* stages = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   const int tid = threadIdx.x;
   if (tid == 0) {
     abort_flag = 0;
-    mbar_init(&full_bar[0], 1);
-    mbar_init(&full_bar[1], 1);
+    for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
     fence_barrier_init();
     tma_prefetch_descriptor(&map_in);
   }
@@ -106,21 +106,40 @@ __global__ void __launch_bounds__(256) depthwise3x3_tma_kernel(const __grid_cons
   const int row0 = (tid >> 7) * 4;
 
   long long t = blockIdx.x;
-  if (tid == 0 && t < a.tiles) request(t, 0);
+  if (tid == 0) {
+    for (int s = 0; s < kStages - 1; ++s)
+      if (t + static_cast<long long>(s) * gridDim.x < a.tiles) request(t + static_cast<long long>(s) * gridDim.x, s);
+  }
   int it = 0;
   for (; t < a.tiles; t += gridDim.x, ++it) {
-    const int stage = it & 1;
-    const long long next = t + gridDim.x;
-    if (tid == 0 && next < a.tiles) request(next, stage ^ 1);   // that stage was consumed before the last barrier
-    if (!mbar_wait_bounded(&full_bar[stage], static_cast<uint32_t>(it >> 1) & 1u, abort, kDwWaitLimitCycles)) break;
+    const int stage = it % kStages;
+    const uint32_t parity = static_cast<uint32_t>(it / kStages) & 1u;
+    // the tile kStages - 1 ahead goes into the stage that was consumed before the last barrier
+    const long long ahead = t + static_cast<long long>(kStages - 1) * gridDim.x;
+    if (tid == 0 && ahead < a.tiles) request(ahead, (it + kStages - 1) % kStages);
+    if (!mbar_wait_bounded(&full_bar[stage], parity, abort, kDwWaitLimitCycles)) break;
     int cb, tx, ty, img;
     decode(t, cb, tx, ty, img);
     const int c0 = cb * kChannels + cg * 4;
     const uint8_t* box = stages + stage * Box::kStageBytes;
     float4 k[9];
+    float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 sl = make_float4(1.f, 1.f, 1.f, 1.f);
     if (c0 < a.c) {
 #pragma unroll
       for (int j = 0; j < 9; ++j) k[j] = __ldg(reinterpret_cast<const float4*>(a.w + static_cast<size_t>(j) * a.c + c0));
+      if (a.scale) sc = __ldg(reinterpret_cast<const float4*>(a.scale + c0));
+      if (a.shift) sh = __ldg(reinterpret_cast<const float4*>(a.shift + c0));
+      if (a.act == 1) {
+        sl = make_float4(a.slope, a.slope, a.slope, a.slope);
+      } else if (a.act == 2) {
+        if (a.prelu_shared) {
+          const float p = __ldg(a.prelu);
+          sl = make_float4(p, p, p, p);
+        } else {
+          sl = __ldg(reinterpret_cast<const float4*>(a.prelu + c0));
+        }
+      }
     }
     float4 acc[4];
 #pragma unroll
@@ -154,10 +173,10 @@ __global__ void __launch_bounds__(256) depthwise3x3_tma_kernel(const __grid_cons
         const int oy = ty * kTileH + row0 + i;
         if (oy >= a.ho) break;
         float4 r4;
-        r4.x = dw_tail(acc[i].x, c0, a);
-        r4.y = dw_tail(acc[i].y, c0 + 1, a);
-        r4.z = dw_tail(acc[i].z, c0 + 2, a);
-        r4.w = dw_tail(acc[i].w, c0 + 3, a);
+        r4.x = dw_tail(acc[i].x, sc.x, sh.x, sl.x);
+        r4.y = dw_tail(acc[i].y, sc.y, sh.y, sl.y);
+        r4.z = dw_tail(acc[i].z, sc.z, sh.z, sl.z);
+        r4.w = dw_tail(acc[i].w, sc.w, sh.w, sl.w);
         *reinterpret_cast<float4*>(a.out + ((static_cast<size_t>(img) * a.ho + oy) * a.wo + ox) * a.c + c0) = r4;
       }
     }
@@ -168,9 +187,9 @@ __global__ void __launch_bounds__(256) depthwise3x3_tma_kernel(const __grid_cons
   if (abort_flag) {
     __syncthreads();
     if (tid == 0) {
-      for (int j = it; j <= it + 1; ++j) {   // the box that did not arrive and the one requested after it
+      for (int j = it; j < it + kStages; ++j) {   // the box that did not arrive and the ones requested after it
         const long long start = clock64();
-        while (!mbar_try_wait(&full_bar[j & 1], static_cast<uint32_t>(j >> 1) & 1u)) {
+        while (!mbar_try_wait(&full_bar[j % kStages], static_cast<uint32_t>(j / kStages) & 1u)) {
           if (clock64() - start > kDwWaitLimitCycles / 8) break;
         }
       }
@@ -213,7 +232,10 @@ int launch_dw(const mcb200_conv_shape& s, const float* in, const DwArgs& args, c
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return -11;
   auto kernel = depthwise3x3_tma_kernel<STRIDE>;
-  const int smem = 2 * Box::kStageBytes + 1024;
+  // Four boxes per CTA at stride 1 (2 CTAs per SM by registers: 190 KB in flight per SM), two at
+  // stride 2 (one CTA per SM by shared memory: 144 KB).
+  const int stage_count = STRIDE == 1 ? 4 : 2;
+  const int smem = stage_count * Box::kStageBytes + 1024;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured[64] = {false};
@@ -231,13 +253,12 @@ int launch_dw(const mcb200_conv_shape& s, const float* in, const DwArgs& args, c
     }
   }
   const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
-  // CTAs per SM by shared memory (227 KiB) and threads (2048): 4 at stride 1, 1 at stride 2.
-  int per_sm = (227 * 1024) / (smem + 1024);
-  if (per_sm > 6) per_sm = 6;
+  int per_sm = (227 * 1024) / (smem + 1024);   // by shared memory: 2 at stride 1, 1 at stride 2
+  if (per_sm > 2) per_sm = 2;                  // by registers
   if (per_sm < 1) per_sm = 1;
   long long blocks = static_cast<long long>(sms) * per_sm;
   if (blocks > args.tiles) blocks = args.tiles;
-  kernel<<<static_cast<unsigned>(blocks), 256, smem, st>>>(map, args);
+  kernel<<<static_cast<unsigned>(blocks), 256, smem, st>>>(map, args, stage_count);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

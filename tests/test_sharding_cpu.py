@@ -71,11 +71,35 @@ def _worker(rank, world, port, tmpdir):
             return run
 
         rows = sh.run_sharded(make_detector, {"fc": logits}, dist=dist, detection=True)
+
+        def make_sparse_detector(batch):
+            def run(inputs):
+                # images with a positive first logit have one detection; a replica without any emits
+                # the layer's placeholder rows (label -1), one per image of its slice
+                hits = [[i, 2, float(inputs["fc"][i, 0]), 0, 0, 1, 1] for i in range(batch) if inputs["fc"][i, 0] > cut]
+                if hits:
+                    return np.asarray(hits, np.float32)
+                return np.asarray([[i, -1, -1, -1, -1, -1, -1] for i in range(batch)], np.float32)
+            return run
+
+        cut = float(np.sort(logits[:, 0])[-2])     # only the largest first logit passes: one replica has a hit
+        sparse = sh.run_sharded(make_sparse_detector, {"fc": logits}, dist=dist, detection=True)
+        cut = 1e9                                   # nobody has a hit: the placeholders of all images survive
+        empty = sh.run_sharded(make_sparse_detector, {"fc": logits}, dist=dist, detection=True)
+
+        def make_proposals(batch):
+            def run(inputs):
+                # two rois per local image, column 0 = image index within the slice
+                return np.asarray([[i, 0, 0, 4 + j, 4 + j] for i in range(batch) for j in range(2)], np.float32)
+            return run
+
+        rois = sh.run_sharded(make_proposals, {"fc": logits}, dist=dist, proposal=True)
         ragged = sh.gather_rows(np.full((rank + 1, 5), rank, np.float32), dist=dist)
         if rank == 0:
-            np.savez(os.path.join(tmpdir, "out.npz"), dense=dense, rows=rows, ragged=ragged, logits=logits)
+            np.savez(os.path.join(tmpdir, "out.npz"), dense=dense, rows=rows, ragged=ragged, logits=logits,
+                     sparse=sparse, empty=empty, rois=rois)
         else:
-            assert dense is None and rows is None and ragged is None
+            assert dense is None and rows is None and ragged is None and sparse is None and rois is None
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -91,5 +115,14 @@ def test_sharded_run_matches_single_replica(tmp_path, world):
     assert np.array_equal(got["dense"], want)                      # batch order preserved
     assert got["rows"][:, 0].tolist() == [float(i) for i in range(7)]  # image ids rebased
     assert np.array_equal(got["rows"][:, 2], got["logits"][:, 0])
+    # one replica had a detection, the others only placeholders: the single real row survives, with
+    # its global image id
+    best = int(np.argmax(got["logits"][:, 0]))
+    assert got["sparse"].shape == (1, 7) and got["sparse"][0, 0] == best and got["sparse"][0, 1] == 2
+    # no replica had any: one placeholder row per image of the whole batch, ids 0..6
+    assert got["empty"].shape == (7, 7) and (got["empty"][:, 1] == -1).all()
+    assert got["empty"][:, 0].tolist() == [float(i) for i in range(7)]
+    # Proposal rois: image ids rebased by the slice offsets
+    assert got["rois"][:, 0].tolist() == [float(i) for i in range(7) for _ in range(2)]
     assert got["ragged"].shape == (sum(r + 1 for r in range(world)), 5)
     assert got["ragged"][:, 0].tolist() == [float(r) for r in range(world) for _ in range(r + 1)]
