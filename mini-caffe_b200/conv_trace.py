@@ -105,8 +105,10 @@ def main():
         assert rc == 0, rc
         torch.cuda.synchronize()
         slots = L.mcb200_conv_trace_read(trace)
-        if slots == 0:
-            raise SystemExit("this library was built without the trace (make -C mini-caffe_b200/csrc trace)")
+        if slots == 0 and rep == args.reps - 1:
+            print("layer n=%d c=%d %dx%d cout=%d k=%d: %.1f us (library without the trace: time only)"
+                  % (args.n, args.c, args.hw, args.hw, args.cout, args.k, ev0.elapsed_time(ev1) * 1e3))
+            return
     t = np.ctypeslib.as_array(trace).reshape(4, SLOTS)
     mode = {0: "matrix", 1: "im2col", 2: "rows", 3: "halo"}[plan.im2col]
     print("layer n=%d c=%d %dx%d cout=%d k=%d stride=%d pad=%d: mode %s, tile width %d, cta pair %d, k-iterations %d, %.1f us"

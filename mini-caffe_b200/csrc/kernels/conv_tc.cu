@@ -147,7 +147,8 @@ struct SmemPlan {
   // K = 32 sub-tiles per stage.  Every stage costs each single-thread role a
   // barrier wait and a signal (a few hundred cycles of pure latency), so where
   // a K = 32 step is short (narrow tiles) a stage carries two of them.
-  // (Row mode has few, odd numbers of k-iterations per tile: single steps.)
+  // (Row mode keeps single steps: two filter rows per stage were measured and change nothing, its
+  // tiles are bound by their epilogue.  64-column tiles as CTA pairs were measured too: slower.)
   // Halo mode: a stage is one pixel strip plus the weight tiles of a whole filter row (sized at run time).
   static constexpr int kSub =
       (kMode != kModeRows && kMode != kModeHalo && kTileABytes + kTileBBytes <= 24 * 1024) ? 2 : 1;
