@@ -51,8 +51,9 @@ long long mcb200_kernel_timing_end_each(double* total_ms, double* each_ms, long 
 /* Diagnostic build only (`make -C mini-caffe_b200/csrc trace` -> lib/libcaffe_trace.so): the
  * convolution kernel's roles of CTA 0 stamp the SM's cycle counter at fixed points of their loops
  * (activation producer, weight producer, MMA issuer: two stamps per k-iteration; first epilogue
- * warp: two per tile).  Copies 4 x 2048 values (role-major, zero where nothing was recorded) to
- * `out`, clears the device array and returns 2048; the ordinary library returns 0.              */
+ * warp: two per tile, and in a fifth row five per 32 x 32 chunk of a launch with the staged
+ * epilogue).  Copies 5 x 2048 values (role-major, zero where nothing was recorded) to `out`,
+ * clears the device array and returns 2048; the ordinary library returns 0.                     */
 int mcb200_conv_trace_read(long long* out);
 
 int mcb200_probe_mma_peak(int bf16, int block_n, int cta_pair, int steps, int reps, double* ms, double* tflops,

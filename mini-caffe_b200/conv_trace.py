@@ -9,7 +9,7 @@ single-thread roles spend a k-iteration (cycles of the SM clock):
 
   producer A / B   wait for a free stage, time to issue the loads
   MMA issuer       wait for a full stage (this is where load latency shows), time to issue
-  epilogue warp 0  wait for the accumulator per tile, time to store the tile
+  epilogue warp 0  wait for the accumulator per tile, time to store the tile, and the phases of a chunk
 
 A diagnostic, not part of the engine; needs a GPU.
 """
@@ -23,6 +23,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 SLOTS = 2048
+ROLES = 5
 
 
 class ConvShape(ctypes.Structure):
@@ -75,14 +76,28 @@ def main():
                   args.pad, 1, 1, 1, 0, 0)
     assert L.mcb200_conv_out_shape(ctypes.byref(s)) == 0
     g = torch.Generator().manual_seed(0)
-    x = torch.randn((args.n, args.hw, args.hw, args.c), generator=g).cuda()
     w = (torch.randn((args.cout, args.c, args.k, args.k), generator=g) * 0.05).cuda()
-    packed = torch.empty(L.mcb200_conv_packed_weight_count(ctypes.byref(s)), device="cuda")
-    assert L.mcb200_conv_pack_weights(ctypes.byref(s), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(packed.data_ptr()), None) == 0
     raw = ctypes.create_string_buffer(ctypes.sizeof(ConvPlan) + 64)
     plan = ConvPlan.from_address((ctypes.addressof(raw) + 63) & ~63)
-    assert L.mcb200_conv_tc_plan(ctypes.byref(s), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(packed.data_ptr()),
-                                 ctypes.byref(plan)) == 0
+    if args.c <= 4:
+        # an image in front of the first layer: row mode over a zero-bordered copy with 4 floats per pixel
+        assert L.mcb200_conv_rows_supported(ctypes.byref(s)) == 1
+        L.mcb200_conv_rows_packed_weight_count.restype = ctypes.c_size_t
+        image = torch.randn((args.n, args.c, args.hw, args.hw), generator=g).cuda()
+        hp, wp = ctypes.c_int(), ctypes.c_int()
+        assert L.mcb200_conv_rows_padded_dims(ctypes.byref(s), ctypes.byref(hp), ctypes.byref(wp)) == 0
+        x = torch.zeros((args.n, hp.value, wp.value, 4), device="cuda")
+        assert L.mcb200_conv_rows_pad_input(ctypes.byref(s), ctypes.c_void_p(image.data_ptr()), ctypes.c_void_p(x.data_ptr()), None) == 0
+        packed = torch.empty(L.mcb200_conv_rows_packed_weight_count(ctypes.byref(s)), device="cuda")
+        assert L.mcb200_conv_rows_pack_weights(ctypes.byref(s), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(packed.data_ptr()), None) == 0
+        assert L.mcb200_conv_rows_plan(ctypes.byref(s), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(packed.data_ptr()),
+                                       ctypes.byref(plan)) == 0
+    else:
+        x = torch.randn((args.n, args.hw, args.hw, args.c), generator=g).cuda()
+        packed = torch.empty(L.mcb200_conv_packed_weight_count(ctypes.byref(s)), device="cuda")
+        assert L.mcb200_conv_pack_weights(ctypes.byref(s), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(packed.data_ptr()), None) == 0
+        assert L.mcb200_conv_tc_plan(ctypes.byref(s), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(packed.data_ptr()),
+                                     ctypes.byref(plan)) == 0
     out = torch.empty((args.n, s.ho, s.wo, args.cout), device="cuda")
     res = torch.randn((args.n, s.ho, s.wo, args.cout), generator=g).cuda() if args.residual else None
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -92,7 +107,7 @@ def main():
     if res is not None:
         ep.residual, ep.residual_ld = res.data_ptr(), args.cout
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    trace = (ctypes.c_longlong * (4 * SLOTS))()
+    trace = (ctypes.c_longlong * (ROLES * SLOTS))()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for rep in range(args.reps):
         flush.zero_()                      # the layer's input comes from DRAM, as inside a network
@@ -109,7 +124,7 @@ def main():
             print("layer n=%d c=%d %dx%d cout=%d k=%d: %.1f us (library without the trace: time only)"
                   % (args.n, args.c, args.hw, args.hw, args.cout, args.k, ev0.elapsed_time(ev1) * 1e3))
             return
-    t = np.ctypeslib.as_array(trace).reshape(4, SLOTS)
+    t = np.ctypeslib.as_array(trace).reshape(ROLES, SLOTS)
     mode = {0: "matrix", 1: "im2col", 2: "rows", 3: "halo"}[plan.im2col]
     print("layer n=%d c=%d %dx%d cout=%d k=%d stride=%d pad=%d: mode %s, tile width %d, cta pair %d, k-iterations %d, %.1f us"
           % (args.n, args.c, args.hw, args.hw, args.cout, args.k, args.stride, args.pad, mode, plan.block_n, plan.cta_pair,
@@ -131,6 +146,14 @@ def main():
         print(summary("epilogue: wait for accumulator", (pairs[1:, 0] - pairs[:-1, 1]).tolist()))
         print(summary("epilogue: store the tile", (pairs[:, 1] - pairs[:, 0]).tolist()))
         print("epilogue: %d tiles, %.0f cycles per tile" % (len(pairs), (pairs[-1, 1] - pairs[0, 0]) / max(1, len(pairs) - 1)))
+    c = t[4][t[4] > 0]
+    c = c[: len(c) // 5 * 5].reshape(-1, 5)
+    if len(c) >= 2:
+        print("epilogue warp 0, per 32 x 32 chunk (staged epilogue), %d chunks:" % len(c))
+        for name, col in (("  accumulator -> registers (tcgen05.ld)", 1), ("  wait for the slot / the residual", 2),
+                          ("  tail arithmetic + write to the slot", 3), ("  fence + store issue", 4)):
+            print(summary(name, (c[:, col] - c[:, col - 1]).tolist()))
+        print(summary("  from store issue to the next chunk", (c[1:, 0] - c[:-1, 4]).tolist()))
     if args.dump:
         origin = min(int(t[r][0]) for r in range(4) if t[r][0] > 0)
         print("k-iteration  A: free issued | B: free issued | MMA: full issued   (cycles since the first stamp)")

@@ -106,6 +106,15 @@ struct ConvTcArgs {
   int halo_staged;               // halo mode: results pass through a shared-memory slot so that the stores are
                                  // whole 128-byte rows (fp32 output with 16-byte aligned rows)
   long long wait_limit;          // bound of every barrier wait, in SM cycles
+  int resident_b_bytes;          // row mode: all filter rows' weight tiles stay in shared memory (bytes; 0 = streamed
+                                 // with the activations).  Every M tile of such a layer multiplies the same
+                                 // weights, and a third of what its ring pulled out of L2 was this one image.
+  // Row mode over planes (rows_strip): the zero-bordered copy keeps every stride_w-th pixel of a row
+  // together (stride_w planes per row), a k-iteration loads `plane_bytes` of each plane once, and
+  // the tensor core reads output pixel m's window straight out of it: pixel 2*kk and 2*kk + 1 of
+  // the window are one K = 8 step, their rows lie 16 bytes apart (un-swizzled core matrices).
+  int rows_strip;
+  int plane_bytes;
   int drop_last_weight_load;     // test hook: the weight producer leaves out its last k-iteration (see
                                  // mcb200_conv_test_drop_weight_load): the waits on that stage run out
 };
@@ -114,18 +123,30 @@ struct ConvTcArgs {
 // first epilogue warp of CTA 0 stamp clock64() at fixed points of their loops into a device
 // array that mcb200_conv_trace_read copies out.  Role 0: activation producer (per k-iteration:
 // stage free, loads issued); 1: weight producer (same); 2: MMA issuer (per k-iteration: stage
-// full, MMAs issued and committed); 3: epilogue warp 0 (per tile: accumulator ready, tile stored).
+// full, MMAs issued and committed); 3: epilogue warp 0 (per tile: accumulator ready, tile stored);
+// 4: the same warp inside its chunk loop, five stamps per 32 x 32 chunk of a launch with the staged
+// epilogue (chunk begins, accumulator in registers, slot free / residual there, tail computed and
+// written to the slot, store issued).
 #ifdef MCB200_CONV_TRACE
 constexpr int kTraceSlots = 2048;
-__device__ long long g_conv_trace[4 * kTraceSlots];
+constexpr int kTraceRoles = 5;
+__device__ long long g_conv_trace[kTraceRoles * kTraceSlots];
 #define MCB200_TRACE_DECL int trace_n = 0
 #define MCB200_TRACE(role)                                                                         \
   do {                                                                                             \
     if (blockIdx.x == 0 && trace_n < kTraceSlots) g_conv_trace[(role) * kTraceSlots + trace_n++] = clock64(); \
   } while (0)
+#define MCB200_TRACE_CHUNK_DECL int trace_c = 0
+#define MCB200_TRACE_CHUNK()                                                                       \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && ew == 0 && lane == 0 && trace_c < kTraceSlots)                          \
+      g_conv_trace[4 * kTraceSlots + trace_c++] = clock64();                                       \
+  } while (0)
 #else
 #define MCB200_TRACE_DECL
 #define MCB200_TRACE(role)
+#define MCB200_TRACE_CHUNK_DECL
+#define MCB200_TRACE_CHUNK()
 #endif
 
 constexpr int kMaxStages = 8;
@@ -220,6 +241,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ uint64_t tmem_empty_bar[2];
   __shared__ uint64_t res_bar[kEpilogueWarps][kMaxSlots];   // per epilogue warp, per staging slot
   __shared__ uint64_t col_bar[2];              // per-column table of a tile is complete
+  __shared__ uint64_t wres_bar;                // row mode: the resident weight tiles have landed
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ __align__(16) float col_scale[2][BN];   // per-column constants of the current tiles
@@ -229,9 +251,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
   const uint32_t raw_addr = smem_addr(smem_raw);
   uint8_t* tiles = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  const int stage_bytes = kMode == kModeHalo ? args.stage_bytes : Plan::kStageBytes;
-  const int stage_b_offset = kMode == kModeHalo ? args.stage_b_offset : Plan::kStageBOffset;
-  uint8_t* staging_base = tiles + stages * stage_bytes;
+  const int stage_bytes = (kMode == kModeHalo || kMode == kModeRows) ? args.stage_bytes : Plan::kStageBytes;
+  const int stage_b_offset = (kMode == kModeHalo || kMode == kModeRows) ? args.stage_b_offset : Plan::kStageBOffset;
+  const bool resident_b = kMode == kModeRows && args.resident_b_bytes > 0;
+  uint8_t* resident = tiles + stages * stage_bytes;   // stages are multiples of 1024 bytes: so is this address
+  uint8_t* staging_base = resident + (kMode == kModeRows ? args.resident_b_bytes : 0);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -250,22 +274,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int num_tiles = n_tiles * m_units;
   auto unit_to_mt = [&](int unit) { return kPair ? 2 * unit + static_cast<int>(rank) : unit; };
 
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 2);                      // one arrival per producer thread of this CTA
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
+  // Some fifty barriers: a thread each (one thread doing them all costs every launch most of a
+  // microsecond before its first load can go out).
+  {
+    const int t = static_cast<int>(threadIdx.x);
+    if (t == 0) abort_flag = 0;
+    if (t < stages) {
+      mbar_init(&full_bar[t], resident_b ? 1 : 2);     // one arrival per producer thread that fills the stage
+      mbar_init(&empty_bar[t], 1);
+      fence_barrier_init();
+    } else if (t >= 32 && t < 34) {
+      const int b = t - 32;
       mbar_init(&tmem_full_bar[b], 1);
       mbar_init(&tmem_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);   // one arrival per epilogue warp
       mbar_init(&col_bar[b], kEpilogueWarps);
+      fence_barrier_init();
+    } else if (t >= 64 && t < 64 + kEpilogueWarps * kMaxSlots) {
+      mbar_init(&res_bar[(t - 64) / kMaxSlots][(t - 64) % kMaxSlots], 1);
+      fence_barrier_init();
+    } else if (t == 34) {
+      tma_prefetch_descriptor(&map_a);
+      tma_prefetch_descriptor(&map_b);
+    } else if (t == 35) {
+      mbar_init(&wres_bar, 1);
+      fence_barrier_init();
     }
-    for (int w = 0; w < kEpilogueWarps; ++w)
-      for (int r = 0; r < kMaxSlots; ++r) mbar_init(&res_bar[w][r], 1);
-    fence_barrier_init();
-    tma_prefetch_descriptor(&map_a);
-    tma_prefetch_descriptor(&map_b);
   }
   if (warp == kWarpMma) {
     tmem_alloc(&tmem_base_slot, 2 * BN);
@@ -419,7 +452,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (j >= nsub) break;
             if (kMode == kModeRows) {
               // A sub-tile is one filter row: tile_rows pixels x (8 pixels x 4 channels) of a padded input row.
-              tma_load_4d(&map_a, bar, a_dst, 0, base_w, row_h, base_n);   // pixels past the row read as zero
+              if (args.rows_strip) {
+                // 16-pixel chunks [base_w / 16, ...) of every plane of padded row row_h (segments start at multiples of 128)
+                tma_load_5d(&map_a, bar, a_dst, 0, base_w >> 4, 0, row_h, base_n);
+              } else {
+                tma_load_4d(&map_a, bar, a_dst, 0, base_w, row_h, base_n);   // pixels past the row read as zero
+              }
               row_h += args.dil_h;
             } else if (kMode == kModeHalo) {
               // One strip of 128 + halo pixels x one channel block, at filter row off_h: every tap
@@ -474,6 +512,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int issued = 0;
       bool alive = true;
       MCB200_TRACE_DECL;
+      if (resident_b) {
+        // All filter rows at once, into their own region; the ring then carries activations only.
+        const int loads = args.drop_last_weight_load ? args.k_iters - 1 : args.k_iters;
+        mbar_expect_tx(&wres_bar, Plan::kTileBBytes * static_cast<uint32_t>(args.k_iters));
+        for (int k = 0; k < loads; ++k) tma_load_2d(&map_b, &wres_bar, resident + k * Plan::kTileBBytes, k * kElemsK, 0);
+        // The copies land before this CTA may release its shared memory (bounded, like every wait).
+        const long long start = clock64();
+        while (!mbar_try_wait(&wres_bar, 0u)) {
+          if (clock64() - start > wait_limit) break;
+        }
+        alive = false;   // nothing to stream
+      }
       for (int tile = worker; tile < num_tiles && alive; tile += workers) {
         // A CTA of a pair fetches the half of the weight tile that matches its rank.
         const int n0 = (tile % n_tiles) * BN + static_cast<int>(rank) * Plan::kTileBRows;
@@ -547,6 +597,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool alive = true;
       MCB200_TRACE_DECL;
       const uint32_t tiles_addr = smem_addr(tiles);
+      if (resident_b) {
+        if (!mbar_wait_bounded(&wres_bar, 0u, abort, wait_limit)) alive = false;
+        tc_fence_after_sync();
+      }
       for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
         const int ab = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1) & 1u;
@@ -565,7 +619,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int nsub = args.k_iters - k < Plan::kSub ? args.k_iters - k : Plan::kSub;
           const uint32_t a_addr = tiles_addr + static_cast<uint32_t>(pos.stage * stage_bytes);
           uint64_t desc_a = umma_desc_k_sw128(a_addr);
-          uint64_t desc_b = umma_desc_k_sw128(a_addr + stage_b_offset);
+          uint64_t desc_b = umma_desc_k_sw128(
+              resident_b ? smem_addr(resident) + static_cast<uint32_t>(k) * Plan::kTileBBytes : a_addr + stage_b_offset);
           if (kMode == kModeHalo) {
             // Tap s of the filter row reads the strip s * dil_w pixel rows (128 bytes each) further
             // down: the same swizzled bytes, another start address.  The swizzle is a function of
@@ -594,9 +649,26 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               desc_b += Plan::kTileBBytes >> 4;
             }
           }
+          if (kMode == kModeRows && args.rows_strip) {
+            // Window pixels (2 kk, 2 kk + 1) of every output pixel of the tile: with one plane they are
+            // neighbours in it (16 bytes on), with two planes they sit at the same index of plane 0 and 1.
+            const int steps = (args.kw + 1) >> 1;
+            const uint32_t lbo = args.stride_w == 1 ? 16u : static_cast<uint32_t>(args.plane_bytes);
+            const uint32_t step_bytes = args.stride_w == 1 ? 32u : 16u;
+#pragma unroll
+            for (int kk = 0; kk < kMmaPerBlock; ++kk) {
+              if (kk >= steps) break;
+              if (!kHalf) {
+                umma_tf32(tmem_acc, umma_desc_k_plain(a_addr + static_cast<uint32_t>(kk) * step_bytes, lbo, 128u),
+                          desc_b + 2 * kk, idesc, accumulate);
+              }
+              accumulate = 1u;
+            }
+          }
 #pragma unroll
           for (int j = 0; j < Plan::kSub; ++j) {
             if (kMode == kModeHalo) break;
+            if (kMode == kModeRows && args.rows_strip) break;
             if (j >= nsub) break;
 #pragma unroll
             for (int kk = 0; kk < kMmaPerBlock; ++kk) {
@@ -719,6 +791,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int local = 0;
     bool alive = true;
     MCB200_TRACE_DECL;
+    MCB200_TRACE_CHUNK_DECL;
     int table_n0[2] = {-1, -1};          // first column the per-column tables were filled for
     uint32_t table_fills[2] = {0u, 0u};
     for (int tile = worker; tile < num_tiles && alive; tile += workers, ++local) {
@@ -778,8 +851,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (col0 >= args.cout) break;          // uniform across the warp
         const int g = seq++;
         uint32_t acc[32];
+        MCB200_TRACE_CHUNK();
         tmem_load_32x32(tmem_acc + static_cast<uint32_t>(chunk * 32), acc);
         tmem_load_wait();
+        MCB200_TRACE_CHUNK();
         const float4* sc4 = reinterpret_cast<const float4*>(t_scale + chunk * 32);
         const float4* sh4 = reinterpret_cast<const float4*>(t_shift + chunk * 32);
         const float4* sl4 = reinterpret_cast<const float4*>(t_slope + chunk * 32);
@@ -854,6 +929,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             __syncwarp();
           }
+          MCB200_TRACE_CHUNK();
           // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
           // piece j stored at position j ^ (row & 7) (the 128-byte swizzle).
           // The result overwrites the residual in place.
@@ -919,6 +995,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(buf + ((j ^ swz) << 2)) = v[j];
           }
+          MCB200_TRACE_CHUNK();
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -929,6 +1006,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             tma_store_commit();
           }
+          MCB200_TRACE_CHUNK();
         } else {
           // ---- plain stores: rows that are not 16-byte aligned, and halo mode, whose tiles are
           // pieces of the virtual output grid (a lane's row may be one of the positions that are
@@ -1388,9 +1466,33 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     if (force_depth && atoi(force_depth) >= 1) args.res_depth = atoi(force_depth);
     if (args.res_depth > args.slots - 1) args.res_depth = args.slots - 1;
   }
+  if (kMode == kModeRows && !args.ep.residual) {
+    // One staging slot per warp: with the weights resident the ring then keeps eight activation
+    // tiles in flight (measured on 7 x 7 stride-2 and 3 x 3 first layers at batch 64: 3-7 % quicker
+    // than two slots and a six-deep ring).
+    args.slots = 1;
+    const char* force_slots = getenv("MCB200_ROWS_SLOTS");   // experiments: "1" / "2"
+    if (force_slots && (force_slots[0] == '1' || force_slots[0] == '2')) args.slots = force_slots[0] - '0';
+  }
   const int slot_bytes = (kHalf && args.out_half) ? 2048 : 4096;
   int stage_bytes = Plan::kStageBytes;
   int staging_bytes = Plan::staging_bytes(args.slots, slot_bytes);
+  int resident_bytes = 0;
+  if (kMode == kModeRows) {
+    // One N tile: every M tile multiplies the same kh weight tiles; they stay in shared memory
+    // when they take at most a quarter of it, and the ring carries activations only.
+    const long long all_rows = static_cast<long long>(args.k_iters) * Plan::kTileBBytes;
+    const char* off = getenv("MCB200_ROWS_RESIDENT");   // "0": stream the weights with the activations (experiments)
+    if (plan->shape.cout <= BN && all_rows <= 56 * 1024 && !(off && off[0] == '0')) resident_bytes = static_cast<int>(all_rows);
+    args.resident_b_bytes = resident_bytes;
+    args.rows_strip = plan->strip_rows > 0 ? 1 : 0;
+    args.plane_bytes = plan->strip_rows * 16;
+    if (args.rows_strip) args.a_bytes = plan->shape.stride_w * args.plane_bytes;
+    const int a_stage = args.rows_strip ? (args.a_bytes + 1023) / 1024 * 1024 : kTileABytes;
+    args.stage_b_offset = a_stage;
+    args.stage_bytes = resident_bytes ? a_stage : a_stage + Plan::kTileBBytes;
+    stage_bytes = args.stage_bytes;
+  }
   if (kMode == kModeHalo) {
     // A stage = the pixel strip (rounded up to the 1024-byte swizzle period) + the weight tiles of
     // the kw taps of one filter row.  The epilogue stores from registers: no staging.
@@ -1411,11 +1513,11 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     const char* pf = getenv("MCB200_L2_PREFETCH");
     args.l2_prefetch = (kMode != kModeRows && count <= 64 && pf && pf[0] == '1') ? 1 : 0;
   }
-  int stages = (dynamic_limit - 1024 - staging_bytes) / stage_bytes;
+  int stages = (dynamic_limit - 1024 - staging_bytes - resident_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   args.stages = stages;
-  const int dynamic_bytes = stages * stage_bytes + staging_bytes + 1024;
+  const int dynamic_bytes = stages * stage_bytes + staging_bytes + resident_bytes + 1024;
   const CUtensorMap* ma = reinterpret_cast<const CUtensorMap*>(plan->tma_a);
   const CUtensorMap* mb = reinterpret_cast<const CUtensorMap*>(plan->tma_b);
   const CUtensorMap* mo = reinterpret_cast<const CUtensorMap*>(plan->tma_out);
@@ -1754,7 +1856,7 @@ int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, co
   a.group_cout = plan->shape.group > 1 ? plan->shape.cout / plan->shape.group : 0;
   a.group_cin = plan->shape.group > 1 ? plan->shape.c / plan->shape.group : 0;
   a.wp = plan->shape.wo;
-  a.stage_bytes = a.stage_b_offset = 0;
+  a.stage_bytes = a.stage_b_offset = a.resident_b_bytes = a.rows_strip = a.plane_bytes = 0;
   if (plan->im2col == kModeHalo) {
     // Tiles are pieces of the virtual output grid: results leave through plain (128-bit) stores.
     a.tma_epilogue = 0;
@@ -1883,6 +1985,45 @@ __global__ void pad_nhwc4_kernel(const float* __restrict__ src, float4* __restri
   }
 }
 
+// The same copy with the pixels of a row sorted into `planes` planes of `wq` pixels: padded pixel
+// x goes to plane x % planes, index x / planes (what the strip form of row mode loads).
+__global__ void pad_nhwc4_planes_kernel(const float* __restrict__ src, float4* __restrict__ dst, int n, int c, int h,
+                                        int w, int pad_h, int pad_w, int hp, int planes, int wq) {
+  const long long total = static_cast<long long>(n) * hp * planes * wq;
+  const size_t plane = static_cast<size_t>(h) * w;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int iq = static_cast<int>(i % wq);
+    const int pl = static_cast<int>((i / wq) % planes);
+    const int yp = static_cast<int>((i / (static_cast<long long>(wq) * planes)) % hp);
+    const int img = static_cast<int>(i / (static_cast<long long>(wq) * planes * hp));
+    const int x = iq * planes + pl - pad_w, y = yp - pad_h;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (x >= 0 && x < w && y >= 0 && y < h) {
+      const float* s = src + static_cast<size_t>(img) * c * plane + static_cast<size_t>(y) * w + x;
+      v.x = s[0];
+      if (c > 1) v.y = s[plane];
+      if (c > 2) v.z = s[2 * plane];
+      if (c > 3) v.w = s[3 * plane];
+    }
+    dst[i] = v;
+  }
+}
+
+// Strip form of row mode (filter strides 1 and 2), only with MCB200_ROWS_STRIP=1.  It pulls four to
+// seven times fewer bytes out of L2 than the overlapping-window form and computes the same values,
+// but the tensor core reads an un-swizzled operand slowly: measured at batch 64, a 7 x 7 stride-2
+// first layer takes 683 cycles per filter row instead of 530 (the four MMAs alone occupy their
+// issuing thread for 304 cycles instead of 85), and the 3 x 3 first layers of MobileNet and SSD,
+// whose tiles are bound by their epilogue, do not change.  The padded copy's layout and the plan
+// both follow this predicate.
+bool rows_strip_layout(const mcb200_conv_shape* s) {
+  const char* on = getenv("MCB200_ROWS_STRIP");
+  return (s->stride_w == 1 || s->stride_w == 2) && on && on[0] == '1';
+}
+
+constexpr int kStripPixels = 144;   // per plane and load: 128 output pixels + the window's reach, in chunks of 16
+
 }  // namespace
 }  // namespace mcb200
 
@@ -1900,6 +2041,11 @@ extern "C" int mcb200_conv_rows_padded_dims(const mcb200_conv_shape* s, int* hp,
   *hp = t.h + 2 * t.pad_h;
   const int reach = (t.wo - 1) * t.stride_w + 8;   // the last tile row reads 8 pixels
   *wp = t.w + 2 * t.pad_w > reach ? t.w + 2 * t.pad_w : reach;
+  if (rows_strip_layout(&t)) {
+    // stride_w planes per row, each a whole number of 16-pixel chunks
+    const int wq = ((*wp + t.stride_w - 1) / t.stride_w + 15) / 16 * 16;
+    *wp = wq * t.stride_w;
+  }
   return 0;
 }
 
@@ -1926,8 +2072,14 @@ extern "C" int mcb200_conv_rows_pad_input(const mcb200_conv_shape* s, const floa
   if (total == 0) return 0;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  pad_nhwc4_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, wp);
+  if (rows_strip_layout(s)) {
+    pad_nhwc4_planes_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, s->stride_w,
+        wp / s->stride_w);
+  } else {
+    pad_nhwc4_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, wp);
+  }
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
@@ -1959,6 +2111,22 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   // Activation view: 32 floats (8 pixels x 4 channels) starting at padded pixel q * stride_w of padded row y.
   // Consecutive q overlap (the pitch of dimension 1 is stride_w pixels, less than the 8-pixel extent).
   CUtensorMap* ma = reinterpret_cast<CUtensorMap*>(plan->tma_a);
+  CUresult r;
+  if (rows_strip_layout(s)) {
+    // Strip form: (64 floats = a chunk of 16 pixels, chunks of a plane, planes, padded rows, images); a load takes
+    // kStripPixels / 16 chunks of every plane of one row, un-swizzled, so that a plane's pixels lie 16 bytes apart.
+    const cuuint64_t planes = static_cast<cuuint64_t>(s->stride_w);
+    const cuuint64_t wq = static_cast<cuuint64_t>(wp) / planes;
+    plan->strip_rows = kStripPixels;
+    const cuuint64_t dims5[5] = {64, wq / 16, planes, static_cast<cuuint64_t>(hp), static_cast<cuuint64_t>(s->n)};
+    const cuuint64_t strides5[4] = {256, wq * 16, planes * wq * 16, planes * wq * 16 * hp};
+    const cuuint32_t box5[5] = {64, kStripPixels / 16, static_cast<cuuint32_t>(planes), 1, 1};
+    const cuuint32_t estr5[5] = {1, 1, 1, 1, 1};
+    r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(padded_in), dims5, strides5, box5, estr5,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
+  }
   const cuuint64_t dims[4] = {kBlockK, static_cast<cuuint64_t>(plan->shape.wo), static_cast<cuuint64_t>(hp),
                               static_cast<cuuint64_t>(s->n)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s->stride_w) * 16, static_cast<cuuint64_t>(wp) * 16,
@@ -1966,10 +2134,12 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   // One M tile = up to 128 output pixels of a row; wider rows are cut into segments.
   const cuuint32_t box[4] = {kBlockK, static_cast<cuuint32_t>(plan->shape.wo < kBlockM ? plan->shape.wo : kBlockM), 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(padded_in), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
+  if (!rows_strip_layout(s)) {
+    r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(padded_in), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
+  }
   CUtensorMap* mb = reinterpret_cast<CUtensorMap*>(plan->tma_b);
   const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kBlockK;
   const cuuint64_t bdims[2] = {kp, static_cast<cuuint64_t>(s->cout)};
@@ -1983,15 +2153,17 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   return 0;
 }
 
-// With -DMCB200_CONV_TRACE: copies the cycle stamps of the last traced launches' CTA 0 (4 roles x
+// With -DMCB200_CONV_TRACE: copies the cycle stamps of the last traced launches' CTA 0 (5 roles x
 // 2048 slots, see MCB200_TRACE above) to `out` and clears the device array; returns the number
 // of values per role, or 0 when the library was built without the trace.
 extern "C" int mcb200_conv_trace_read(long long* out) {
 #ifdef MCB200_CONV_TRACE
   if (!out) return -1;
   if (cudaDeviceSynchronize() != cudaSuccess) return -2;
-  if (cudaMemcpyFromSymbol(out, mcb200::g_conv_trace, sizeof(long long) * 4 * mcb200::kTraceSlots) != cudaSuccess) return -3;
-  static long long zeros[4 * mcb200::kTraceSlots];
+  if (cudaMemcpyFromSymbol(out, mcb200::g_conv_trace, sizeof(long long) * mcb200::kTraceRoles * mcb200::kTraceSlots) !=
+      cudaSuccess)
+    return -3;
+  static long long zeros[mcb200::kTraceRoles * mcb200::kTraceSlots];
   if (cudaMemcpyToSymbol(mcb200::g_conv_trace, zeros, sizeof(zeros)) != cudaSuccess) return -4;
   return mcb200::kTraceSlots;
 #else

@@ -271,6 +271,67 @@ __global__ void pool_nhwc_kernel(const float* __restrict__ in, float* __restrict
   }
 }
 
+// A window that covers the whole image (global pooling in front of a classifier: 7 x 7 pixels,
+// thousands of channels, one output pixel).  One thread per output would walk the pixels in a
+// dependent loop with few threads in all; here a block takes one image and 128 channels, its
+// eight warps take every eighth pixel (all loads of a thread are independent), and warp 0 adds
+// the eight partial results in a fixed order.
+constexpr int kGlobalPoolWarps = 8;
+
+__global__ void __launch_bounds__(32 * kGlobalPoolWarps)
+pool_global_kernel(const float4* __restrict__ in, float4* __restrict__ out, int pixels, int cg, int chunks, int method,
+                   float area) {
+  __shared__ float4 part[kGlobalPoolWarps][32];
+  const int n = blockIdx.x / chunks;
+  const int g = (blockIdx.x - n * chunks) * 32 + (threadIdx.x & 31);   // group of four channels
+  const int w = threadIdx.x >> 5;
+  const bool is_max = method == MCB200_POOL_MAX;
+  float4 acc = is_max ? make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX) : make_float4(0.f, 0.f, 0.f, 0.f);
+  if (g < cg) {
+    const float4* p = in + static_cast<size_t>(n) * pixels * cg + g;
+#pragma unroll 4
+    for (int i = w; i < pixels; i += kGlobalPoolWarps) {
+      const float4 v = __ldg(p + static_cast<size_t>(i) * cg);
+      if (is_max) {
+        acc.x = fmaxf(acc.x, v.x);
+        acc.y = fmaxf(acc.y, v.y);
+        acc.z = fmaxf(acc.z, v.z);
+        acc.w = fmaxf(acc.w, v.w);
+      } else {
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+    }
+  }
+  part[w][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (w == 0 && g < cg) {
+    for (int j = 1; j < kGlobalPoolWarps; ++j) {
+      const float4 v = part[j][threadIdx.x];
+      if (is_max) {
+        acc.x = fmaxf(acc.x, v.x);
+        acc.y = fmaxf(acc.y, v.y);
+        acc.z = fmaxf(acc.z, v.z);
+        acc.w = fmaxf(acc.w, v.w);
+      } else {
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+    }
+    if (!is_max) {
+      acc.x /= area;
+      acc.y /= area;
+      acc.z /= area;
+      acc.w /= area;
+    }
+    out[static_cast<size_t>(n) * cg + g] = acc;
+  }
+}
+
 // Max pooling with a K x K window (K = 2, 3), channels % 4 == 0: one thread per
 // output pixel and four channels.  All K*K loads are issued before the first
 // comparison (taps outside the image read nothing and count as -FLT_MAX), so
@@ -377,6 +438,54 @@ __global__ void softmax_rows_kernel(const float* __restrict__ in, float* __restr
     for (int c = lane; c < channels; c += 32) s += expf(x[c] - m);
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     for (int c = lane; c < channels; c += 32) y[c] = expf(x[c] - m) / s;
+  }
+}
+
+// inner == 1, long rows (a classifier's 1000 scores) and too few of them to fill the GPU with one
+// warp each: a block per row, the row held in registers (up to eight values per thread), the two
+// reductions through shuffles and one shared array.
+constexpr int kSoftmaxBlock = 128;
+constexpr int kSoftmaxPerThread = 8;
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* scratch) {
+  for (int o = 16; o > 0; o >>= 1) {
+    const float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, u) : v + u;
+  }
+  __syncthreads();   // the previous reduction's readers are done with scratch
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = scratch[0];
+  for (int j = 1; j < kSoftmaxBlock / 32; ++j) r = is_max ? fmaxf(r, scratch[j]) : r + scratch[j];
+  return r;
+}
+
+__global__ void __launch_bounds__(kSoftmaxBlock)
+softmax_row_block_kernel(const float* __restrict__ in, float* __restrict__ out, int channels) {
+  __shared__ float scratch[kSoftmaxBlock / 32];
+  const float* x = in + static_cast<size_t>(blockIdx.x) * channels;
+  float* y = out + static_cast<size_t>(blockIdx.x) * channels;
+  float v[kSoftmaxPerThread];
+  float m = -FLT_MAX;
+#pragma unroll
+  for (int j = 0; j < kSoftmaxPerThread; ++j) {
+    const int c = threadIdx.x + j * kSoftmaxBlock;
+    v[j] = c < channels ? x[c] : -FLT_MAX;
+    m = fmaxf(m, v[j]);
+  }
+  m = block_reduce(m, true, scratch);
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < kSoftmaxPerThread; ++j) {
+    const int c = threadIdx.x + j * kSoftmaxBlock;
+    v[j] = c < channels ? expf(v[j] - m) : 0.f;
+    s += v[j];
+  }
+  s = block_reduce(s, false, scratch);
+#pragma unroll
+  for (int j = 0; j < kSoftmaxPerThread; ++j) {
+    const int c = threadIdx.x + j * kSoftmaxBlock;
+    if (c < channels) y[c] = v[j] / s;
   }
 }
 
@@ -578,7 +687,14 @@ extern "C" int mcb200_pool_nhwc(const float* in, float* out, int n, int h, int w
   const long long items = static_cast<long long>(n) * ho * wo * (vec ? c / 4 : c);
   const bool small_max = vec && method == MCB200_POOL_MAX && kh == kw && (kh == 2 || kh == 3) &&
                          items < 0x7fffffffLL;
-  if (small_max) {
+  const bool whole_image = vec && ho == 1 && wo == 1 && ph == 0 && pw == 0 && kh >= h && kw >= w && h * w >= 16 &&
+                           static_cast<long long>(n) * ((c / 4 + 31) / 32) < 0x7fffffffLL;
+  if (whole_image) {
+    const int chunks = (c / 4 + 31) / 32;
+    pool_global_kernel<<<n * chunks, 32 * kGlobalPoolWarps, 0, as_stream(stream)>>>(
+        reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out), h * w, c / 4, chunks, method,
+        static_cast<float>(h * w));
+  } else if (small_max) {
     const float4* in4 = reinterpret_cast<const float4*>(in);
     float4* out4 = reinterpret_cast<float4*>(out);
     if (kh == 3) {
@@ -623,7 +739,9 @@ extern "C" int mcb200_pool_max_nhwc_bf16(const uint16_t* in, uint16_t* out, int 
 extern "C" int mcb200_softmax(const float* in, float* out, int outer, int channels, int inner, void* stream) {
   if (!in || !out || outer < 0 || channels < 1 || inner < 1) return -1;
   if (outer == 0) return 0;
-  if (inner == 1) {
+  if (inner == 1 && channels > 128 && channels <= kSoftmaxBlock * kSoftmaxPerThread && outer <= 148 * 16 * 8) {
+    softmax_row_block_kernel<<<outer, kSoftmaxBlock, 0, as_stream(stream)>>>(in, out, channels);
+  } else if (inner == 1) {
     const int threads = 256;
     const int rows_per_block = threads / 32;
     softmax_rows_kernel<<<grid_for((static_cast<long long>(outer) + rows_per_block - 1) / rows_per_block * threads,

@@ -108,7 +108,26 @@ def test_first_layer_convolution_with_wide_rows(capi, gpu_engine, reflib, channe
     assert_close(got["c"], want["c"], "wide first layer")
 
 
-@pytest.mark.parametrize("stride,size", [(1, (14, 14)), (2, (15, 9)), (1, (5, 3)), (2, (2, 2))])
+@pytest.mark.parametrize("size,k,stride,pad,cout", [((23, 300), 3, 1, 1, 64), ((30, 257), 7, 2, 3, 24),
+                                                    ((17, 40), 3, 2, 1, 32)])
+def test_first_layer_strip_form(monkeypatch, capi, gpu_engine, reflib, size, k, stride, pad, cout):
+    """The opt-in strip form of row mode (the padded image sorted into stride_w planes, one load per
+    filter row, un-swizzled operand descriptors) computes what the default form computes."""
+    monkeypatch.setenv("MCB200_ROWS_STRIP", "1")
+    wl = pkg("workloads")
+    b = wl.NetBuilder("strip")
+    b.input([("data", (2, 3) + size)])
+    b.conv("c", "data", "c", 3, cout, k, stride=stride, pad=pad)
+    b.relu("c_relu", "c")
+    weights = wl.init_params(b.params, seed=23)
+    x = {"data": np.random.default_rng(24).standard_normal((2, 3) + size).astype(np.float32)}
+    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["c"])
+    assert_close(got["c"], want["c"], "strip form")
+    assert tensor_core_launches(capi, gpu_engine, b, weights, x) == 1
+
+
+@pytest.mark.parametrize("stride,size", [(1, (14, 14)), (2, (15, 9)), (1, (5, 3)), (2, (2, 2)), (1, (17, 23)),
+                                         (2, (33, 19)), (1, (8, 8)), (2, (16, 17))])
 def test_depthwise_3x3_sizes(capi, gpu_engine, reflib, stride, size):
     wl = pkg("workloads")
     b = wl.NetBuilder("dw3")
@@ -146,6 +165,29 @@ def test_global_pooling_odd_channels(capi, gpu_engine, reflib):
     got, want = both(capi, gpu_engine, reflib, b, {}, x, ["g", "m"], marks=["g"])
     assert np.abs(got["g"] - want["g"]).max() <= 1e-6
     assert np.array_equal(got["m"], want["m"])
+
+
+def test_global_pooling_wide_and_long_softmax_rows(capi, gpu_engine, reflib):
+    """A classifier's tail: a pooling window over the whole 7 x 7 image with many channels (a block per
+    image and 128 channels, partial sums added in a fixed order) and softmax over rows of hundreds of
+    values (a block per row)."""
+    wl = pkg("workloads")
+    b = wl.NetBuilder("tail")
+    b.input([("data", (3, 136, 7, 7)), ("scores", (5, 1000)), ("short", (2, 300))])
+    b.pool("g", "data", "g", "AVE", global_pooling=True)
+    b.pool("m", "data", "m", "MAX", global_pooling=True)
+    b.softmax("p", "scores", "p", axis=1)
+    b.softmax("q", "short", "q", axis=1)
+    rng = np.random.default_rng(14)
+    x = {"data": rng.standard_normal((3, 136, 7, 7)).astype(np.float32),
+         "scores": rng.standard_normal((5, 1000)).astype(np.float32) * 4,
+         "short": rng.standard_normal((2, 300)).astype(np.float32) * 4}
+    got, want = both(capi, gpu_engine, reflib, b, {}, x, ["g", "m", "p", "q"], marks=["g", "p"])
+    assert np.abs(got["g"] - want["g"]).max() <= 1e-6
+    assert np.array_equal(got["m"], want["m"])
+    for name in ("p", "q"):
+        assert np.abs(got[name] - want[name]).max() <= 2e-6, name
+        assert np.abs(got[name].sum(axis=1) - 1).max() <= 1e-5
 
 
 def test_softmax_axes(capi, gpu_engine, reflib):
