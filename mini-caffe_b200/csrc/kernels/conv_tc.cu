@@ -109,12 +109,6 @@ struct ConvTcArgs {
   int resident_b_bytes;          // row mode: all filter rows' weight tiles stay in shared memory (bytes; 0 = streamed
                                  // with the activations).  Every M tile of such a layer multiplies the same
                                  // weights, and a third of what its ring pulled out of L2 was this one image.
-  // Row mode over planes (rows_strip): the zero-bordered copy keeps every stride_w-th pixel of a row
-  // together (stride_w planes per row), a k-iteration loads `plane_bytes` of each plane once, and
-  // the tensor core reads output pixel m's window straight out of it: pixel 2*kk and 2*kk + 1 of
-  // the window are one K = 8 step, their rows lie 16 bytes apart (un-swizzled core matrices).
-  int rows_strip;
-  int plane_bytes;
   int drop_last_weight_load;     // test hook: the weight producer leaves out its last k-iteration (see
                                  // mcb200_conv_test_drop_weight_load): the waits on that stage run out
 };
@@ -452,12 +446,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (j >= nsub) break;
             if (kMode == kModeRows) {
               // A sub-tile is one filter row: tile_rows pixels x (8 pixels x 4 channels) of a padded input row.
-              if (args.rows_strip) {
-                // 16-pixel chunks [base_w / 16, ...) of every plane of padded row row_h (segments start at multiples of 128)
-                tma_load_5d(&map_a, bar, a_dst, 0, base_w >> 4, 0, row_h, base_n);
-              } else {
-                tma_load_4d(&map_a, bar, a_dst, 0, base_w, row_h, base_n);   // pixels past the row read as zero
-              }
+              tma_load_4d(&map_a, bar, a_dst, 0, base_w, row_h, base_n);   // pixels past the row read as zero
               row_h += args.dil_h;
             } else if (kMode == kModeHalo) {
               // One strip of 128 + halo pixels x one channel block, at filter row off_h: every tap
@@ -649,26 +638,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               desc_b += Plan::kTileBBytes >> 4;
             }
           }
-          if (kMode == kModeRows && args.rows_strip) {
-            // Window pixels (2 kk, 2 kk + 1) of every output pixel of the tile: with one plane they are
-            // neighbours in it (16 bytes on), with two planes they sit at the same index of plane 0 and 1.
-            const int steps = (args.kw + 1) >> 1;
-            const uint32_t lbo = args.stride_w == 1 ? 16u : static_cast<uint32_t>(args.plane_bytes);
-            const uint32_t step_bytes = args.stride_w == 1 ? 32u : 16u;
-#pragma unroll
-            for (int kk = 0; kk < kMmaPerBlock; ++kk) {
-              if (kk >= steps) break;
-              if (!kHalf) {
-                umma_tf32(tmem_acc, umma_desc_k_plain(a_addr + static_cast<uint32_t>(kk) * step_bytes, lbo, 128u),
-                          desc_b + 2 * kk, idesc, accumulate);
-              }
-              accumulate = 1u;
-            }
-          }
 #pragma unroll
           for (int j = 0; j < Plan::kSub; ++j) {
             if (kMode == kModeHalo) break;
-            if (kMode == kModeRows && args.rows_strip) break;
             if (j >= nsub) break;
 #pragma unroll
             for (int kk = 0; kk < kMmaPerBlock; ++kk) {
@@ -1467,10 +1439,8 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     if (args.res_depth > args.slots - 1) args.res_depth = args.slots - 1;
   }
   if (kMode == kModeRows && !args.ep.residual) {
-    // One staging slot per warp: with the weights resident the ring then keeps eight activation
-    // tiles in flight (measured on 7 x 7 stride-2 and 3 x 3 first layers at batch 64: 3-7 % quicker
-    // than two slots and a six-deep ring).
-    args.slots = 1;
+    // (One staging slot and a deeper ring: quicker on the layer alone with a flushed L2, slower
+    // inside ResNet-50.)
     const char* force_slots = getenv("MCB200_ROWS_SLOTS");   // experiments: "1" / "2"
     if (force_slots && (force_slots[0] == '1' || force_slots[0] == '2')) args.slots = force_slots[0] - '0';
   }
@@ -1485,12 +1455,8 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
     const char* off = getenv("MCB200_ROWS_RESIDENT");   // "0": stream the weights with the activations (experiments)
     if (plan->shape.cout <= BN && all_rows <= 56 * 1024 && !(off && off[0] == '0')) resident_bytes = static_cast<int>(all_rows);
     args.resident_b_bytes = resident_bytes;
-    args.rows_strip = plan->strip_rows > 0 ? 1 : 0;
-    args.plane_bytes = plan->strip_rows * 16;
-    if (args.rows_strip) args.a_bytes = plan->shape.stride_w * args.plane_bytes;
-    const int a_stage = args.rows_strip ? (args.a_bytes + 1023) / 1024 * 1024 : kTileABytes;
-    args.stage_b_offset = a_stage;
-    args.stage_bytes = resident_bytes ? a_stage : a_stage + Plan::kTileBBytes;
+    args.stage_b_offset = kTileABytes;
+    args.stage_bytes = resident_bytes ? kTileABytes : kTileABytes + Plan::kTileBBytes;
     stage_bytes = args.stage_bytes;
   }
   if (kMode == kModeHalo) {
@@ -1856,7 +1822,7 @@ int launch_core(mcb200_conv_plan* plan, void* out, bool out_half, int out_ld, co
   a.group_cout = plan->shape.group > 1 ? plan->shape.cout / plan->shape.group : 0;
   a.group_cin = plan->shape.group > 1 ? plan->shape.c / plan->shape.group : 0;
   a.wp = plan->shape.wo;
-  a.stage_bytes = a.stage_b_offset = a.resident_b_bytes = a.rows_strip = a.plane_bytes = 0;
+  a.stage_bytes = a.stage_b_offset = a.resident_b_bytes = 0;
   if (plan->im2col == kModeHalo) {
     // Tiles are pieces of the virtual output grid: results leave through plain (128-bit) stores.
     a.tma_epilogue = 0;
@@ -1985,45 +1951,6 @@ __global__ void pad_nhwc4_kernel(const float* __restrict__ src, float4* __restri
   }
 }
 
-// The same copy with the pixels of a row sorted into `planes` planes of `wq` pixels: padded pixel
-// x goes to plane x % planes, index x / planes (what the strip form of row mode loads).
-__global__ void pad_nhwc4_planes_kernel(const float* __restrict__ src, float4* __restrict__ dst, int n, int c, int h,
-                                        int w, int pad_h, int pad_w, int hp, int planes, int wq) {
-  const long long total = static_cast<long long>(n) * hp * planes * wq;
-  const size_t plane = static_cast<size_t>(h) * w;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int iq = static_cast<int>(i % wq);
-    const int pl = static_cast<int>((i / wq) % planes);
-    const int yp = static_cast<int>((i / (static_cast<long long>(wq) * planes)) % hp);
-    const int img = static_cast<int>(i / (static_cast<long long>(wq) * planes * hp));
-    const int x = iq * planes + pl - pad_w, y = yp - pad_h;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (x >= 0 && x < w && y >= 0 && y < h) {
-      const float* s = src + static_cast<size_t>(img) * c * plane + static_cast<size_t>(y) * w + x;
-      v.x = s[0];
-      if (c > 1) v.y = s[plane];
-      if (c > 2) v.z = s[2 * plane];
-      if (c > 3) v.w = s[3 * plane];
-    }
-    dst[i] = v;
-  }
-}
-
-// Strip form of row mode (filter strides 1 and 2), only with MCB200_ROWS_STRIP=1.  It pulls four to
-// seven times fewer bytes out of L2 than the overlapping-window form and computes the same values,
-// but the tensor core reads an un-swizzled operand slowly: measured at batch 64, a 7 x 7 stride-2
-// first layer takes 683 cycles per filter row instead of 530 (the four MMAs alone occupy their
-// issuing thread for 304 cycles instead of 85), and the 3 x 3 first layers of MobileNet and SSD,
-// whose tiles are bound by their epilogue, do not change.  The padded copy's layout and the plan
-// both follow this predicate.
-bool rows_strip_layout(const mcb200_conv_shape* s) {
-  const char* on = getenv("MCB200_ROWS_STRIP");
-  return (s->stride_w == 1 || s->stride_w == 2) && on && on[0] == '1';
-}
-
-constexpr int kStripPixels = 144;   // per plane and load: 128 output pixels + the window's reach, in chunks of 16
-
 }  // namespace
 }  // namespace mcb200
 
@@ -2041,11 +1968,6 @@ extern "C" int mcb200_conv_rows_padded_dims(const mcb200_conv_shape* s, int* hp,
   *hp = t.h + 2 * t.pad_h;
   const int reach = (t.wo - 1) * t.stride_w + 8;   // the last tile row reads 8 pixels
   *wp = t.w + 2 * t.pad_w > reach ? t.w + 2 * t.pad_w : reach;
-  if (rows_strip_layout(&t)) {
-    // stride_w planes per row, each a whole number of 16-pixel chunks
-    const int wq = ((*wp + t.stride_w - 1) / t.stride_w + 15) / 16 * 16;
-    *wp = wq * t.stride_w;
-  }
   return 0;
 }
 
@@ -2072,14 +1994,8 @@ extern "C" int mcb200_conv_rows_pad_input(const mcb200_conv_shape* s, const floa
   if (total == 0) return 0;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  if (rows_strip_layout(s)) {
-    pad_nhwc4_planes_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, s->stride_w,
-        wp / s->stride_w);
-  } else {
-    pad_nhwc4_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, wp);
-  }
+  pad_nhwc4_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, wp);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
@@ -2108,25 +2024,15 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   plan->k_iters = s->kh;
   plan->block_n = pick_block_n(s->cout, plan->m, plan->k_iters);
   plan->im2col = kModeRows;
+  // (Measured and dropped: a strip form that sorts the padded row into stride_w planes, loads a
+  // filter row's pixels once (four to seven times fewer bytes out of L2) and lets the tensor core
+  // read the windows through un-swizzled descriptors, rows 16 bytes apart.  Same values, but an
+  // MMA with an un-swizzled operand occupied its issuing thread 76 cycles instead of 21, a 7 x 7
+  // stride-2 first layer at batch 64 took 135 us instead of 106, and even the runtime switch
+  // between the two forms cost the single-thread loops 100 cycles per filter row.)
   // Activation view: 32 floats (8 pixels x 4 channels) starting at padded pixel q * stride_w of padded row y.
   // Consecutive q overlap (the pitch of dimension 1 is stride_w pixels, less than the 8-pixel extent).
   CUtensorMap* ma = reinterpret_cast<CUtensorMap*>(plan->tma_a);
-  CUresult r;
-  if (rows_strip_layout(s)) {
-    // Strip form: (64 floats = a chunk of 16 pixels, chunks of a plane, planes, padded rows, images); a load takes
-    // kStripPixels / 16 chunks of every plane of one row, un-swizzled, so that a plane's pixels lie 16 bytes apart.
-    const cuuint64_t planes = static_cast<cuuint64_t>(s->stride_w);
-    const cuuint64_t wq = static_cast<cuuint64_t>(wp) / planes;
-    plan->strip_rows = kStripPixels;
-    const cuuint64_t dims5[5] = {64, wq / 16, planes, static_cast<cuuint64_t>(hp), static_cast<cuuint64_t>(s->n)};
-    const cuuint64_t strides5[4] = {256, wq * 16, planes * wq * 16, planes * wq * 16 * hp};
-    const cuuint32_t box5[5] = {64, kStripPixels / 16, static_cast<cuuint32_t>(planes), 1, 1};
-    const cuuint32_t estr5[5] = {1, 1, 1, 1, 1};
-    r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(padded_in), dims5, strides5, box5, estr5,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
-  }
   const cuuint64_t dims[4] = {kBlockK, static_cast<cuuint64_t>(plan->shape.wo), static_cast<cuuint64_t>(hp),
                               static_cast<cuuint64_t>(s->n)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s->stride_w) * 16, static_cast<cuuint64_t>(wp) * 16,
@@ -2134,12 +2040,10 @@ extern "C" int mcb200_conv_rows_plan(const mcb200_conv_shape* s, const float* pa
   // One M tile = up to 128 output pixels of a row; wider rows are cut into segments.
   const cuuint32_t box[4] = {kBlockK, static_cast<cuuint32_t>(plan->shape.wo < kBlockM ? plan->shape.wo : kBlockM), 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  if (!rows_strip_layout(s)) {
-    r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(padded_in), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
-  }
+  CUresult r = api.tiled(ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(padded_in), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -100 - static_cast<int>(r);
   CUtensorMap* mb = reinterpret_cast<CUtensorMap*>(plan->tma_b);
   const cuuint64_t kp = static_cast<cuuint64_t>(plan->k_iters) * kBlockK;
   const cuuint64_t bdims[2] = {kp, static_cast<cuuint64_t>(s->cout)};

@@ -108,16 +108,6 @@ __device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, uint64_t* ba
       : "memory");
 }
 
-__device__ __forceinline__ void tma_load_5d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y, int z,
-                                            int w, int v) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      :
-      : "r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z),
-        "r"(w), "r"(v)
-      : "memory");
-}
-
 // im2col mode over a (C, W, H, N) tensor: (c, w, h, n) is the first channel and
 // the base pixel (top-left of the filter window) of the first output pixel of
 // the tile, (off_w, off_h) the filter-tap offset in input pixels.
@@ -288,20 +278,6 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_byte_addr) {
   d |= static_cast<uint64_t>(1) << 46;                           // descriptor version (Blackwell)
   d |= static_cast<uint64_t>(2) << 61;                           // layout: SWIZZLE_128B
   return d;
-}
-
-// Shared-memory operand descriptor for a K-major tile stored without swizzle: the unit is a
-// core matrix of 8 rows x 16 bytes (row r at byte 16 * r); `sbo` is the distance from one group
-// of 8 rows to the next, `lbo` the distance from one 16-byte step along K to the next.  Neither
-// has to be the dense value: rows that are 16 bytes apart in memory (neighbouring pixels of
-// four floats) are the rows of a core matrix as they lie.
-__device__ __forceinline__ uint64_t umma_desc_k_plain(uint32_t smem_byte_addr, uint32_t lbo, uint32_t sbo) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_byte_addr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>((lbo & 0x3FFFF) >> 4) << 16;
-  d |= static_cast<uint64_t>((sbo & 0x3FFFF) >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;                           // descriptor version (Blackwell)
-  return d;                                                      // layout bits 61..63 = 0: no swizzle
 }
 
 // Instruction descriptor, kind::tf32, fp32 accumulate, A and B K-major, M x N tile.

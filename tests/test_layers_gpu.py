@@ -108,24 +108,6 @@ def test_first_layer_convolution_with_wide_rows(capi, gpu_engine, reflib, channe
     assert_close(got["c"], want["c"], "wide first layer")
 
 
-@pytest.mark.parametrize("size,k,stride,pad,cout", [((23, 300), 3, 1, 1, 64), ((30, 257), 7, 2, 3, 24),
-                                                    ((17, 40), 3, 2, 1, 32)])
-def test_first_layer_strip_form(monkeypatch, capi, gpu_engine, reflib, size, k, stride, pad, cout):
-    """The opt-in strip form of row mode (the padded image sorted into stride_w planes, one load per
-    filter row, un-swizzled operand descriptors) computes what the default form computes."""
-    monkeypatch.setenv("MCB200_ROWS_STRIP", "1")
-    wl = pkg("workloads")
-    b = wl.NetBuilder("strip")
-    b.input([("data", (2, 3) + size)])
-    b.conv("c", "data", "c", 3, cout, k, stride=stride, pad=pad)
-    b.relu("c_relu", "c")
-    weights = wl.init_params(b.params, seed=23)
-    x = {"data": np.random.default_rng(24).standard_normal((2, 3) + size).astype(np.float32)}
-    got, want = both(capi, gpu_engine, reflib, b, weights, x, ["c"])
-    assert_close(got["c"], want["c"], "strip form")
-    assert tensor_core_launches(capi, gpu_engine, b, weights, x) == 1
-
-
 @pytest.mark.parametrize("stride,size", [(1, (14, 14)), (2, (15, 9)), (1, (5, 3)), (2, (2, 2)), (1, (17, 23)),
                                          (2, (33, 19)), (1, (8, 8)), (2, (16, 17))])
 def test_depthwise_3x3_sizes(capi, gpu_engine, reflib, stride, size):
