@@ -890,16 +890,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               cur_slot = 0;
               cur_parity ^= 1u;
             }
-          } else if (g >= slots) {
-            // The store that last used this slot must have finished reading it.
-            if (lane == 0) {
-              if (slots == 2) {
-                tma_store_wait_read<1>();
-              } else {
-                tma_store_wait_read<0>();
-              }
-            }
-            __syncwarp();
           }
           MCB200_TRACE_CHUNK();
           // Row `lane` of the 32 x 32 tile is 128 bytes: eight 16-byte pieces,
@@ -950,6 +940,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (ep.round_tf32) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) round4(v[j]);
+          }
+          if (!has_res && g >= slots) {
+            // The store that last used this slot must have finished reading it.  Asked only now,
+            // with the chunk's values in registers: the query costs its thread some 200 cycles
+            // whatever the answer, which the table loads above spend in flight.
+            if (lane == 0) {
+              if (slots == 2) {
+                tma_store_wait_read<1>();
+              } else {
+                tma_store_wait_read<0>();
+              }
+            }
+            __syncwarp();
           }
           // Residual and result rows of different widths overlap other lanes' rows.
           if (has_res && (args.out_half != 0) != kHalf) __syncwarp();
