@@ -433,6 +433,20 @@ def secondary_figures(capi, wl, engine, L, stream, torch, peaks, tf32_peak, rank
                                          tf32_peak, reps=10)
     out["detection_output"] = detection_output_figure(capi, wl, engine, L, stream, torch)
     out["resnet50_bf16_storage"] = bf16_storage_figure(capi, wl, engine, L, stream, torch)
+    # The shipped WGAN generator's structure at its own batch (64): five Deconvolution layers on the
+    # tensor-core kernel (stride-1 convolution, reversed filter, of the input spread over zeros).
+    gb = wl.wgan_generator(64)
+    gnet = build_net(capi, engine, gb, wl.init_params(gb.params, seed=0, bn_identity=False))
+    gnet.forward(**wl.wgan_noise(64))
+    gms = time_forwards(engine, L, gnet, stream, torch, 30)
+    gnet.close()
+    # useful FLOPs of a transposed convolution: every input element meets every filter tap once
+    gflops, cin, side = 0, 100, 1
+    for i, cout in enumerate((512, 256, 128, 64, 3)):
+        gflops += 2 * 64 * side * side * cin * cout * 16
+        side, cin = (4 if i == 0 else side * 2), cout
+    out["wgan_g"] = {"batch": 64, "ms_per_step": gms, "images_per_s": 64 / (gms * 1e-3), "deconv_flops": gflops,
+                     "tf32_tflops_achieved": gflops / (gms * 1e-3) / 1e12, "deconvolution_layers": 5}
 
     if ref is not None:
         out["proposal"]["cpu_baseline"] = proposal_cpu(capi, wl, ref)
@@ -444,6 +458,9 @@ def secondary_figures(capi, wl, engine, L, stream, torch, peaks, tf32_peak, rank
         ms = cpu_forward_ms(capi, ref, small, wl.init_params(small.params, seed=0), wl.normal_image_input(4, seed=0))
         out["mobilenet_v1_b64"]["cpu_baseline"] = {"images_per_s": 4 / (ms * 1e-3), "batch": 4, "cores": os.cpu_count(),
                                                    "kind": "reference", "sample": "1 pass at batch 4"}
+        ms = cpu_forward_ms(capi, ref, gb, wl.init_params(gb.params, seed=0, bn_identity=False), wl.wgan_noise(64))
+        out["wgan_g"]["cpu_baseline"] = {"images_per_s": 64 / (ms * 1e-3), "batch": 64, "cores": os.cpu_count(),
+                                         "kind": "reference", "sample": "1 pass at batch 64"}
         small = wl.ssd300_vgg16(1)
         ms = cpu_forward_ms(capi, ref, small, wl.init_params(small.params, seed=0), wl.ssd_input(1, seed=0))
         out["ssd300_b32"]["cpu_baseline"] = {"images_per_s": 1 / (ms * 1e-3), "batch": 1, "cores": os.cpu_count(),
@@ -505,6 +522,9 @@ def init_ranks(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the one JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     def barrier():

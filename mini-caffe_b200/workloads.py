@@ -267,6 +267,35 @@ def mobilenet_v1(batch, num_classes=1000):
     return b
 
 
+def wgan_generator(batch, noise=100, widths=(512, 256, 128, 64)):
+    """The structure of mini-caffe's shipped WGAN generator (example/models/wgan/g.prototxt): noise
+    [batch, 100, 1, 1] -> Deconvolution 4x4 to 4 x 4 x 512 -> three Deconvolutions 4x4 stride 2 pad 1
+    (each followed by BatchNorm on batch statistics, Scale, ReLU) -> Deconvolution to 3 x 64 x 64 -> TanH."""
+    b = NetBuilder("wgan_g")
+    b.input([("z", (batch, noise, 1, 1))])
+    prev, cin = "z", noise
+    for i, cout in enumerate(widths):
+        name = "deconv%d" % i
+        geometry = "kernel_size: 4" if i == 0 else "kernel_size: 4 stride: 2 pad: 1"
+        b.raw(name, "Deconvolution", [prev], [name], "convolution_param { num_output: %d %s bias_term: false }" % (cout, geometry))
+        b.params.append((name + "_0", (cin, cout, 4, 4), "he", cin))
+        b.raw("bn%d" % i, "BatchNorm", [name], [name], "batch_norm_param { use_global_stats: false }")
+        for j, kind in enumerate(("bn_mean", "bn_var", "one")):
+            b.params.append(("bn%d_%d" % (i, j), (cout,) if j < 2 else (1,), kind, 0))
+        b.scale("scale%d" % i, name, cout)
+        b.relu("relu%d" % i, name)
+        prev, cin = name, cout
+    b.raw("out", "Deconvolution", [prev], ["out"], "convolution_param { num_output: 3 kernel_size: 4 stride: 2 pad: 1 }")
+    b.params.append(("out_0", (cin, 3, 4, 4), "he", cin))
+    b.params.append(("out_1", (3,), "uniform", 0))
+    b.raw("tanh", "TanH", ["out"], ["image"])
+    return b
+
+
+def wgan_noise(batch, noise=100, seed=0):
+    return {"z": np.random.default_rng(seed + 5000).standard_normal((batch, noise, 1, 1)).astype(np.float32)}
+
+
 def normal_image_input(batch, size=224, seed=0):
     return {"data": np.random.default_rng(seed + 3000).standard_normal((batch, 3, size, size)).astype(np.float32)}
 
