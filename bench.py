@@ -433,6 +433,15 @@ def secondary_figures(capi, wl, engine, L, stream, torch, peaks, tf32_peak, rank
                                          tf32_peak, reps=10)
     out["detection_output"] = detection_output_figure(capi, wl, engine, L, stream, torch)
     out["resnet50_bf16_storage"] = bf16_storage_figure(capi, wl, engine, L, stream, torch)
+    # The other batch sizes the benchmark definition names for ResNet-50 (64 is the headline)
+    sweep = {}
+    for b in (1, 16, 256):
+        rnet = build_resnet(capi, wl, engine, b)
+        rnet.forward(**wl.image_input(b, seed=0))
+        ms = time_forwards(engine, L, rnet, stream, torch, 30 if b < 256 else 10)
+        rnet.close()
+        sweep[str(b)] = {"ms_per_step": ms, "images_per_s": b / (ms * 1e-3)}
+    out["resnet50_batch_sweep"] = sweep
     # The shipped WGAN generator's structure at its own batch (64): five Deconvolution layers on the
     # tensor-core kernel (stride-1 convolution, reversed filter, of the input spread over zeros).
     gb = wl.wgan_generator(64)

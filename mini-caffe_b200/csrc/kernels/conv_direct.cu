@@ -104,6 +104,9 @@ template <int STRIDE, bool IN_HALF, bool OUT_HALF>
 __global__ void __launch_bounds__(256)
 depthwise3x3_kernel(const void* __restrict__ in_any, const float* __restrict__ w, void* __restrict__ out_any,
                     mcb200_conv_shape s, mcb200_epilogue ep) {
+  // the pointwise convolution behind this layer may set itself up meanwhile (it waits with
+  // griddepcontrol.wait before it touches a tensor)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const float* in = static_cast<const float*>(in_any);
   const uint16_t* in16 = static_cast<const uint16_t*>(in_any);
   float* out = static_cast<float*>(out_any);

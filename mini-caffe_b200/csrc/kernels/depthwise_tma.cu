@@ -80,6 +80,11 @@ __global__ void __launch_bounds__(256) depthwise3x3_tma_kernel(const __grid_cons
     tma_prefetch_descriptor(&map_in);
   }
   __syncthreads();
+  // Up to here the CTA has only set itself up, which may overlap the tail of the previous launch of
+  // the stream (programmatic dependent launch); from here on it touches tensors.  The next launch
+  // may begin its own set-up as soon as every CTA of this one has got this far.
+  grid_launch_dependents();
+  grid_dependency_wait();
   volatile int* abort = &abort_flag;
 
   // tile index -> (channel block, tile column, tile row, image); channel blocks fastest, so that
@@ -258,9 +263,19 @@ int launch_dw(const mcb200_conv_shape& s, const float* in, const DwArgs& args, c
   if (per_sm < 1) per_sm = 1;
   long long blocks = static_cast<long long>(sms) * per_sm;
   if (blocks > args.tiles) blocks = args.tiles;
-  kernel<<<static_cast<unsigned>(blocks), 256, smem, st>>>(map, args, stage_count);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel orders itself with griddepcontrol.wait
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t launched = cudaLaunchKernelEx(&cfg, kernel, map, args, stage_count);
   count_launch();
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launched);
 }
 
 }  // namespace

@@ -24,6 +24,11 @@ inline int grid_for(long long work_items, int threads, int max_blocks_per_sm = 1
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
+// A following launch that uses programmatic dependent launch (the convolution kernels do) may begin
+// its set-up once every block of this kernel has got here; it waits with griddepcontrol.wait
+// before it touches a tensor, so nothing else changes.
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float activate(float v, int act, float slope) {
   return (act != 0 && v <= 0.f) ? v * slope : v;
 }
@@ -165,6 +170,7 @@ __device__ __forceinline__ float eltwise_combine(float acc, float v, float coeff
 }
 
 __global__ void eltwise_vec4_kernel(EltwiseArgs a, float4* __restrict__ out, long long count4) {
+  allow_dependents();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < count4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -201,6 +207,7 @@ struct PoolArgs {
 // One thread per output pixel and group of VEC channels.
 template <int VEC>
 __global__ void pool_nhwc_kernel(const float* __restrict__ in, float* __restrict__ out, PoolArgs a) {
+  allow_dependents();
   const int cg = a.c / VEC;
   const long long total = static_cast<long long>(a.n) * a.ho * a.wo * cg;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -281,6 +288,7 @@ constexpr int kGlobalPoolWarps = 8;
 __global__ void __launch_bounds__(32 * kGlobalPoolWarps)
 pool_global_kernel(const float4* __restrict__ in, float4* __restrict__ out, int pixels, int cg, int chunks, int method,
                    float area) {
+  allow_dependents();
   __shared__ float4 part[kGlobalPoolWarps][32];
   const int n = blockIdx.x / chunks;
   const int g = (blockIdx.x - n * chunks) * 32 + (threadIdx.x & 31);   // group of four channels
@@ -339,6 +347,7 @@ pool_global_kernel(const float4* __restrict__ in, float4* __restrict__ out, int 
 // dependent loop; index arithmetic is 32-bit.
 template <int K>
 __global__ void pool_max_small_kernel(const float4* __restrict__ in, float4* __restrict__ out, PoolArgs a) {
+  allow_dependents();
   const int cg = a.c >> 2;
   const unsigned total = static_cast<unsigned>(a.n) * a.ho * a.wo * cg;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -555,6 +564,7 @@ __global__ void permute_kernel(const float* __restrict__ in, float* __restrict__
 // One warp per pixel: sum of squares by shuffle, then scale.
 __global__ void normalize_nhwc_kernel(const float* __restrict__ in, float* __restrict__ out, long long pixels,
                                       int channels, const float* __restrict__ scale, int scale_shared, float eps) {
+  allow_dependents();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (long long p = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); p < pixels;
