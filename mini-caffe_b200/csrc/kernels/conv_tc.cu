@@ -1931,27 +1931,30 @@ __global__ void pack_rows_weights_kernel(const float* __restrict__ w, float* __r
   }
 }
 
-// (N, C<=4, H, W) -> zero-bordered channels-last copy with 4 floats per pixel.  One block row per
-// padded image row (blockIdx.y = image * hp + row), one thread per pixel: no index divisions, one
-// coalesced read per colour plane and one 16-byte write.
-__global__ void pad_nhwc4_kernel(const float* __restrict__ src, float4* __restrict__ dst, int c, int h, int w,
+// (N, C<=4, H, W) -> zero-bordered channels-last copy with 4 floats per pixel.
+__global__ void pad_nhwc4_kernel(const float* __restrict__ src, float4* __restrict__ dst, int n, int c, int h, int w,
                                  int pad_h, int pad_w, int hp, int wp) {
   grid_launch_dependents();   // the convolution behind this copy may set itself up meanwhile
-  const int xp = blockIdx.x * blockDim.x + threadIdx.x;
-  if (xp >= wp) return;
-  const int img = blockIdx.y / hp;
-  const int yp = blockIdx.y - img * hp;
-  const int x = xp - pad_w, y = yp - pad_h;
+  // (A form with one block row per padded image row and no index divisions was measured: 33.8 us
+  // against 24.7 us for 64 x 3 x 224 x 224: many small blocks with three loads per thread.)
+  const long long total = static_cast<long long>(n) * hp * wp;
   const size_t plane = static_cast<size_t>(h) * w;
-  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (x >= 0 && x < w && y >= 0 && y < h) {
-    const float* s = src + static_cast<size_t>(img) * c * plane + static_cast<size_t>(y) * w + x;
-    v.x = __ldg(s);
-    if (c > 1) v.y = __ldg(s + plane);
-    if (c > 2) v.z = __ldg(s + 2 * plane);
-    if (c > 3) v.w = __ldg(s + 3 * plane);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int xp = static_cast<int>(i % wp);
+    const int yp = static_cast<int>((i / wp) % hp);
+    const int img = static_cast<int>(i / (static_cast<long long>(wp) * hp));
+    const int x = xp - pad_w, y = yp - pad_h;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (x >= 0 && x < w && y >= 0 && y < h) {
+      const float* s = src + static_cast<size_t>(img) * c * plane + static_cast<size_t>(y) * w + x;
+      v.x = s[0];
+      if (c > 1) v.y = s[plane];
+      if (c > 2) v.z = s[2 * plane];
+      if (c > 3) v.w = s[3 * plane];
+    }
+    dst[i] = v;
   }
-  dst[static_cast<size_t>(blockIdx.y) * wp + xp] = v;
 }
 
 }  // namespace
@@ -1995,18 +1998,10 @@ extern "C" int mcb200_conv_rows_pad_input(const mcb200_conv_shape* s, const floa
   if (reinterpret_cast<uintptr_t>(padded) & 15) return -2;
   const long long total = static_cast<long long>(s->n) * hp * wp;
   if (total == 0) return 0;
-  const long long rows = static_cast<long long>(s->n) * hp;
-  if (rows > 0x7fffffffLL) return -3;
-  // grid.y carries (image, row); images beyond its 65535 limit go in further launches
-  const int rows_per_launch = 65535 / hp * hp;
-  if (rows_per_launch == 0) return -3;
-  for (long long first = 0; first < rows; first += rows_per_launch) {
-    const int count = static_cast<int>(rows - first < rows_per_launch ? rows - first : rows_per_launch);
-    const long long img0 = first / hp;
-    pad_nhwc4_kernel<<<dim3((wp + 127) / 128, count, 1), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        src_nchw + img0 * s->c * s->h * s->w, reinterpret_cast<float4*>(padded) + first * wp, s->c, s->h, s->w, s->pad_h,
-        s->pad_w, hp, wp);
-  }
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  pad_nhwc4_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src_nchw, reinterpret_cast<float4*>(padded), s->n, s->c, s->h, s->w, s->pad_h, s->pad_w, hp, wp);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
