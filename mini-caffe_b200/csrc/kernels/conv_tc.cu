@@ -1297,7 +1297,12 @@ int pick_block_n(int cout, long long m, int k_iters, double* cost_out = nullptr)
     if (bn > 64 && bn / 2 >= cout) break;   // wider than the layer: only padding
     const long long tiles = m_tiles * ((cout + bn - 1) / bn);
     const long long waves = (tiles + 147) / 148;
-    const double per_tile = static_cast<double>(k_iters) * (kTileABytes + 128.0 * bn) + 8192.0 * (bn / 32);
+    // 64 KiB of operand-byte equivalents per 32-column chunk of epilogue: a chunk costs a warp
+    // 1400-2300 cycles (two warps per tensor-memory quadrant), as long as some 64 KiB take to
+    // arrive.  (Measured in interleaved runs of the three benchmark networks: the 8 KiB this
+    // started with sent the 128 -> 512 residual layers of ResNet-50 to 256-column tiles, six waves
+    // of eight chunks where eleven waves of four are 6 % quicker; values of 48-96 KiB agree.)
+    const double per_tile = static_cast<double>(k_iters) * (kTileABytes + 128.0 * bn) + 65536.0 * (bn / 32);
     const double cost = static_cast<double>(waves) * per_tile;
     if (bn == 64 || cost < best_cost * 0.97) {   // prefer the narrower tile on near ties
       best = bn;
@@ -1360,7 +1365,9 @@ int pick_block_n_halo(int cout, long long m_virtual, int k_iters, int kw, int st
 int pick_cta_pair(int block_n, long long m, int k_iters) {
   const char* force = getenv("MCB200_CTA_PAIR");   // "0" / "1": override for experiments
   if (force && (force[0] == '0' || force[0] == '1')) return block_n >= 128 && force[0] == '1' ? 1 : 0;
-  return (block_n >= 128 && m > kBlockM && k_iters > 16) ? 1 : 0;
+  // 256-column tiles pair from 16 k-iterations (the 512 -> 1024 stride-2 projection of ResNet-50:
+  // 39 -> 34 us), 128-column tiles from 17 (the 512 -> 2048 residual layers lose 1-2 us at 16).
+  return (block_n >= 128 && m > kBlockM && k_iters >= (block_n == 256 ? 16 : 17)) ? 1 : 0;
 }
 
 // Tile map for the staged epilogue over a row-major matrix with row pitch `ld`
