@@ -1432,29 +1432,24 @@ cudaError_t launch_variant(const mcb200_conv_plan* plan, ConvTcArgs args, cudaSt
   const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
   const long long workers_max = kPair ? sms / 2 : sms;
   const unsigned workers = static_cast<unsigned>(tiles < workers_max ? tiles : workers_max);
-  // Staging slots per epilogue warp.  With a residual: three where tiles are so
-  // short that the ring needs little (load, work and store of consecutive
-  // chunks overlap), else two.  Without: two when the epilogue is the busy
-  // or the exposed part (few k-iterations per tile, or a single tile per CTA so
-  // that no next main loop covers it); otherwise one, and a deeper ring.
+  // Staging slots per epilogue warp.  With a residual: three where tiles are so short that the
+  // ring needs little (load, work and store of consecutive chunks overlap), else two.  Without:
+  // one, and the ring takes the rest.  (Two slots for short or single tiles were the rule until
+  // interleaved runs on one GPU showed one slot to be as quick or quicker on every layer of the
+  // three benchmark networks: ResNet-50 1.963 -> 1.946 ms per pass, MobileNet-v1 0.778 -> 0.776,
+  // SSD300 5.00 -> 4.98; a 7 x 7 first layer keeps eight activation tiles in flight instead of six.)
   const int k_units = args.k_iters * (kHalf ? 2 : 1);   // in 32-channel steps, the unit the rules were measured in
-  args.slots = args.ep.residual != nullptr ? (k_units <= 4 ? 3 : 2)
-                                           : ((k_units < 16 || tiles <= workers_max) ? 2 : 1);
+  args.slots = args.ep.residual != nullptr ? (k_units <= 4 ? 3 : 2) : 1;
   args.res_depth = 1;
-  if (args.ep.residual != nullptr) {
+  if (args.ep.residual == nullptr) {
+    const char* force = getenv("MCB200_SLOTS");   // experiments: "1" / "2"
+    if (force && (force[0] == '1' || force[0] == '2')) args.slots = force[0] - '0';
+  } else {
     const char* force_slots = getenv("MCB200_RES_SLOTS");   // experiments: "2" .. "8"
     const char* force_depth = getenv("MCB200_RES_DEPTH");   // experiments: "1" .. slots - 1
     if (force_slots && atoi(force_slots) >= 2 && atoi(force_slots) <= kMaxSlots) args.slots = atoi(force_slots);
     if (force_depth && atoi(force_depth) >= 1) args.res_depth = atoi(force_depth);
     if (args.res_depth > args.slots - 1) args.res_depth = args.slots - 1;
-  }
-  if (kMode == kModeRows && !args.ep.residual) {
-    // Filters of five rows and more: one staging slot per warp, so that the ring keeps eight
-    // activation tiles in flight instead of six (interleaved runs on one GPU: ResNet-50 1.999 ->
-    // 1.988 ms per pass; the three-row first layers of MobileNet and SSD300 do not change).
-    if (args.k_iters >= 5) args.slots = 1;
-    const char* force_slots = getenv("MCB200_ROWS_SLOTS");   // experiments: "1" / "2"
-    if (force_slots && (force_slots[0] == '1' || force_slots[0] == '2')) args.slots = force_slots[0] - '0';
   }
   const int slot_bytes = (kHalf && args.out_half) ? 2048 : 4096;
   int stage_bytes = Plan::kStageBytes;
