@@ -361,9 +361,20 @@ def dense_net_figure(capi, wl, engine, L, stream, torch, builder, feed, batch, p
     net.forward(**feed)
     work = wl.conv_work(builder, {name: blob.shape for name, blob in net.blobs()})
     ms = time_forwards(engine, L, net, stream, torch, reps)
+    # each tensor-core convolution launch's own duration, in launch order (median of five passes)
+    passes = []
+    for _ in range(5):
+        L.mcb200_kernel_timing_begin()
+        engine.check(L.CaffeNetForward(net.handle))
+        total = ctypes.c_double(0.0)
+        each = (ctypes.c_double * 512)()
+        n = int(L.mcb200_kernel_timing_end_each(ctypes.byref(total), each, 512))
+        passes.append([each[i] * 1e3 for i in range(min(n, 512))])
+    conv_tc_us = ([round(sorted(p[i] for p in passes)[2], 1) for i in range(len(passes[0]))]
+                  if all(len(p) == len(passes[0]) for p in passes) else [])
     net.close()
     out = {"batch": batch, "ms_per_step": ms, "images_per_s": batch / (ms * 1e-3), "conv_flops": work["flops"],
-           "conv_algorithmic_bytes": work["bytes"], "conv_layers": work["layers"]}
+           "conv_algorithmic_bytes": work["bytes"], "conv_layers": work["layers"], "conv_tc_launch_us": conv_tc_us}
     out.update(bound_of(work["flops"], work["bytes"], ms, peaks, tf32_peak))
     return out
 
