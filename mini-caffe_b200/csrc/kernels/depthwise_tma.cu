@@ -19,6 +19,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -237,9 +238,16 @@ int launch_dw(const mcb200_conv_shape& s, const float* in, const DwArgs& args, c
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return -11;
   auto kernel = depthwise3x3_tma_kernel<STRIDE>;
-  // Four boxes per CTA at stride 1 (2 CTAs per SM by registers: 190 KB in flight per SM), two at
-  // stride 2 (one CTA per SM by shared memory: 144 KB).
-  const int stage_count = STRIDE == 1 ? 4 : 2;
+  // Boxes per CTA: two at stride 1 (two CTAs per SM by registers), three at stride 2 (one CTA per
+  // SM by shared memory: 215 KB).  Measured in interleaved MobileNet-v1 passes at batch 64 (0.777 ms
+  // with four and two boxes): three boxes at stride 2 0.773, and two instead of four at stride 1
+  // on top of that 0.771; with the launches chained (programmatic dependent launch) a deeper ring at
+  // stride 1 no longer pays.
+  int stage_count = STRIDE == 1 ? 2 : 3;
+  if (const char* env = getenv(STRIDE == 1 ? "MCB200_DW_STAGES_S1" : "MCB200_DW_STAGES_S2")) {   // experiments
+    const int v = atoi(env);
+    if (v >= 2 && v <= kMaxDwStages && v * Box::kStageBytes + 2048 <= 227 * 1024) stage_count = v;
+  }
   const int smem = stage_count * Box::kStageBytes + 1024;
   int dev = 0;
   cudaGetDevice(&dev);
