@@ -55,7 +55,7 @@ E2E_THREADS = 2        # host threads per GPU in the end-to-end leg, each with i
 # the 54 launches of one pass at batch 64) from one ncu launch-list capture of this workload, and
 # the hash of the kernel sources the capture was made with.  A different hash means the figure is
 # stale: the line then carries null until the capture is repeated.
-CONV_TRAFFIC = {"bytes_per_launch": 87.99e6, "kernel_sha16": "fa709a58220a3074"}
+CONV_TRAFFIC = {"bytes_per_launch": 87.96e6, "kernel_sha16": "98fe4693f73f507b"}
 METRIC = "resnet50_images_per_sec"
 UNIT = "images/s"
 
@@ -542,10 +542,19 @@ def init_ranks(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the one JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL writes its version banner to file descriptor 1 when the first communicator comes up;
+        # stdout carries the one JSON line, so descriptor 1 points at stderr until that has happened.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     def barrier():
         if world > 1:

@@ -1702,10 +1702,6 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
       plan->im2col = kModeHalo;
       plan->m_virtual = static_cast<int>(mv);
       plan->strip_rows = kBlockM + halo_w;
-      if (const char* rows_env = getenv("MCB200_HALO_STRIP_ROWS")) {   // experiment: a longer strip than needed
-        const int rows = atoi(rows_env);
-        if (rows >= plan->strip_rows && rows <= 256) plan->strip_rows = rows;
-      }
       plan->k_iters = halo_k_iters;
       plan->block_n = bn;
       plan->cta_pair = pair;
