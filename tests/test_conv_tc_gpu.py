@@ -396,6 +396,27 @@ def test_planner_takes_halo_mode_for_the_benchmark_layers(kernels):
             assert plan.im2col == mode, (c, hw, n, plan.im2col)
 
 
+def test_planner_widths_and_pairing_for_measured_layers(kernels):
+    """Planner rules that were set from interleaved runs of the benchmark networks: halo mode keeps to
+    128-column tiles (paired where there are two M tiles), 256-column tiles pair from 16
+    k-iterations, 128-column tiles from 17, and the 128 -> 512 layers of ResNet-50's third stage take
+    128-column tiles.  Width and pairing do not change the order of the sums over K."""
+    cases = [
+        # n, c, hw, cout, k, stride, pad -> mode, width, pair
+        (8, 512, 38, 512, 3, 1, 1, 3, 128, 1),      # VGG conv4_2 at 300 x 300
+        (8, 256, 75, 256, 3, 1, 1, 3, 128, 1),      # VGG conv3_2
+        (64, 512, 28, 1024, 1, 2, 0, 1, 256, 1),    # ResNet-50 res4a_branch1: 16 k-iterations
+        (64, 512, 28, 128, 1, 1, 0, 0, 128, 0),     # res3b_branch2a: 16 k-iterations at 128 columns
+        (64, 128, 28, 512, 1, 1, 0, 0, 128, 0),     # res3b_branch2c: four k-iterations, many waves
+    ]
+    for n, c, hw, cout, k, stride, pad, mode, width, pair in cases:
+        x = torch.zeros((n, c, hw, hw), device="cuda")
+        wt = torch.zeros((cout, c, k, k))
+        _, plan = run_conv(kernels, x, wt, stride=stride, pad=pad, dil=1)
+        assert (plan.im2col, plan.block_n, plan.cta_pair) == (mode, width, pair), (c, hw, cout, plan.im2col, plan.block_n,
+                                                                                   plan.cta_pair)
+
+
 @pytest.mark.parametrize("halo", ["0", "1"])
 def test_bounded_waits_run_out_and_the_context_stays_usable(kernels, halo):
     """Every barrier wait of the kernel is bounded.  The test hook makes the weight producer leave out
