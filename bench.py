@@ -55,7 +55,7 @@ E2E_THREADS = 2        # host threads per GPU in the end-to-end leg, each with i
 # the 54 launches of one pass at batch 64) from one ncu launch-list capture of this workload, and
 # the hash of the kernel sources the capture was made with.  A different hash means the figure is
 # stale: the line then carries null until the capture is repeated.
-CONV_TRAFFIC = {"bytes_per_launch": 87.96e6, "kernel_sha16": "98fe4693f73f507b"}
+CONV_TRAFFIC = {"bytes_per_launch": 87.96e6, "kernel_sha16": "fb7a1d4658a37bed"}
 METRIC = "resnet50_images_per_sec"
 UNIT = "images/s"
 

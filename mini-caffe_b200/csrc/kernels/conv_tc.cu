@@ -1681,13 +1681,15 @@ int plan_core(const mcb200_conv_shape* s, const void* in, const void* packed_w, 
   // 52.8 -> 49.8 us, 28-pixel rows 37.1 -> 33.4, 7-pixel rows 43.0 -> 37.3, but 14-pixel rows 35.3
   // -> 43.3: there every CTA has a single 256-column tile, and the halo mode's epilogue (plain
   // stores, since a tile of the virtual grid is not a box of the output tensor) is exposed where
-  // the im2col mode's TMA tile stores are half as long.  Hence: rows of at least 24 output pixels
-  // (several tiles per CTA hide the epilogue) or at most 8 (the strips save the most), and never
-  // when the widened rows would cost more than half again as many positions.
+  // the im2col mode's TMA tile stores are half as long (37.2 against 35.5 us once the mode kept to
+  // 128-column tiles).  SSD300 at batch 32, 512 -> 512 on 19-pixel rows: 102 -> 82 us, the two
+  // detection heads on the same map 84 -> 69 and 66 -> 63; on its 10-pixel rows 36 -> 38.  Hence:
+  // rows of at least 16 output pixels or at most 8 (the strips save the most), and never when the
+  // widened rows would cost more than half again as many positions.
   const int halo_w = (s->kw - 1) * s->dil_w;
   const char* halo_env = getenv("MCB200_HALO");   // "0" / "1": override for experiments and tests
   const bool halo_forced = halo_env && halo_env[0] == '1';
-  const bool halo_pays = 2 * halo_w <= plan->shape.wo && (plan->shape.wo >= 24 || plan->shape.wo <= 8);
+  const bool halo_pays = 2 * halo_w <= plan->shape.wo && (plan->shape.wo >= 16 || plan->shape.wo <= 8);
   if (!pointwise && s->stride_h == 1 && s->stride_w == 1 && s->kw > 1 && halo_w <= kMaxHaloRows &&
       !(halo_env && halo_env[0] == '0') && (halo_forced || halo_pays)) {
     const long long mv = static_cast<long long>(s->n) * plan->shape.ho * (plan->shape.wo + halo_w);
