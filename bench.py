@@ -50,7 +50,19 @@ ENGINE_LIB = os.path.join(ROOT, "mini-caffe_b200", "lib", "libcaffe.so")
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libcaffe_ref.so")
 KERNEL_SOURCES = [os.path.join(ROOT, "mini-caffe_b200", "csrc", "kernels", f) for f in ("conv_tc.cu", "sm100.cuh")]
 BATCH_PER_GPU = 64
-E2E_THREADS = 2        # host threads per GPU in the end-to-end leg, each with its own Net
+def _e2e_threads():
+    """Host threads per GPU in the end-to-end leg, each with its own Net and stream.  Three where the
+    host has the cores for it: the third net's kernels run on the SMs that the under-filled launches
+    of the other two leave idle (measured on one B200: 31 500 images/s with two threads, 35 200 with
+    three or four); two when eight ranks share sixteen cores."""
+    forced = os.environ.get("MCB200_E2E_THREADS")
+    if forced:
+        return max(1, int(forced))
+    per_rank = (os.cpu_count() or 2) // max(1, int(os.environ.get("WORLD_SIZE", "1")))
+    return 3 if per_rank >= 3 else 2
+
+
+E2E_THREADS = _e2e_threads()
 # DRAM bytes per convolution launch (dram__bytes_read.sum + dram__bytes_write.sum, averaged over
 # the 54 launches of one pass at batch 64) from one ncu launch-list capture of this workload, and
 # the hash of the kernel sources the capture was made with.  A different hash means the figure is
