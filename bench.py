@@ -748,12 +748,20 @@ def main():
             for _ in range(2):
                 blob.data
                 engine.check(L.CaffeNetForward(own.handle))
+            share = args.steps // E2E_THREADS + (1 if tid < args.steps % E2E_THREADS else 0)
             for _ in range(e2e_repeats):
                 start_line.wait()
-                for _ in range(args.steps // E2E_THREADS + (1 if tid < args.steps % E2E_THREADS else 0)):
+                for _ in range(share):
                     blob.data
                     engine.check(L.CaffeNetForward(own.handle))
                     out.data
+                finish_line.wait()
+            # the same nets with the input left on the device: what the concurrency alone is worth
+            for _ in range(e2e_repeats):
+                start_line.wait()
+                for _ in range(share):
+                    engine.check(L.CaffeNetForward(own.handle))
+                out.data                     # one read at the end: waits for this thread's stream
                 finish_line.wait()
             own.close()
         except Exception as exc:   # surfaced by the main thread
@@ -765,6 +773,7 @@ def main():
     for w in workers:
         w.start()
     e2e_loops = []
+    resident_loops = []
     try:
         for _ in range(e2e_repeats):
             barrier()
@@ -775,6 +784,12 @@ def main():
             e2e_local = time.perf_counter() - t0
             windows.append((w0, time.monotonic()))
             e2e_loops.append(max_over_ranks(e2e_local))
+        for _ in range(e2e_repeats):
+            barrier()
+            start_line.wait()
+            t0 = time.perf_counter()
+            finish_line.wait()
+            resident_loops.append(max_over_ranks(time.perf_counter() - t0))
     except threading.BrokenBarrierError:
         e2e_loops.append(float("nan"))
     for w in workers:
@@ -785,6 +800,7 @@ def main():
     e2e_s = statistics.median(e2e_loops)
     clocks = sampler.finish(windows) if sampler else None
     e2e_value = world * batch * args.steps / e2e_s
+    concurrent_value = (world * batch * args.steps / statistics.median(resident_loops)) if resident_loops else None
     e2e_single_value = world * batch * args.steps / e2e_single_s
     h2d = int(np.prod(x.shape)) * 4
     d2h = int(np.prod(prob_blob.shape)) * 4
@@ -885,6 +901,11 @@ def main():
                     "loops_s": e2e_loops,
                     "how": "CaffeNetForward on host buffers; %d host threads per GPU, one Net each, K steps in total "
                            "per loop, median of %d loops" % (E2E_THREADS, e2e_repeats)},
+            "concurrent_nets": {"value": concurrent_value, "unit": UNIT, "nets_per_gpu": E2E_THREADS,
+                                "how": "the end-to-end leg's nets and threads with the input left on the device: K steps "
+                                       "in total per loop, one Net and stream per thread; kernels of one net run on the "
+                                       "SMs an under-filled launch of another leaves idle, so this exceeds `value`, "
+                                       "which is one Net on one stream"},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "secondary": extras,
             "cpu_baseline": cpu if cpu else {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
                                              "sample": "skipped (--no-cpu-baseline)" if args.no_cpu_baseline
